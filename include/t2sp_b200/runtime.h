@@ -1,0 +1,171 @@
+/* C ABI of libt2sp_b200.so: the B200 replacement for the host interface and device
+ * runtime that T2SP generates for its dense-tensor kernels.
+ *
+ * What it replaces in the reference:
+ *   - the generated host functions `int <k>(halide_buffer_t*...)`
+ *     (emitter Halide/src/CodeGen_C.cpp:1712-1738,2746-2818; checked-in example
+ *     t2s/peppers/blas/level3/syrk/release/s10/syrk-interface.{h,cpp}),
+ *   - the AOT device runtime they call (t2s/src/AOT-OpenCL-Runtime.{h,cpp}),
+ *   - the generated device kernels (e.g. t2s/tests/performance/gemm/bitstream/a10/a.cl).
+ *
+ * Conventions kept from the reference: inputs first, output last; return 0 on success,
+ * otherwise the negative halide_error_code_t that the matching halide_error_* reporter
+ * returns (HalideRuntime.h:957-1143); buffers are caller-owned; dim 0 is innermost with
+ * stride 1; a buffer with host==NULL and device==0 is a bounds query and gets its shape
+ * filled in. Differences: calls are repeatable and thread-safe, nothing ever exits the
+ * process, and there is no CPU fallback: without a CUDA device every compute entry fails
+ * with halide_error_code_device_interface_no_device.
+ */
+#ifndef T2SP_B200_RUNTIME_H
+#define T2SP_B200_RUNTIME_H
+
+#include "abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#ifdef T2SP_B200_OWN_HALIDE_ABI
+/* Subset of halide_error_code_t (HalideRuntime.h:957-1143) that this library returns. */
+enum halide_error_code_t {
+    halide_error_code_success = 0,
+    halide_error_code_generic_error = -1,
+    halide_error_code_bad_type = -3,
+    halide_error_code_access_out_of_bounds = -4,
+    halide_error_code_buffer_allocation_too_large = -5,
+    halide_error_code_buffer_extents_too_large = -6,
+    halide_error_code_constraint_violated = -8,
+    halide_error_code_out_of_memory = -11,
+    halide_error_code_buffer_argument_is_null = -12,
+    halide_error_code_copy_to_host_failed = -14,
+    halide_error_code_copy_to_device_failed = -15,
+    halide_error_code_device_malloc_failed = -16,
+    halide_error_code_device_sync_failed = -17,
+    halide_error_code_device_free_failed = -18,
+    halide_error_code_device_run_failed = -23,
+    halide_error_code_buffer_extents_negative = -28,
+    halide_error_code_host_is_null = -34,
+    halide_error_code_device_interface_no_device = -36,
+    halide_error_code_bad_dimensions = -43
+};
+#endif
+
+/* ---- element types accepted --------------------------------------------------------
+ * fp32 in / fp32 out (the reference's only type: type word 73730, syrk-interface.cpp:149);
+ * additionally bf16 or f16 in / fp32 out and int8 in / int32 out for GEMM.            */
+
+/* How fp32 inputs are multiplied on the tensor cores. */
+enum t2sp_precision {
+    T2SP_PRECISION_DEFAULT = 0, /* $T2SP_B200_PRECISION if set, else TF32X3 */
+    T2SP_PRECISION_TF32X3 = 1   /* three TF32 MMAs per product, ~fp32 accuracy */
+};
+
+/* ---- GEMM:  C[i,j] = sum_k A[i,k] * B[k,j]          (t2s/tests/performance/gemm/gemm.cpp:30-63)
+ * A: 2-D (K_tot, I_tot), B: 2-D (J_tot, K_tot)                                (gemm.cpp:58-59)
+ * C: layout 0 = 2-D (J_tot, I_tot)                               (gemm.cpp:89, gemm-run-gpu.cpp:58)
+ *    layout 1 = 6-D (JJJ, III, JJ, II, J, I), element (jjj,iii,jj,ii,j,i) holds
+ *               C[iii + III*ii + III*II*i, jjj + JJJ*jj + JJJ*JJ*j]    (gemm-run-fpga.cpp:69,80-85)
+ * With desc == NULL the layout is taken from C->dimensions and, for 6-D, the tile extents
+ * from C's own extents.                                                                */
+typedef struct t2sp_gemm_desc {
+    int32_t layout;
+    int32_t JJJ, III, JJ, II; /* layout 1: inner tile extents (0 = read them from C) */
+    int32_t precision;        /* enum t2sp_precision */
+} t2sp_gemm_desc;
+int t2sp_b200_gemm(halide_buffer_t *A, halide_buffer_t *B, halide_buffer_t *C, const t2sp_gemm_desc *desc);
+
+/* ---- 2-D convolution, stride 1, input already enlarged by KX-1 / KY-1
+ *                                                     (t2s/tests/performance/conv/conv.cpp:30-65)
+ * I: 2-D (CI*N, IY*IX)    element (ci + CI*n, iy + IY*ix)                     (conv.cpp:52)
+ * K: 2-D (CO*KX, CI*KY)   element (co + CO*kx, ci + CI*ky)                    (conv.cpp:53)
+ * O: layout 0 = 2-D (CO*N, OY*OX)  element (co + CO*n, oy + OY*ox)            (conv.cpp:54)
+ *    layout 1 = 10-D (COOO,YYY,XXX,COO,YY,XX,Y,X,CO,N)              (conv-run-fpga.cpp:68,73-93)
+ * The flattened 2-D buffers cannot be un-flattened without CI, CO, KY, KX, OY, OX, which
+ * the reference bakes into the generated code from const-parameters.h; here they arrive
+ * in the descriptor. N is read from the buffers.                                       */
+typedef struct t2sp_conv_desc {
+    int32_t layout;
+    int32_t CI, CO, KY, KX, OY, OX;              /* totals */
+    int32_t COOO, YYY, XXX, COO, YY, XX, Y, X;   /* layout 1 tile extents (CO outer and N come from O) */
+    int32_t precision;
+} t2sp_conv_desc;
+int t2sp_b200_conv(halide_buffer_t *I, halide_buffer_t *K, halide_buffer_t *O, const t2sp_conv_desc *desc);
+
+/* ---- capsule convolution: per output pose V[my,mx] = sum W[my,mk] * P[mk,mx] over
+ * (mk, ci, ky, kx), input position (s*oy+ky, s*ox+kx)   (t2s/tests/performance/capsule/capsule.cpp:28-66)
+ * P: 2-D (CI*MK*MX*NN, IY*IX*N)   element (ci + CI*mk + CI*MK*mx + CI*MK*MX*nn, iy + IY*ix + IY*IX*n)
+ * W: 2-D (CO*MY, CI*KY*KX*MK)     element (co + CO*my, cii + CII*ky + CII*KY*kx + CII*KY*KX*ci_o + CI*KY*KX*mk)
+ * V: layout 0 = 2-D (CO*MY*MX*NN, OY*OX*N)                                 (capsule.cpp:52-54)
+ *    layout 1 = 10-D (COOO,YYY_XXX,YY_XX,Y_X,MY,MX,COO,NN,CO,N), pixel slot
+ *               p = yyy_xxx + YYY_XXX*yy_xx + YYY_XXX*YY_XX*y_x, oy = p % OY, ox = p / OY;
+ *               slots with p >= OY*OX are written as 0        (capsule-run-fpga.cpp:73,78-104)
+ * IY = s*OY + KY - s, IX likewise. The reference hard-codes s = 2 (capsule.cpp:40-41). */
+typedef struct t2sp_capsule_desc {
+    int32_t layout;
+    int32_t CI, CII, CO, KY, KX, OY, OX, MY, MX, MK, NN, stride;
+    int32_t COOO, YYY_XXX, YY_XX, Y_X, COO;      /* layout 1 tile extents */
+    int32_t precision;
+} t2sp_capsule_desc;
+int t2sp_b200_capsule(halide_buffer_t *P, halide_buffer_t *W, halide_buffer_t *V, const t2sp_capsule_desc *desc);
+
+/* ---- TTM:  c(i,j,k) = sum_l a(l,i,j) * b(l,k)   (t2s/tests/correctness/buffer/tmm_small.cpp:46-64,
+ *                                                  golden t2s/tests/correctness/util/util.h:428-441)
+ * a: 3-D (L,I,J), b: 2-D (L,K)
+ * c: layout 0 = 3-D (I,J,K)
+ *    layout 1 = 9-D (JJ,KK,II,KKK,JJJ,III,OK,OJ,OI) with i = iii + III*ii + III*II*oi,
+ *               j = jjj + JJJ*jj + JJJ*JJ*oj, k = kkk + KKK*kk + KKK*KK*ok  (tmm_small.cpp:116-129) */
+typedef struct t2sp_ttm_desc {
+    int32_t layout;
+    int32_t precision;
+} t2sp_ttm_desc;
+int t2sp_b200_ttm(halide_buffer_t *a, halide_buffer_t *b, halide_buffer_t *c, const t2sp_ttm_desc *desc);
+
+/* ---- MTTKRP:  d(i,r) = sum_k ( sum_l a(l,i,k) * c(l,r) ) * b(k,r)
+ *                                   (golden only: t2s/tests/correctness/util/util.h:464-481, with
+ *                                    its outer loop bound `i < K` read as `i < I`)
+ * a: 3-D (L,I,K), b: 2-D (K,R), c: 2-D (L,R), d: 2-D (I,R). Argument order follows the
+ * golden helper: (a, b, c, d). The Khatri-Rao product of b and c is formed tile by tile
+ * in shared memory and never written to global memory.                                 */
+typedef struct t2sp_mttkrp_desc {
+    int32_t precision;
+    int32_t splits; /* split factor over the (l,k) contraction; 0 = choose */
+} t2sp_mttkrp_desc;
+int t2sp_b200_mttkrp(halide_buffer_t *a, halide_buffer_t *b, halide_buffer_t *c, halide_buffer_t *d,
+                     const t2sp_mttkrp_desc *desc);
+
+/* ---- device residency --------------------------------------------------------------
+ * Counterpart of halide_device_malloc / halide_copy_to_device / halide_copy_to_host /
+ * halide_device_free in t2s/src/AOT-OpenCL-Runtime.cpp:74-117,402-441, and of
+ * halide_cuda_wrap_device_ptr (Halide/src/runtime/HalideRuntimeCuda.h:45-60).
+ * A buffer whose `device` field is non-zero and whose device_interface is
+ * t2sp_b200_device_interface() is read from / written to device memory directly:
+ * inputs are copied from `host` only if no device copy exists or host_dirty is set;
+ * outputs stay on the device (device_dirty is set) when the output buffer has a device
+ * allocation, otherwise they are copied to `host` and host_dirty is set.             */
+const struct halide_device_interface_t *t2sp_b200_device_interface(void);
+int t2sp_b200_device_malloc(halide_buffer_t *buf);
+int t2sp_b200_device_free(halide_buffer_t *buf);
+int t2sp_b200_copy_to_device(halide_buffer_t *buf);
+int t2sp_b200_copy_to_host(halide_buffer_t *buf);
+int t2sp_b200_wrap_device_ptr(halide_buffer_t *buf, uint64_t device_ptr);
+int t2sp_b200_detach_device_ptr(halide_buffer_t *buf);
+
+/* ---- execution control -------------------------------------------------------------
+ * Calls are synchronous by default, like the reference's (clFinish per call,
+ * AOT-OpenCL-Runtime.cpp:312-358). */
+int t2sp_b200_set_device(int ordinal);          /* CUDA device for the calling thread (default 0) */
+int t2sp_b200_set_stream(void *cuda_stream);    /* stream for the calling thread; NULL = library's own */
+int t2sp_b200_set_async(int enable);            /* 1: calls on device-resident buffers return after enqueue */
+int t2sp_b200_sync(void);                       /* wait for the thread's stream; reports kernel status */
+void t2sp_b200_release(void);                   /* free cached device allocations and streams */
+uint64_t t2sp_b200_kernel_launches(void);       /* kernels launched by this library since load */
+/* Device time of the last synchronous call's kernels in nanoseconds, as the reference's
+ * runtime records per kernel (AOT-OpenCL-Runtime.cpp:360-396). It is also written to
+ * exec_time.txt in dirname($BITSTREAM) or to $T2SP_B200_EXEC_TIME_FILE when set.      */
+double t2sp_b200_last_kernel_ns(void);
+const char *t2sp_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* T2SP_B200_RUNTIME_H */

@@ -1,0 +1,951 @@
+// The five operator entry points: argument validation in the order the generated host
+// code performs it (null -> bounds query -> type -> dimensions -> extents -> output coverage
+// -> innermost stride -> sizes -> host pointer; t2s/peppers/blas/level3/syrk/release/s10/
+// syrk-interface.cpp:29-928), then lowering to one launch of the contraction kernel.
+// The host serializer/deserializer loops of the reference (syrk-interface.cpp:976-1240,
+// 2143-2317) have no counterpart: TMA strides and the epilogue's address maps read and write
+// the caller's layouts in place.
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <algorithm>
+#include <string>
+
+#include "host_rt.h"
+
+extern "C" {
+int halide_error_bad_type(void*, const char*, uint32_t, uint32_t);
+int halide_error_bad_dimensions(void*, const char*, int32_t, int32_t);
+int halide_error_access_out_of_bounds(void*, const char*, int, int, int, int, int);
+int halide_error_buffer_allocation_too_large(void*, const char*, uint64_t, uint64_t);
+int halide_error_buffer_extents_negative(void*, const char*, int, int);
+int halide_error_buffer_extents_too_large(void*, const char*, int64_t, int64_t);
+int halide_error_constraint_violated(void*, const char*, int, const char*, int);
+int halide_error_buffer_argument_is_null(void*, const char*);
+int halide_error_host_is_null(void*, const char*);
+}
+
+namespace t2sp {
+cudaEvent_t rt_event(int which);
+
+namespace {
+
+constexpr uint32_t type_word(int code, int bits) { return uint32_t(code) | (uint32_t(bits) << 8) | (1u << 16); }
+constexpr uint32_t kF32 = type_word(2, 32), kBF16 = type_word(4, 16), kF16 = type_word(2, 16), kI8 = type_word(0, 8),
+                   kI32 = type_word(0, 32);
+
+uint32_t buf_type_word(const halide_buffer_t* b) {
+    uint32_t w;
+    memcpy(&w, &b->type, 4);
+    return w;
+}
+
+struct Arg {
+    halide_buffer_t* b;
+    const char* name;   // "A"
+    bool is_output;
+    int dims;
+    std::string role() const { return std::string(is_output ? "Output buffer " : "Input buffer ") + name; }
+};
+
+// Fills a bounds-query buffer with a dense shape of the given extents.
+void fill_query(halide_buffer_t* b, uint32_t tword, int dims, const int* ext) {
+    memcpy(&b->type, &tword, 4);
+    b->dimensions = dims;
+    int64_t stride = 1;
+    for (int d = 0; d < dims; ++d) {
+        b->dim[d].min = 0;
+        b->dim[d].extent = ext[d];
+        b->dim[d].stride = static_cast<int32_t>(stride);
+        b->dim[d].flags = 0;
+        stride *= ext[d];
+    }
+}
+
+int check_null(const Arg* args, int n) {
+    // the generated code tests the output first, then the inputs last to first
+    for (int i = n - 1; i >= 0; --i)
+        if (!args[i].b) return halide_error_buffer_argument_is_null(nullptr, args[i].name);
+    return 0;
+}
+
+int check_type_dims(const Arg& a, uint32_t want) {
+    if (buf_type_word(a.b) != want) return halide_error_bad_type(nullptr, a.role().c_str(), buf_type_word(a.b), want);
+    if (a.b->dimensions != a.dims)
+        return halide_error_bad_dimensions(nullptr, a.role().c_str(), a.b->dimensions, a.dims);
+    return 0;
+}
+
+int check_extents_nonneg(const Arg& a) {
+    for (int d = 0; d < a.b->dimensions; ++d)
+        if (a.b->dim[d].extent < 0)
+            return halide_error_buffer_extents_negative(nullptr, a.role().c_str(), d, a.b->dim[d].extent);
+    return 0;
+}
+
+// The buffer must cover [0, need-1] in dimension d.
+int check_covers(const Arg& a, int d, int need) {
+    const int mn = a.b->dim[d].min, mx = mn + a.b->dim[d].extent - 1;
+    if (mn > 0 || mx < need - 1)
+        return halide_error_access_out_of_bounds(nullptr, a.role().c_str(), d, 0, need - 1, mn, mx);
+    return 0;
+}
+
+int check_stride0(const Arg& a) {
+    if (a.b->dim[0].stride != 1) {
+        std::string v = std::string(a.name) + ".stride.0";
+        return halide_error_constraint_violated(nullptr, v.c_str(), a.b->dim[0].stride, "1", 1);
+    }
+    return 0;
+}
+
+int check_sizes(const Arg& a) {
+    const int64_t span = buf_elems_span(a.b);
+    const int64_t bytes = span * ((a.b->type.bits + 7) / 8);
+    // The reference caps a buffer at 2^31-1 bytes because its indices are 32-bit
+    // (syrk-interface.cpp:368-432); here indices are 64-bit and the cap is the 2^31-1 limit
+    // of Halide's int32 extents and strides themselves.
+    int64_t prod = 1;
+    for (int d = 0; d < a.b->dimensions; ++d) {
+        prod *= std::max(a.b->dim[d].extent, 1);
+        if (prod > (int64_t(1) << 40))
+            return halide_error_buffer_extents_too_large(nullptr, a.name, prod, int64_t(1) << 40);
+    }
+    if (bytes > (int64_t(1) << 40))
+        return halide_error_buffer_allocation_too_large(nullptr, a.name, bytes, uint64_t(1) << 40);
+    return 0;
+}
+
+int check_host(const Arg& a) {
+    if (!a.b->host && !buf_on_our_device(a.b)) return halide_error_host_is_null(nullptr, a.role().c_str());
+    return 0;
+}
+
+int constraint(const char* var, int val, const char* want_name, int want) {
+    return halide_error_constraint_violated(nullptr, var, val, want_name, want);
+}
+
+// Offset (elements) from the buffer's first stored element to coordinate 0 in every dimension.
+int64_t origin_offset(const halide_buffer_t* b) {
+    int64_t off = 0;
+    for (int d = 0; d < b->dimensions; ++d) off -= int64_t(b->dim[d].min) * b->dim[d].stride;
+    return off;
+}
+
+bool tma_ok(const void* base, std::initializer_list<int64_t> strides_bytes) {
+    if (reinterpret_cast<uintptr_t>(base) & 15) return false;
+    for (int64_t s : strides_bytes)
+        if (s <= 0 || (s & 15)) return false;
+    return true;
+}
+
+int tma_unsupported(const char* name) {
+    fprintf(stderr,
+            "t2sp_b200: buffer %s cannot be read by TMA in place (base address and every outer stride must be "
+            "16-byte aligned)\n",
+            name);
+    return halide_error_code_constraint_violated;
+}
+
+void add_digit2(Digits& d, int div, int mod, int div2, int mod2, long long stride) {
+    if (d.n >= kMaxDigits) return;
+    d.div[d.n] = div;
+    d.mod[d.n] = mod <= 0 ? 1 : mod;
+    d.div2[d.n] = div2;
+    d.mod2[d.n] = mod2 <= 0 ? 1 : mod2;
+    d.stride[d.n] = stride;
+    d.n++;
+}
+void add_digit(Digits& d, int div, int mod, long long stride) { add_digit2(d, div, mod, 1, 1 << 30, stride); }
+
+int resolve_precision(int p) {
+    if (p == T2SP_PRECISION_DEFAULT) {
+        const char* e = getenv("T2SP_B200_PRECISION");
+        if (e && strcmp(e, "tf32x3") != 0 && strcmp(e, "") != 0)
+            fprintf(stderr, "t2sp_b200: unknown T2SP_B200_PRECISION '%s', using tf32x3\n", e);
+        return T2SP_PRECISION_TF32X3;
+    }
+    return p;
+}
+
+// Cuts the row space (ext[0] fastest) into TMA boxes: whole leading dimensions, then a divisor
+// of the first dimension that does not fit. box[] gets the box extents.
+void plan_rows(RowSpace& rs, int* box) {
+    int remaining = kBlockM;
+    int rows = 1;
+    bool partial = false;
+    for (int d = 0; d < rs.nd; ++d) {
+        int b = 1;
+        if (!partial) {
+            for (int c = std::min(rs.ext[d], remaining); c >= 1; --c)
+                if (rs.ext[d] % c == 0) { b = c; break; }
+            if (b < rs.ext[d]) partial = true;
+            remaining /= b;
+        }
+        box[d] = b;
+        rows *= b;
+    }
+    rs.rows_per_box = rows;
+    rs.boxes_per_tile = std::max(1, kBlockM / rows);
+}
+
+struct Timing {
+    bool on = false;
+};
+
+// Runs one lowered contraction: launch, optional timing, status check.
+int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool sync_after) {
+    ThreadState& ts = tls();
+    cudaStream_t s = rt_stream();
+    p.status = rt_status_word();
+    const int tiles = p.tiles_m * p.tiles_n;
+    const int grid = std::max(1, std::min(tiles, core_sm_count()));
+    if (sync_after) cudaEventRecord(rt_event(0), s);
+    cudaError_t e = core_launch(arith, op, bn, p, grid, s);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "t2sp_b200: %s: kernel launch failed: %s\n", who, cudaGetErrorString(e));
+        return halide_error_code_device_run_failed;
+    }
+    rt_count_launch(1);
+    if (sync_after) cudaEventRecord(rt_event(1), s);
+    (void)ts;
+    return 0;
+}
+
+int finish_call(const char* who, const char* kernel_name, bool sync_after) {
+    if (!sync_after) return 0;
+    int rc = rt_check_status(who);
+    if (rc) return rc;
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, rt_event(0), rt_event(1)) == cudaSuccess) {
+        tls().last_kernel_ns = double(ms) * 1e6;
+        rt_write_exec_time(kernel_name, tls().last_kernel_ns);
+    }
+    if (getenv("T2SP_B200_LOG")) fprintf(stderr, "t2sp_b200: %s: kernels %.1f us\n", who, tls().last_kernel_ns * 1e-3);
+    return 0;
+}
+
+bool all_resident(std::initializer_list<const halide_buffer_t*> bufs) {
+    for (auto* b : bufs)
+        if (!buf_on_our_device(b) || ((b->flags & 1u) && b->host)) return false;
+    return true;
+}
+
+struct Views {
+    DeviceView v[4];
+    int n = 0;
+    ~Views() {
+        for (int i = 0; i < n; ++i) rt_drop_view(&v[i]);
+    }
+};
+
+uint32_t idesc_for(int arith, uint32_t in_type, bool b_mn_major, int bn) {
+    if (arith == AR_F16) return make_instr_desc(1, in_type == kBF16 ? 1 : 0, false, b_mn_major, kBlockM, bn);
+    if (arith == AR_TF32X3) return make_instr_desc(1, 2, false, b_mn_major, kBlockM, bn);
+    return make_instr_desc(2, 1, false, b_mn_major, kBlockM, bn);
+}
+
+CUtensorMapDataType tmap_type(uint32_t tword) {
+    if (tword == kF32) return CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    if (tword == kBF16) return CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    if (tword == kF16) return CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    return CU_TENSOR_MAP_DATA_TYPE_UINT8;
+}
+
+int arith_for(uint32_t tword) {
+    if (tword == kF32) return AR_TF32X3;
+    if (tword == kI8) return AR_I8;
+    return AR_F16;
+}
+
+int block_k_for(int arith) { return arith == AR_F16 ? 64 : (arith == AR_TF32X3 ? 32 : 128); }
+
+}  // namespace
+}  // namespace t2sp
+
+using namespace t2sp;
+
+// ======================================================================================= GEMM
+extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buffer_t* C,
+                              const t2sp_gemm_desc* desc) {
+    int layout = desc ? desc->layout : (C && C->dimensions == 6 ? 1 : 0);
+    Arg args[3] = {{A, "A", false, 2}, {B, "B", false, 2}, {C, "C", true, layout ? 6 : 2}};
+    if (int e = check_null(args, 3)) return e;
+
+    // ---- bounds queries: fill in what can be inferred and return
+    if (buf_is_bounds_query(A) || buf_is_bounds_query(B) || buf_is_bounds_query(C)) {
+        int K = 0, M = 0, N = 0;
+        if (!buf_is_bounds_query(A) && A->dimensions == 2) { K = A->dim[0].extent; M = A->dim[1].extent; }
+        if (!buf_is_bounds_query(B) && B->dimensions == 2) { N = B->dim[0].extent; if (!K) K = B->dim[1].extent; }
+        if (!buf_is_bounds_query(C)) {
+            if (layout == 0 && C->dimensions == 2) { if (!N) N = C->dim[0].extent; if (!M) M = C->dim[1].extent; }
+            if (layout == 1 && C->dimensions == 6) {
+                if (!N) N = C->dim[0].extent * C->dim[2].extent * C->dim[4].extent;
+                if (!M) M = C->dim[1].extent * C->dim[3].extent * C->dim[5].extent;
+            }
+        }
+        const uint32_t in_t = !buf_is_bounds_query(A) ? buf_type_word(A) : (!buf_is_bounds_query(B) ? buf_type_word(B) : kF32);
+        const uint32_t out_t = in_t == kI8 ? kI32 : kF32;
+        if (buf_is_bounds_query(A)) { int e2[2] = {K, M}; fill_query(A, in_t, 2, e2); }
+        if (buf_is_bounds_query(B)) { int e2[2] = {N, K}; fill_query(B, in_t, 2, e2); }
+        if (buf_is_bounds_query(C)) {
+            if (layout == 0) { int e2[2] = {N, M}; fill_query(C, out_t, 2, e2); }
+            else {
+                const int JJJ = desc && desc->JJJ ? desc->JJJ : 1, III = desc && desc->III ? desc->III : 1;
+                const int JJ = desc && desc->JJ ? desc->JJ : 1, II = desc && desc->II ? desc->II : 1;
+                int e6[6] = {JJJ, III, JJ, II, N / (JJJ * JJ), M / (III * II)};
+                fill_query(C, out_t, 6, e6);
+            }
+        }
+        return 0;
+    }
+
+    // ---- types and dimensionality
+    const uint32_t in_t = buf_type_word(A);
+    if (in_t != kF32 && in_t != kBF16 && in_t != kF16 && in_t != kI8)
+        return halide_error_bad_type(nullptr, args[0].role().c_str(), in_t, kF32);
+    if (int e = check_type_dims(args[0], in_t)) return e;
+    if (int e = check_type_dims(args[1], in_t)) return e;
+    if (int e = check_type_dims(args[2], in_t == kI8 ? kI32 : kF32)) return e;
+    for (auto& a : args)
+        if (int e = check_extents_nonneg(a)) return e;
+
+    const int K = A->dim[0].extent, M = A->dim[1].extent, N = B->dim[0].extent;
+    if (B->dim[1].extent != K) return constraint("B.extent.1", B->dim[1].extent, "A.extent.0", K);
+
+    // ---- output coverage
+    int JJJ = 1, III = 1, JJ = 1, II = 1;
+    if (layout == 0) {
+        if (int e = check_covers(args[2], 0, N)) return e;
+        if (int e = check_covers(args[2], 1, M)) return e;
+    } else {
+        JJJ = desc && desc->JJJ ? desc->JJJ : C->dim[0].extent;
+        III = desc && desc->III ? desc->III : C->dim[1].extent;
+        JJ = desc && desc->JJ ? desc->JJ : C->dim[2].extent;
+        II = desc && desc->II ? desc->II : C->dim[3].extent;
+        if (JJJ <= 0 || III <= 0 || JJ <= 0 || II <= 0) return constraint("C.tile.extent", 0, "positive", 1);
+        if (N % (JJJ * JJ)) return constraint("B.extent.0", N, "multiple of JJJ*JJ", JJJ * JJ);
+        if (M % (III * II)) return constraint("A.extent.1", M, "multiple of III*II", III * II);
+        const int need[6] = {JJJ, III, JJ, II, N / (JJJ * JJ), M / (III * II)};
+        for (int d = 0; d < 6; ++d)
+            if (int e = check_covers(args[2], d, need[d])) return e;
+    }
+    for (auto& a : args)
+        if (int e = check_stride0(a)) return e;
+    for (auto& a : args)
+        if (int e = check_sizes(a)) return e;
+    for (auto& a : args)
+        if (int e = check_host(a)) return e;
+    if (M == 0 || N == 0) return 0;
+
+    // ---- device
+    if (int e = rt_ensure_device()) return e;
+    const bool resident = all_resident({A, B, C});
+    const bool sync_after = !(resident && tls().async);
+    Views vw;
+    if (int e = rt_input_view(A, "A", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = rt_input_view(B, "B", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = rt_output_view(C, "C", &vw.v[vw.n])) return e;
+    vw.n++;
+    const int es = (A->type.bits + 7) / 8;
+    char* pa = static_cast<char*>(vw.v[0].ptr) + origin_offset(A) * es;
+    char* pb = static_cast<char*>(vw.v[1].ptr) + origin_offset(B) * es;
+    uint32_t* pc = static_cast<uint32_t*>(vw.v[2].ptr) + origin_offset(C);
+
+    if (K == 0) {
+        // empty contraction: the result is all zeros
+        cudaMemsetAsync(vw.v[2].ptr, 0, vw.v[2].bytes, rt_stream());
+    } else {
+        const int arith = arith_for(in_t);
+        if (arith == AR_TF32X3) resolve_precision(desc ? desc->precision : 0);
+        const int bk = block_k_for(arith);
+        const int bn = core_pick_bn(arith, OP_GEMM, N);
+        const int64_t lda = int64_t(A->dim[1].stride) * es, ldb = int64_t(B->dim[1].stride) * es;
+        if (!tma_ok(pa, {lda})) return tma_unsupported("A");
+        if (!tma_ok(pb, {ldb})) return tma_unsupported("B");
+        CoreParams p;
+        memset(&p, 0, sizeof(p));
+        {
+            uint64_t dims[2] = {uint64_t(K), uint64_t(M)}, str[2] = {uint64_t(es), uint64_t(lda)};
+            uint32_t box[2] = {uint32_t(bk), uint32_t(kBlockM)};
+            if (!rt_encode_tmap(&p.mapA[0], tmap_type(in_t), 2, pa, dims, str, box)) return tma_unsupported("A");
+        }
+        {
+            uint64_t dims[2] = {uint64_t(N), uint64_t(K)}, str[2] = {uint64_t(es), uint64_t(ldb)};
+            uint32_t box[2] = {uint32_t(128 / es), uint32_t(bk)};
+            if (!rt_encode_tmap(&p.mapB, tmap_type(in_t), 2, pb, dims, str, box)) return tma_unsupported("B");
+        }
+        p.M = M; p.N = N; p.tile_rows = kBlockM;
+        p.num_kb = (K + bk - 1) / bk; p.total_kb = p.num_kb;
+        p.tiles_m = (M + kBlockM - 1) / kBlockM; p.tiles_n = (N + bn - 1) / bn;
+        p.idesc = idesc_for(arith, in_t, true, bn);
+        p.out = pc;
+        if (layout == 0) {
+            p.epi = EPI_ROWMAJOR;
+            p.ldo = C->dim[1].stride;
+        } else {
+            p.epi = EPI_SCATTER;
+            add_digit(p.dm, 1, III, C->dim[1].stride);
+            add_digit(p.dm, III, II, C->dim[3].stride);
+            add_digit(p.dm, III * II, 1 << 30, C->dim[5].stride);
+            add_digit(p.dn, 1, JJJ, C->dim[0].stride);
+            add_digit(p.dn, JJJ, JJ, C->dim[2].stride);
+            add_digit(p.dn, JJJ * JJ, 1 << 30, C->dim[4].stride);
+        }
+        if (int e = run_core("gemm", arith, OP_GEMM, bn, p, sync_after)) return e;
+    }
+    if (int e = rt_finish_output(C, "C", &vw.v[2])) return e;
+    return finish_call("gemm", "kernel_Out", sync_after);
+}
+
+// ======================================================================================= TTM
+extern "C" int t2sp_b200_ttm(halide_buffer_t* a, halide_buffer_t* b, halide_buffer_t* c, const t2sp_ttm_desc* desc) {
+    int layout = desc ? desc->layout : (c && c->dimensions == 9 ? 1 : 0);
+    Arg args[3] = {{a, "a", false, 3}, {b, "b", false, 2}, {c, "c", true, layout ? 9 : 3}};
+    if (int e = check_null(args, 3)) return e;
+    if (buf_is_bounds_query(a) || buf_is_bounds_query(b) || buf_is_bounds_query(c)) {
+        int L = 0, I = 0, J = 0, Kn = 0;
+        if (!buf_is_bounds_query(a) && a->dimensions == 3) { L = a->dim[0].extent; I = a->dim[1].extent; J = a->dim[2].extent; }
+        if (!buf_is_bounds_query(b) && b->dimensions == 2) { if (!L) L = b->dim[0].extent; Kn = b->dim[1].extent; }
+        if (!buf_is_bounds_query(c) && layout == 0 && c->dimensions == 3) {
+            if (!I) I = c->dim[0].extent; if (!J) J = c->dim[1].extent; if (!Kn) Kn = c->dim[2].extent;
+        }
+        if (buf_is_bounds_query(a)) { int e3[3] = {L, I, J}; fill_query(a, kF32, 3, e3); }
+        if (buf_is_bounds_query(b)) { int e2[2] = {L, Kn}; fill_query(b, kF32, 2, e2); }
+        if (buf_is_bounds_query(c) && layout == 0) { int e3[3] = {I, J, Kn}; fill_query(c, kF32, 3, e3); }
+        return 0;
+    }
+    for (auto& x : args)
+        if (int e = check_type_dims(x, kF32)) return e;
+    for (auto& x : args)
+        if (int e = check_extents_nonneg(x)) return e;
+    const int L = a->dim[0].extent, I = a->dim[1].extent, J = a->dim[2].extent, Kn = b->dim[1].extent;
+    if (b->dim[0].extent != L) return constraint("b.extent.0", b->dim[0].extent, "a.extent.0", L);
+    int III = 1, II = 1, JJJ = 1, JJ = 1, KKK = 1, KK = 1;
+    if (layout == 0) {
+        if (int e = check_covers(args[2], 0, I)) return e;
+        if (int e = check_covers(args[2], 1, J)) return e;
+        if (int e = check_covers(args[2], 2, Kn)) return e;
+    } else {
+        JJ = c->dim[0].extent; KK = c->dim[1].extent; II = c->dim[2].extent;
+        KKK = c->dim[3].extent; JJJ = c->dim[4].extent; III = c->dim[5].extent;
+        if (JJ <= 0 || KK <= 0 || II <= 0 || KKK <= 0 || JJJ <= 0 || III <= 0) return constraint("c.tile.extent", 0, "positive", 1);
+        if (I % (III * II)) return constraint("a.extent.1", I, "multiple of III*II", III * II);
+        if (J % (JJJ * JJ)) return constraint("a.extent.2", J, "multiple of JJJ*JJ", JJJ * JJ);
+        if (Kn % (KKK * KK)) return constraint("b.extent.1", Kn, "multiple of KKK*KK", KKK * KK);
+        if (int e = check_covers(args[2], 6, Kn / (KKK * KK))) return e;
+        if (int e = check_covers(args[2], 7, J / (JJJ * JJ))) return e;
+        if (int e = check_covers(args[2], 8, I / (III * II))) return e;
+    }
+    for (auto& x : args)
+        if (int e = check_stride0(x)) return e;
+    for (auto& x : args)
+        if (int e = check_sizes(x)) return e;
+    for (auto& x : args)
+        if (int e = check_host(x)) return e;
+    const int64_t Mrows = int64_t(I) * J;
+    if (Mrows == 0 || Kn == 0) return 0;
+    if (Mrows >= (int64_t(1) << 31)) return halide_error_buffer_extents_too_large(nullptr, "a", Mrows, (int64_t(1) << 31) - 1);
+    if (J > 1 && int64_t(a->dim[2].stride) != int64_t(I) * a->dim[1].stride) {
+        fprintf(stderr, "t2sp_b200: ttm: a must be dense across (i, j): a.stride.2 == a.extent.1 * a.stride.1\n");
+        return constraint("a.stride.2", a->dim[2].stride, "a.extent.1*a.stride.1", I * a->dim[1].stride);
+    }
+
+    if (int e = rt_ensure_device()) return e;
+    const bool resident = all_resident({a, b, c});
+    const bool sync_after = !(resident && tls().async);
+    Views vw;
+    if (int e = rt_input_view(a, "a", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = rt_input_view(b, "b", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = rt_output_view(c, "c", &vw.v[vw.n])) return e;
+    vw.n++;
+    char* pa = static_cast<char*>(vw.v[0].ptr) + origin_offset(a) * 4;
+    char* pb = static_cast<char*>(vw.v[1].ptr) + origin_offset(b) * 4;
+    uint32_t* pc = static_cast<uint32_t*>(vw.v[2].ptr) + origin_offset(c);
+    if (L == 0) {
+        cudaMemsetAsync(vw.v[2].ptr, 0, vw.v[2].bytes, rt_stream());
+    } else {
+        resolve_precision(desc ? desc->precision : 0);
+        const int M = static_cast<int>(Mrows), N = Kn;
+        const int bn = core_pick_bn(AR_TF32X3, OP_TTM, N);
+        const int64_t lda = int64_t(a->dim[1].stride) * 4, ldb = int64_t(b->dim[1].stride) * 4;
+        if (!tma_ok(pa, {lda})) return tma_unsupported("a");
+        if (!tma_ok(pb, {ldb})) return tma_unsupported("b");
+        CoreParams p;
+        memset(&p, 0, sizeof(p));
+        {
+            uint64_t dims[2] = {uint64_t(L), uint64_t(M)}, str[2] = {4, uint64_t(lda)};
+            uint32_t box[2] = {32, uint32_t(kBlockM)};
+            if (!rt_encode_tmap(&p.mapA[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, pa, dims, str, box)) return tma_unsupported("a");
+        }
+        {
+            uint64_t dims[2] = {uint64_t(L), uint64_t(N)}, str[2] = {4, uint64_t(ldb)};
+            uint32_t box[2] = {32, uint32_t(bn)};
+            if (!rt_encode_tmap(&p.mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, pb, dims, str, box)) return tma_unsupported("b");
+        }
+        p.M = M; p.N = N; p.tile_rows = kBlockM;
+        p.num_kb = (L + 31) / 32; p.total_kb = p.num_kb;
+        p.tiles_m = (M + kBlockM - 1) / kBlockM; p.tiles_n = (N + bn - 1) / bn;
+        p.idesc = idesc_for(AR_TF32X3, kF32, false, bn);
+        p.out = pc;
+        if (layout == 0) {
+            if (c->dim[0].stride == 1 && (J == 1 || c->dim[1].stride == I)) {
+                p.epi = EPI_COLMAJOR;  // rows (i + I*j) are contiguous in the output
+                p.ldo = c->dim[2].stride;
+            } else {
+                p.epi = EPI_SCATTER;
+                add_digit(p.dm, 1, I, c->dim[0].stride);
+                add_digit(p.dm, I, 1 << 30, c->dim[1].stride);
+                add_digit(p.dn, 1, 1 << 30, c->dim[2].stride);
+            }
+        } else {
+            p.epi = EPI_SCATTER;
+            add_digit(p.dm, 1, III, c->dim[5].stride);
+            add_digit(p.dm, III, II, c->dim[2].stride);
+            add_digit(p.dm, III * II, I / (III * II), c->dim[8].stride);
+            add_digit(p.dm, I, JJJ, c->dim[4].stride);
+            add_digit(p.dm, I * JJJ, JJ, c->dim[0].stride);
+            add_digit(p.dm, I * JJJ * JJ, 1 << 30, c->dim[7].stride);
+            add_digit(p.dn, 1, KKK, c->dim[3].stride);
+            add_digit(p.dn, KKK, KK, c->dim[1].stride);
+            add_digit(p.dn, KKK * KK, 1 << 30, c->dim[6].stride);
+        }
+        if (int e = run_core("ttm", AR_TF32X3, OP_TTM, bn, p, sync_after)) return e;
+    }
+    if (int e = rt_finish_output(c, "c", &vw.v[2])) return e;
+    return finish_call("ttm", "kernel_unloader", sync_after);
+}
+
+// ======================================================================================= CONV
+extern "C" int t2sp_b200_conv(halide_buffer_t* I, halide_buffer_t* K, halide_buffer_t* O,
+                              const t2sp_conv_desc* desc) {
+    if (!desc) {
+        fprintf(stderr, "t2sp_b200: conv needs a descriptor (CI, CO, KY, KX, OY, OX cannot be read off the flattened buffers)\n");
+        return halide_error_code_generic_error;
+    }
+    const int layout = desc->layout;
+    Arg args[3] = {{I, "I", false, 2}, {K, "K", false, 2}, {O, "O", true, layout ? 10 : 2}};
+    if (int e = check_null(args, 3)) return e;
+    const int CI = desc->CI, CO = desc->CO, KY = desc->KY, KX = desc->KX, OY = desc->OY, OX = desc->OX;
+    if (CI <= 0 || CO <= 0 || KY <= 0 || KX <= 0 || OY <= 0 || OX <= 0) return constraint("conv.desc", 0, "positive", 1);
+    const int IY = OY + KY - 1, IX = OX + KX - 1;
+    if (buf_is_bounds_query(I) || buf_is_bounds_query(K) || buf_is_bounds_query(O)) {
+        int N = 0;
+        if (!buf_is_bounds_query(I) && I->dimensions == 2) N = I->dim[0].extent / CI;
+        else if (!buf_is_bounds_query(O) && layout == 0 && O->dimensions == 2) N = O->dim[0].extent / CO;
+        else if (!buf_is_bounds_query(O) && layout == 1 && O->dimensions == 10) N = O->dim[9].extent;
+        if (buf_is_bounds_query(I)) { int e2[2] = {CI * N, IY * IX}; fill_query(I, kF32, 2, e2); }
+        if (buf_is_bounds_query(K)) { int e2[2] = {CO * KX, CI * KY}; fill_query(K, kF32, 2, e2); }
+        if (buf_is_bounds_query(O)) {
+            if (layout == 0) { int e2[2] = {CO * N, OY * OX}; fill_query(O, kF32, 2, e2); }
+            else {
+                const int den = std::max(1, desc->COOO * desc->COO);
+                int e10[10] = {desc->COOO, desc->YYY, desc->XXX, desc->COO, desc->YY, desc->XX, desc->Y, desc->X, CO / den, N};
+                fill_query(O, kF32, 10, e10);
+            }
+        }
+        return 0;
+    }
+    for (auto& x : args)
+        if (int e = check_type_dims(x, kF32)) return e;
+    for (auto& x : args)
+        if (int e = check_extents_nonneg(x)) return e;
+    if (I->dim[0].extent % CI) return constraint("I.extent.0", I->dim[0].extent, "multiple of CI", CI);
+    const int N = I->dim[0].extent / CI;
+    if (I->dim[1].extent != IY * IX) return constraint("I.extent.1", I->dim[1].extent, "IY*IX", IY * IX);
+    if (K->dim[0].extent != CO * KX) return constraint("K.extent.0", K->dim[0].extent, "CO*KX", CO * KX);
+    if (K->dim[1].extent != CI * KY) return constraint("K.extent.1", K->dim[1].extent, "CI*KY", CI * KY);
+    if (layout == 0) {
+        if (int e = check_covers(args[2], 0, CO * N)) return e;
+        if (int e = check_covers(args[2], 1, OY * OX)) return e;
+    } else {
+        if (desc->COOO <= 0 || desc->COO <= 0 || desc->YYY <= 0 || desc->YY <= 0 || desc->Y <= 0 || desc->XXX <= 0 ||
+            desc->XX <= 0 || desc->X <= 0)
+            return constraint("conv.desc.tile", 0, "positive", 1);
+        if (desc->YYY * desc->YY * desc->Y != OY) return constraint("YYY*YY*Y", desc->YYY * desc->YY * desc->Y, "OY", OY);
+        if (desc->XXX * desc->XX * desc->X != OX) return constraint("XXX*XX*X", desc->XXX * desc->XX * desc->X, "OX", OX);
+        if (CO % (desc->COOO * desc->COO)) return constraint("CO", CO, "multiple of COOO*COO", desc->COOO * desc->COO);
+        const int need[10] = {desc->COOO, desc->YYY, desc->XXX, desc->COO, desc->YY, desc->XX, desc->Y, desc->X,
+                              CO / (desc->COOO * desc->COO), N};
+        for (int d = 0; d < 10; ++d)
+            if (int e = check_covers(args[2], d, need[d])) return e;
+    }
+    for (auto& x : args)
+        if (int e = check_stride0(x)) return e;
+    for (auto& x : args)
+        if (int e = check_sizes(x)) return e;
+    for (auto& x : args)
+        if (int e = check_host(x)) return e;
+    if (N == 0) return 0;
+    const int64_t Mrows = int64_t(N) * OY * OX;
+    if (Mrows >= (int64_t(1) << 31)) return halide_error_buffer_extents_too_large(nullptr, "O", Mrows, (int64_t(1) << 31) - 1);
+
+    if (int e = rt_ensure_device()) return e;
+    const bool resident = all_resident({I, K, O});
+    const bool sync_after = !(resident && tls().async);
+    Views vw;
+    if (int e = rt_input_view(I, "I", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = rt_input_view(K, "K", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = rt_output_view(O, "O", &vw.v[vw.n])) return e;
+    vw.n++;
+    char* pi = static_cast<char*>(vw.v[0].ptr) + origin_offset(I) * 4;
+    char* pk = static_cast<char*>(vw.v[1].ptr) + origin_offset(K) * 4;
+    uint32_t* po = static_cast<uint32_t*>(vw.v[2].ptr) + origin_offset(O);
+    resolve_precision(desc->precision);
+
+    const int bn = core_pick_bn(AR_TF32X3, OP_CONV, CO);
+    const int64_t s1 = int64_t(I->dim[1].stride) * 4, t1 = int64_t(K->dim[1].stride) * 4;
+    if (!tma_ok(pi, {int64_t(CI) * 4, s1})) return tma_unsupported("I");
+    if (!tma_ok(pk, {int64_t(CO) * 4, t1})) return tma_unsupported("K");
+    CoreParams p;
+    memset(&p, 0, sizeof(p));
+    p.rows.nd = 3;
+    p.rows.ext[0] = N; p.rows.ext[1] = OY; p.rows.ext[2] = OX; p.rows.ext[3] = 1;
+    int rbox[4] = {1, 1, 1, 1};
+    plan_rows(p.rows, rbox);
+    {
+        // input as (ci, n, iy, ix)
+        uint64_t dims[4] = {uint64_t(CI), uint64_t(N), uint64_t(IY), uint64_t(IX)};
+        uint64_t str[4] = {4, uint64_t(CI) * 4, uint64_t(s1), uint64_t(IY) * uint64_t(s1)};
+        uint32_t box[4] = {32, uint32_t(rbox[0]), uint32_t(rbox[1]), uint32_t(rbox[2])};
+        if (!rt_encode_tmap(&p.mapA[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, pi, dims, str, box)) return tma_unsupported("I");
+    }
+    {
+        // weights as (co, kx, ci, ky)
+        uint64_t dims[4] = {uint64_t(CO), uint64_t(KX), uint64_t(CI), uint64_t(KY)};
+        uint64_t str[4] = {4, uint64_t(CO) * 4, uint64_t(t1), uint64_t(CI) * uint64_t(t1)};
+        uint32_t box[4] = {32, 1, 32, 1};
+        if (!rt_encode_tmap(&p.mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, pk, dims, str, box)) return tma_unsupported("K");
+    }
+    p.M = static_cast<int>(Mrows); p.N = CO;
+    p.tile_rows = p.rows.rows_per_box * p.rows.boxes_per_tile;
+    p.cblks = (CI + 31) / 32; p.KY = KY; p.KX = KX; p.stride = 1;
+    p.num_kb = KY * KX * p.cblks; p.total_kb = p.num_kb;
+    p.tiles_m = (p.M + p.tile_rows - 1) / p.tile_rows; p.tiles_n = (CO + bn - 1) / bn;
+    p.idesc = idesc_for(AR_TF32X3, kF32, true, bn);
+    p.out = po;
+    if (layout == 0) {
+        const int64_t so = O->dim[1].stride;
+        if (so == int64_t(CO) * N) {
+            p.epi = EPI_ROWMAJOR;
+            p.ldo = CO;
+        } else {
+            p.epi = EPI_SCATTER;
+            add_digit(p.dm, 1, N, CO);
+            add_digit(p.dm, N, 1 << 30, so);
+            add_digit(p.dn, 1, 1 << 30, 1);
+        }
+    } else {
+        p.epi = EPI_SCATTER;
+        const halide_dimension_t* d = O->dim;
+        add_digit(p.dm, 1, N, d[9].stride);
+        add_digit(p.dm, N, desc->YYY, d[1].stride);
+        add_digit(p.dm, N * desc->YYY, desc->YY, d[4].stride);
+        add_digit(p.dm, N * desc->YYY * desc->YY, desc->Y, d[6].stride);
+        add_digit(p.dm, N * OY, desc->XXX, d[2].stride);
+        add_digit(p.dm, N * OY * desc->XXX, desc->XX, d[5].stride);
+        add_digit(p.dm, N * OY * desc->XXX * desc->XX, 1 << 30, d[7].stride);
+        add_digit(p.dn, 1, desc->COOO, d[0].stride);
+        add_digit(p.dn, desc->COOO, desc->COO, d[3].stride);
+        add_digit(p.dn, desc->COOO * desc->COO, 1 << 30, d[8].stride);
+    }
+    if (int e = run_core("conv", AR_TF32X3, OP_CONV, bn, p, sync_after)) return e;
+    if (int e = rt_finish_output(O, "O", &vw.v[2])) return e;
+    return finish_call("conv", "kernel_unloader", sync_after);
+}
+
+// ======================================================================================= CAPSULE
+extern "C" int t2sp_b200_capsule(halide_buffer_t* P, halide_buffer_t* W, halide_buffer_t* V,
+                                 const t2sp_capsule_desc* desc) {
+    if (!desc) {
+        fprintf(stderr, "t2sp_b200: capsule needs a descriptor (the flattened buffers do not carry CI, CII, CO, ...)\n");
+        return halide_error_code_generic_error;
+    }
+    const int layout = desc->layout;
+    Arg args[3] = {{P, "P", false, 2}, {W, "W", false, 2}, {V, "V", true, layout ? 10 : 2}};
+    if (int e = check_null(args, 3)) return e;
+    const int CI = desc->CI, CII = desc->CII, CO = desc->CO, KY = desc->KY, KX = desc->KX, OY = desc->OY, OX = desc->OX;
+    const int MY = desc->MY, MX = desc->MX, MK = desc->MK, NN = desc->NN, s = desc->stride;
+    if (CI <= 0 || CII <= 0 || CO <= 0 || KY <= 0 || KX <= 0 || OY <= 0 || OX <= 0 || MY <= 0 || MX <= 0 || MK <= 0 || NN <= 0)
+        return constraint("capsule.desc", 0, "positive", 1);
+    if (s != 1 && s != 2) return constraint("capsule.desc.stride", s, "1 or 2", 2);
+    if (CI % CII) return constraint("CI", CI, "multiple of CII", CII);
+    const int IY = s * OY + KY - s, IX = s * OX + KX - s;
+    const int Q = MX * NN, NW = CO * MY, CP = CI * MK;
+    if (buf_is_bounds_query(P) || buf_is_bounds_query(W) || buf_is_bounds_query(V)) {
+        int N = 0;
+        if (!buf_is_bounds_query(P) && P->dimensions == 2) N = P->dim[1].extent / (IY * IX);
+        else if (!buf_is_bounds_query(V) && layout == 0 && V->dimensions == 2) N = V->dim[1].extent / (OY * OX);
+        else if (!buf_is_bounds_query(V) && layout == 1 && V->dimensions == 10) N = V->dim[9].extent;
+        if (buf_is_bounds_query(P)) { int e2[2] = {CP * Q, IY * IX * N}; fill_query(P, kF32, 2, e2); }
+        if (buf_is_bounds_query(W)) { int e2[2] = {NW, CI * KY * KX * MK}; fill_query(W, kF32, 2, e2); }
+        if (buf_is_bounds_query(V)) {
+            if (layout == 0) { int e2[2] = {NW * Q, OY * OX * N}; fill_query(V, kF32, 2, e2); }
+            else {
+                const int den = std::max(1, desc->COOO * desc->COO);
+                int e10[10] = {desc->COOO, desc->YYY_XXX, desc->YY_XX, desc->Y_X, MY, MX, desc->COO, NN, CO / den, N};
+                fill_query(V, kF32, 10, e10);
+            }
+        }
+        return 0;
+    }
+    for (auto& x : args)
+        if (int e = check_type_dims(x, kF32)) return e;
+    for (auto& x : args)
+        if (int e = check_extents_nonneg(x)) return e;
+    if (P->dim[0].extent != CP * Q) return constraint("P.extent.0", P->dim[0].extent, "CI*MK*MX*NN", CP * Q);
+    if (P->dim[1].extent % (IY * IX)) return constraint("P.extent.1", P->dim[1].extent, "multiple of IY*IX", IY * IX);
+    const int N = P->dim[1].extent / (IY * IX);
+    if (W->dim[0].extent != NW) return constraint("W.extent.0", W->dim[0].extent, "CO*MY", NW);
+    if (W->dim[1].extent != CI * KY * KX * MK) return constraint("W.extent.1", W->dim[1].extent, "CI*KY*KX*MK", CI * KY * KX * MK);
+    int slots = OY * OX;
+    if (layout == 0) {
+        if (int e = check_covers(args[2], 0, NW * Q)) return e;
+        if (int e = check_covers(args[2], 1, OY * OX * N)) return e;
+    } else {
+        if (desc->COOO <= 0 || desc->COO <= 0 || desc->YYY_XXX <= 0 || desc->YY_XX <= 0 || desc->Y_X <= 0)
+            return constraint("capsule.desc.tile", 0, "positive", 1);
+        slots = desc->YYY_XXX * desc->YY_XX * desc->Y_X;
+        if (slots < OY * OX) return constraint("YYY_XXX*YY_XX*Y_X", slots, "at least OY*OX", OY * OX);
+        if (CO % (desc->COOO * desc->COO)) return constraint("CO", CO, "multiple of COOO*COO", desc->COOO * desc->COO);
+        const int need[10] = {desc->COOO, desc->YYY_XXX, desc->YY_XX, desc->Y_X, MY, MX, desc->COO, NN,
+                              CO / (desc->COOO * desc->COO), N};
+        for (int d = 0; d < 10; ++d)
+            if (int e = check_covers(args[2], d, need[d])) return e;
+    }
+    for (auto& x : args)
+        if (int e = check_stride0(x)) return e;
+    for (auto& x : args)
+        if (int e = check_sizes(x)) return e;
+    for (auto& x : args)
+        if (int e = check_host(x)) return e;
+    if (N == 0) return 0;
+    const int64_t Mrows = int64_t(Q) * OY * OX * N;
+    if (Mrows >= (int64_t(1) << 31)) return halide_error_buffer_extents_too_large(nullptr, "V", Mrows, (int64_t(1) << 31) - 1);
+    // weight box walk: 32 consecutive c' = ci + CI*mk values per k-block
+    int bcii, bcio, bmk;
+    if (CII % 32 == 0) { bcii = 32; bcio = 1; bmk = 1; }
+    else if (CI % 32 == 0 && 32 % CII == 0) { bcii = CII; bcio = 32 / CII; bmk = 1; }
+    else if (32 % CI == 0) { bcii = CII; bcio = CI / CII; bmk = std::min(MK, 32 / CI); }
+    else {
+        fprintf(stderr, "t2sp_b200: capsule: CI=%d CII=%d is not supported (need CII%%32==0, or CI%%32==0 with 32%%CII==0, or 32%%CI==0)\n", CI, CII);
+        return halide_error_code_constraint_violated;
+    }
+
+    if (int e = rt_ensure_device()) return e;
+    const bool resident = all_resident({P, W, V});
+    const bool sync_after = !(resident && tls().async);
+    Views vw;
+    if (int e = rt_input_view(P, "P", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = rt_input_view(W, "W", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = rt_output_view(V, "V", &vw.v[vw.n])) return e;
+    vw.n++;
+    char* pp = static_cast<char*>(vw.v[0].ptr) + origin_offset(P) * 4;
+    char* pw = static_cast<char*>(vw.v[1].ptr) + origin_offset(W) * 4;
+    uint32_t* pv = static_cast<uint32_t*>(vw.v[2].ptr) + origin_offset(V);
+    resolve_precision(desc->precision);
+
+    const int bn = core_pick_bn(AR_TF32X3, OP_CAPSULE, NW);
+    const int64_t s1 = int64_t(P->dim[1].stride) * 4, t1 = int64_t(W->dim[1].stride) * 4;
+    if (!tma_ok(pp, {int64_t(CP) * 4, s1})) return tma_unsupported("P");
+    if (!tma_ok(pw, {t1})) return tma_unsupported("W");
+    CoreParams p;
+    memset(&p, 0, sizeof(p));
+    p.rows.nd = 4;
+    p.rows.ext[0] = Q; p.rows.ext[1] = OY; p.rows.ext[2] = OX; p.rows.ext[3] = N;
+    int rbox[4] = {1, 1, 1, 1};
+    plan_rows(p.rows, rbox);
+    for (int py = 0; py < s; ++py)
+        for (int px = 0; px < s; ++px) {
+            // input of one stride parity as (c', q, iy', ix', n), iy = s*iy' + py, ix = s*ix' + px
+            const int ey = (IY - py + s - 1) / s, ex = (IX - px + s - 1) / s;
+            uint64_t dims[5] = {uint64_t(CP), uint64_t(Q), uint64_t(ey), uint64_t(ex), uint64_t(N)};
+            uint64_t str[5] = {4, uint64_t(CP) * 4, uint64_t(s) * uint64_t(s1), uint64_t(s) * uint64_t(IY) * uint64_t(s1),
+                               uint64_t(IY) * uint64_t(IX) * uint64_t(s1)};
+            uint32_t box[5] = {32, uint32_t(rbox[0]), uint32_t(rbox[1]), uint32_t(rbox[2]), uint32_t(rbox[3])};
+            char* base = pp + (int64_t(py) + int64_t(px) * IY) * s1;
+            if (!rt_encode_tmap(&p.mapA[py + 2 * px], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, base, dims, str, box))
+                return tma_unsupported("P");
+        }
+    {
+        // weights as (n = co + CO*my, cii, tap = ky + KY*kx, ci_outer, mk)
+        uint64_t dims[5] = {uint64_t(NW), uint64_t(CII), uint64_t(KY) * uint64_t(KX), uint64_t(CI / CII), uint64_t(MK)};
+        uint64_t str[5] = {4, uint64_t(t1), uint64_t(CII) * uint64_t(t1), uint64_t(CII) * KY * KX * uint64_t(t1),
+                           uint64_t(CI) * KY * KX * uint64_t(t1)};
+        uint32_t box[5] = {32, uint32_t(bcii), 1, uint32_t(bcio), uint32_t(bmk)};
+        if (!rt_encode_tmap(&p.mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, pw, dims, str, box)) return tma_unsupported("W");
+    }
+    p.M = static_cast<int>(Mrows); p.N = NW;
+    p.tile_rows = p.rows.rows_per_box * p.rows.boxes_per_tile;
+    p.cblks = (CP + 31) / 32; p.KY = KY; p.KX = KX; p.stride = s; p.CI = CI; p.CII = CII;
+    p.num_kb = KY * KX * p.cblks; p.total_kb = p.num_kb;
+    p.tiles_m = (p.M + p.tile_rows - 1) / p.tile_rows; p.tiles_n = (NW + bn - 1) / bn;
+    p.idesc = idesc_for(AR_TF32X3, kF32, true, bn);
+    p.out = pv;
+    if (layout == 0) {
+        const int64_t so = V->dim[1].stride;
+        if (so == int64_t(NW) * Q) {
+            p.epi = EPI_ROWMAJOR;
+            p.ldo = NW;
+        } else {
+            p.epi = EPI_SCATTER;
+            add_digit(p.dm, 1, Q, NW);
+            add_digit(p.dm, Q, 1 << 30, so);
+            add_digit(p.dn, 1, 1 << 30, 1);
+        }
+    } else {
+        if (slots > OY * OX) cudaMemsetAsync(vw.v[2].ptr, 0, vw.v[2].bytes, rt_stream());
+        p.epi = EPI_SCATTER;
+        const halide_dimension_t* d = V->dim;
+        add_digit(p.dm, 1, MX, d[5].stride);
+        add_digit(p.dm, MX, NN, d[7].stride);
+        // pixel number pix = (m / Q) % (OY*OX), then its three tile digits
+        const int PX = OY * OX;
+        add_digit2(p.dm, Q, PX, 1, desc->YYY_XXX, d[1].stride);
+        add_digit2(p.dm, Q, PX, desc->YYY_XXX, desc->YY_XX, d[2].stride);
+        add_digit2(p.dm, Q, PX, desc->YYY_XXX * desc->YY_XX, 1 << 30, d[3].stride);
+        add_digit(p.dm, Q * PX, 1 << 30, d[9].stride);
+        add_digit(p.dn, 1, desc->COOO, d[0].stride);
+        add_digit(p.dn, desc->COOO, desc->COO, d[6].stride);
+        add_digit(p.dn, desc->COOO * desc->COO, CO / (desc->COOO * desc->COO), d[8].stride);
+        add_digit(p.dn, CO, 1 << 30, d[4].stride);
+    }
+    if (int e = run_core("capsule", AR_TF32X3, OP_CAPSULE, bn, p, sync_after)) return e;
+    if (int e = rt_finish_output(V, "V", &vw.v[2])) return e;
+    return finish_call("capsule", "kernel_unloader", sync_after);
+}
+
+// ======================================================================================= MTTKRP
+namespace t2sp {
+// Lowers and launches the split-K MTTKRP into caller-provided partial-sum scratch
+// (splits * I * R floats) followed by the ordered reduction. Shared by the allocating entry.
+int mttkrp_launch(const char* who, float* pa, int64_t lda1, int64_t lda2, const float* pb, int64_t ldb,
+                  const float* pc, int64_t ldc, float* pd, int64_t ldd, int L, int I, int Kd, int R, int splits,
+                  int num_kb, float* scratch, bool sync_after) {
+    const int bn = core_pick_bn(AR_TF32X3, OP_MTTKRP, R);
+    if (bn == 0) return constraint("d.extent.1", R, "at most", 128);
+    if (!tma_ok(pa, {lda1 * 4, lda2 * 4})) return tma_unsupported("a");
+    CoreParams p;
+    memset(&p, 0, sizeof(p));
+    {
+        uint64_t dims[3] = {uint64_t(L), uint64_t(I), uint64_t(Kd)};
+        uint64_t str[3] = {4, uint64_t(lda1) * 4, uint64_t(lda2) * 4};
+        uint32_t box[3] = {32, uint32_t(kBlockM), 1};
+        if (!rt_encode_tmap(&p.mapA[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, pa, dims, str, box)) return tma_unsupported("a");
+    }
+    const int lblks = (L + 31) / 32;
+    p.M = I; p.N = R; p.tile_rows = kBlockM;
+    p.total_kb = lblks * Kd;
+    p.num_kb = num_kb;
+    p.tiles_m = (I + kBlockM - 1) / kBlockM;
+    p.tiles_n = splits; p.splits = splits; p.lblks = lblks;
+    p.idesc = idesc_for(AR_TF32X3, kF32, false, bn);
+    p.epi = EPI_COLMAJOR;      // partial[split][r][i], i fastest
+    p.ldo = I;
+    p.out = scratch;
+    p.fc = pc; p.fb = pb; p.ldfc = ldc; p.ldfb = ldb;
+    p.L = L; p.Kdim = Kd; p.R = R;
+    if (int e = run_core(who, AR_TF32X3, OP_MTTKRP, bn, p, sync_after)) return e;
+    if (ldd == I) {
+        if (reduce_partials_launch(scratch, pd, int64_t(I) * R, splits, rt_stream()) != cudaSuccess)
+            return halide_error_code_device_run_failed;
+    } else {
+        for (int r = 0; r < R; ++r)
+            if (reduce_partials_launch(scratch + int64_t(r) * I, pd + int64_t(r) * ldd, I, splits, rt_stream()) != cudaSuccess)
+                return halide_error_code_device_run_failed;
+    }
+    rt_count_launch(ldd == I ? 1 : R);
+    if (sync_after) cudaEventRecord(rt_event(1), rt_stream());
+    return 0;
+}
+
+// Split plan: enough (row tile, split) pairs to give every SM one CTA, never an empty split.
+void mttkrp_plan(int L, int I, int Kd, int want_splits, int* splits, int* num_kb) {
+    const int total_kb = ((L + 31) / 32) * Kd;
+    const int tiles_m = (I + kBlockM - 1) / kBlockM;
+    int s = want_splits > 0 ? want_splits : std::max(1, core_sm_count() / std::max(1, tiles_m));
+    s = std::max(1, std::min(s, total_kb));
+    const int per = (total_kb + s - 1) / s;
+    *num_kb = per;
+    *splits = (total_kb + per - 1) / per;
+}
+}  // namespace t2sp
+
+extern "C" int t2sp_b200_mttkrp(halide_buffer_t* a, halide_buffer_t* b, halide_buffer_t* c, halide_buffer_t* d,
+                                const t2sp_mttkrp_desc* desc) {
+    Arg args[4] = {{a, "a", false, 3}, {b, "b", false, 2}, {c, "c", false, 2}, {d, "d", true, 2}};
+    if (int e = check_null(args, 4)) return e;
+    if (buf_is_bounds_query(a) || buf_is_bounds_query(b) || buf_is_bounds_query(c) || buf_is_bounds_query(d)) {
+        int L = 0, I = 0, Kd = 0, R = 0;
+        if (!buf_is_bounds_query(a) && a->dimensions == 3) { L = a->dim[0].extent; I = a->dim[1].extent; Kd = a->dim[2].extent; }
+        if (!buf_is_bounds_query(b) && b->dimensions == 2) { if (!Kd) Kd = b->dim[0].extent; R = b->dim[1].extent; }
+        if (!buf_is_bounds_query(c) && c->dimensions == 2) { if (!L) L = c->dim[0].extent; if (!R) R = c->dim[1].extent; }
+        if (!buf_is_bounds_query(d) && d->dimensions == 2) { if (!I) I = d->dim[0].extent; if (!R) R = d->dim[1].extent; }
+        if (buf_is_bounds_query(a)) { int e3[3] = {L, I, Kd}; fill_query(a, kF32, 3, e3); }
+        if (buf_is_bounds_query(b)) { int e2[2] = {Kd, R}; fill_query(b, kF32, 2, e2); }
+        if (buf_is_bounds_query(c)) { int e2[2] = {L, R}; fill_query(c, kF32, 2, e2); }
+        if (buf_is_bounds_query(d)) { int e2[2] = {I, R}; fill_query(d, kF32, 2, e2); }
+        return 0;
+    }
+    for (auto& x : args)
+        if (int e = check_type_dims(x, kF32)) return e;
+    for (auto& x : args)
+        if (int e = check_extents_nonneg(x)) return e;
+    const int L = a->dim[0].extent, I = a->dim[1].extent, Kd = a->dim[2].extent, R = b->dim[1].extent;
+    if (b->dim[0].extent != Kd) return constraint("b.extent.0", b->dim[0].extent, "a.extent.2", Kd);
+    if (c->dim[0].extent != L) return constraint("c.extent.0", c->dim[0].extent, "a.extent.0", L);
+    if (c->dim[1].extent != R) return constraint("c.extent.1", c->dim[1].extent, "b.extent.1", R);
+    if (int e = check_covers(args[3], 0, I)) return e;
+    if (int e = check_covers(args[3], 1, R)) return e;
+    for (auto& x : args)
+        if (int e = check_stride0(x)) return e;
+    for (auto& x : args)
+        if (int e = check_sizes(x)) return e;
+    for (auto& x : args)
+        if (int e = check_host(x)) return e;
+    if (I == 0 || R == 0) return 0;
+    if (R > 128) return constraint("b.extent.1", R, "at most", 128);
+
+    if (int e = rt_ensure_device()) return e;
+    const bool resident = all_resident({a, b, c, d});
+    const bool sync_after = !(resident && tls().async);
+    Views vw;
+    if (int e = rt_input_view(a, "a", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = rt_input_view(b, "b", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = rt_input_view(c, "c", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = rt_output_view(d, "d", &vw.v[vw.n])) return e;
+    vw.n++;
+    float* pa = static_cast<float*>(vw.v[0].ptr) + origin_offset(a);
+    float* pb = static_cast<float*>(vw.v[1].ptr) + origin_offset(b);
+    float* pc = static_cast<float*>(vw.v[2].ptr) + origin_offset(c);
+    float* pd = static_cast<float*>(vw.v[3].ptr) + origin_offset(d);
+    if (L == 0 || Kd == 0) {
+        cudaMemsetAsync(vw.v[3].ptr, 0, vw.v[3].bytes, rt_stream());
+    } else {
+        resolve_precision(desc ? desc->precision : 0);
+        int splits = 0, num_kb = 0;
+        mttkrp_plan(L, I, Kd, desc ? desc->splits : 0, &splits, &num_kb);
+        float* scratch = static_cast<float*>(rt_alloc(size_t(splits) * I * R * sizeof(float)));
+        if (!scratch) return halide_error_code_device_malloc_failed;
+        int rc = mttkrp_launch("mttkrp", pa, a->dim[1].stride, a->dim[2].stride, pb, b->dim[1].stride, pc,
+                               c->dim[1].stride, pd, d->dim[1].stride, L, I, Kd, R, splits, num_kb, scratch, sync_after);
+        // Stream order keeps the scratch block safe: a later call on this stream that reuses it
+        // runs after this call's kernels.
+        rt_free(scratch);
+        if (rc) return rc;
+    }
+    if (int e = rt_finish_output(d, "d", &vw.v[3])) return e;
+    return finish_call("mttkrp", "kernel_unloader", sync_after);
+}

@@ -1,0 +1,436 @@
+// The one contraction kernel every operator lowers to.
+//
+// D[M,N] = sum_K A[M,K] * B[K,N] on the sm_100a tensor cores: TMA streams 128-byte-swizzled
+// operand tiles into a multi-stage shared-memory ring, one thread issues tcgen05.mma into a
+// double-buffered TMEM accumulator, four epilogue warps drain TMEM to global memory.
+// Operators differ only in (a) how a (tile, k-block) pair turns into TMA box coordinates
+// (plain matrix, implicit-GEMM convolution, capsule convolution, 3-D tensor slab) and (b)
+// how an output (row, column) turns into an address (row-major, column-major, mixed-radix
+// scatter for the tiled systolic-array layouts).
+//
+// Arithmetic variants: 16-bit floats (bf16/f16, fp32 accumulate), int8 (int32 accumulate,
+// exact) and "3xTF32" for fp32 data: every fp32 tile is split in shared memory into
+// hi = round_to_tf32(x) and lo = x - hi, and three TF32 MMAs (lo*hi, hi*lo, hi*hi) are
+// accumulated so the product keeps ~fp32 accuracy.
+//
+// Every wait on an mbarrier is bounded: after kWaitTimeoutNs the waiting thread raises a
+// status bit in global memory, tells the rest of the CTA to stop, and the CTA drains and
+// frees its TMEM before returning.
+#pragma once
+#include "ptx.cuh"
+#include "umma_params.h"
+
+namespace t2sp {
+
+template <int ARITH> struct ArithTraits;
+template <> struct ArithTraits<AR_F16> {
+    static constexpr int kElem = 2, kBlockK = 64, kUmmaK = 16, kKind = ptx::KIND_F16;
+};
+template <> struct ArithTraits<AR_TF32X3> {
+    static constexpr int kElem = 4, kBlockK = 32, kUmmaK = 8, kKind = ptx::KIND_TF32;
+};
+template <> struct ArithTraits<AR_I8> {
+    static constexpr int kElem = 1, kBlockK = 128, kUmmaK = 32, kKind = ptx::KIND_I8;
+};
+
+template <int ARITH, int OP, int BN, int STAGES>
+struct CoreCfg {
+    using AT = ArithTraits<ARITH>;
+    static constexpr bool kX3 = (ARITH == AR_TF32X3);
+    static constexpr bool kBMnMajor = (OP == OP_GEMM || OP == OP_CONV || OP == OP_CAPSULE);
+    static constexpr bool kBGenerated = (OP == OP_MTTKRP);
+    static constexpr int kABytes = kBlockM * 128;
+    static constexpr int kBBytes = BN * 128;
+    static constexpr int kStageBytes = (kABytes + kBBytes) * (kX3 ? 2 : 1);
+    static constexpr int kBoxBytesMn = AT::kBlockK * 128;           // one MN-major box: kBlockK rows of 128 B
+    static constexpr int kBoxesMn = kBBytes / kBoxBytesMn;          // boxes per MN-major B tile
+    static constexpr int kBoxElemsMn = 128 / AT::kElem;             // N elements per MN-major box
+    static constexpr int kWarps = 2 + 4 + (kX3 ? 4 : 0);
+    static constexpr int kThreads = kWarps * 32;
+    static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kNumBars = 3 * STAGES + 4;
+    static constexpr int kTailBytes = kNumBars * 8 + 16 + 4 * 256 * 8;
+    static constexpr int kSmemBytes = STAGES * kStageBytes + kTailBytes + 1024;
+    static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "TMEM columns must be a power of two");
+    static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
+};
+
+struct AbortCtx {
+    volatile uint32_t* flag;  // shared memory, CTA-wide
+    unsigned* status;         // global memory
+};
+
+__device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ab, unsigned code) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint32_t polls = 0;
+    while (true) {
+        if (ptx::mbar_try_wait(bar, parity)) return true;
+        if ((++polls & 0x3Fu) == 0) {
+            if (*ab.flag) return false;
+            if (ptx::globaltimer_ns() - t0 > kWaitTimeoutNs) {
+                *ab.flag = 1u;
+                atomicOr(ab.status, code);
+                return false;
+            }
+        }
+    }
+}
+
+// Warp-wide form: lane 0 polls, every lane gets the verdict, so the warp stays converged
+// for the .sync.aligned tcgen05 instructions that follow.
+__device__ __forceinline__ bool bounded_wait_warp(uint64_t* bar, uint32_t parity, const AbortCtx& ab, unsigned code,
+                                                  int lane) {
+    int ok = 1;
+    if (lane == 0) ok = bounded_wait(bar, parity, ab, code) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0;
+}
+
+__device__ __forceinline__ long long digits_offset(const Digits& d, int x) {
+    long long off = 0;
+#pragma unroll
+    for (int i = 0; i < kMaxDigits; ++i)
+        if (i < d.n) off += static_cast<long long>((((x / d.div[i]) % d.mod[i]) / d.div2[i]) % d.mod2[i]) * d.stride[i];
+    return off;
+}
+
+// k-blocks the tile of split `nb` walks (all tiles walk num_kb except MTTKRP's last split).
+template <int OP>
+__device__ __forceinline__ int kb_count(const CoreParams& p, int nb) {
+    if constexpr (OP == OP_MTTKRP) return max(0, min(p.num_kb, p.total_kb - nb * p.num_kb));
+    else return p.num_kb;
+}
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mb, int& nb) {
+    // Groups of 16 row-blocks sweep all column-blocks, rows fastest inside a group, so the
+    // CTAs running at the same time share a small set of A and B panels in L2.
+    constexpr int G = 16;
+    const int per_group = G * tiles_n;
+    const int g = t / per_group, r = t % per_group;
+    const int gm = min(G, tiles_m - g * G);
+    mb = g * G + r % gm;
+    nb = r / gm;
+}
+
+template <int ARITH, int OP, int BN, int STAGES>
+__global__ void __launch_bounds__(CoreCfg<ARITH, OP, BN, STAGES>::kThreads, 1)
+umma_contract_kernel(const __grid_constant__ CoreParams p) {
+    using Cfg = CoreCfg<ARITH, OP, BN, STAGES>;
+    using AT = typename Cfg::AT;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* tail = smem + STAGES * Cfg::kStageBytes;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);  // TMA data landed
+    uint64_t* ready_bar = full_bar + STAGES;                 // 3xTF32: hi/lo split done
+    uint64_t* empty_bar = ready_bar + STAGES;                // MMAs that read the stage retired
+    uint64_t* tfull_bar = empty_bar + STAGES;                // accumulator complete (2)
+    uint64_t* tempty_bar = tfull_bar + 2;                    // accumulator drained (2)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+    uint32_t* abort_slot = tmem_slot + 1;
+    long long* ntable = reinterpret_cast<long long*>(tmem_slot + 4);  // one 256-entry scatter table per epilogue warp
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const AbortCtx ab{abort_slot, p.status};
+    const int num_tiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(&full_bar[s], 1);
+            ptx::mbar_init(&ready_bar[s], 128);
+            ptx::mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(&tfull_bar[a], 1);
+            ptx::mbar_init(&tempty_bar[a], 4);
+        }
+        *abort_slot = 0u;
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc<1>(tmem_slot, Cfg::kTmemCols);
+        ptx::tmem_relinquish<1>();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            if constexpr (OP == OP_CAPSULE) {
+                for (int i = 0; i < 4; ++i) ptx::prefetch_tensormap(&p.mapA[i]);
+            } else {
+                ptx::prefetch_tensormap(&p.mapA[0]);
+            }
+            if constexpr (!Cfg::kBGenerated) ptx::prefetch_tensormap(&p.mapB);
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                int mb, nb;
+                if constexpr (OP == OP_MTTKRP) { mb = t % p.tiles_m; nb = t / p.tiles_m; }
+                else tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+                const int m0 = mb * p.tile_rows, n0 = nb * BN;
+                const int nkb = kb_count<OP>(p, nb);
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!bounded_wait(&empty_bar[s], ph ^ 1, ab, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+                    uint8_t* sa = smem + s * Cfg::kStageBytes;
+                    uint8_t* sb = sa + Cfg::kABytes;
+                    ptx::mbar_expect_tx(&full_bar[s], Cfg::kABytes + (Cfg::kBGenerated ? 0 : Cfg::kBBytes));
+                    if constexpr (OP == OP_GEMM || OP == OP_TTM) {
+                        ptx::tma_load_2d(sa, &p.mapA[0], &full_bar[s], kb * AT::kBlockK, m0);
+                        if constexpr (OP == OP_TTM) {
+                            ptx::tma_load_2d(sb, &p.mapB, &full_bar[s], kb * AT::kBlockK, n0);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < Cfg::kBoxesMn; ++j)
+                                ptx::tma_load_2d(sb + j * Cfg::kBoxBytesMn, &p.mapB, &full_bar[s],
+                                                 n0 + j * Cfg::kBoxElemsMn, kb * AT::kBlockK);
+                        }
+                    } else if constexpr (OP == OP_CONV || OP == OP_CAPSULE) {
+                        const int tap = kb / p.cblks, cb = kb % p.cblks;
+                        const int ky = tap % p.KY, kx = tap / p.KY;
+                        const int c0 = cb * AT::kBlockK;
+                        for (int j = 0; j < p.rows.boxes_per_tile; ++j) {
+                            int r = m0 + j * p.rows.rows_per_box;
+                            int c[4] = {0, 0, 0, 0};
+#pragma unroll
+                            for (int d = 0; d < 4; ++d) {
+                                if (d < p.rows.nd - 1) { c[d] = r % p.rows.ext[d]; r /= p.rows.ext[d]; }
+                                else if (d == p.rows.nd - 1) { c[d] = r; }
+                            }
+                            uint8_t* dst = sa + j * p.rows.rows_per_box * 128;
+                            if constexpr (OP == OP_CONV) {
+                                // input tensor (ci, n, iy, ix); rows are (n, oy, ox)
+                                ptx::tma_load_4d(dst, &p.mapA[0], &full_bar[s], c0, c[0], c[1] + ky, c[2] + kx);
+                            } else {
+                                // input tensor per stride parity (c', q, iy', ix', n); rows are (q, oy, ox, n)
+                                const int sy = ky % p.stride, sx = kx % p.stride;
+                                ptx::tma_load_5d(dst, &p.mapA[sy + 2 * sx], &full_bar[s], c0, c[0],
+                                                 c[1] + ky / p.stride, c[2] + kx / p.stride, c[3]);
+                            }
+                        }
+                        if constexpr (OP == OP_CONV) {
+                            // weight tensor (co, kx, ci, ky)
+#pragma unroll
+                            for (int j = 0; j < Cfg::kBoxesMn; ++j)
+                                ptx::tma_load_4d(sb + j * Cfg::kBoxBytesMn, &p.mapB, &full_bar[s],
+                                                 n0 + j * Cfg::kBoxElemsMn, kx, c0, ky);
+                        } else {
+                            // weight tensor (n=(co,my), cii, tap, ci_outer, mk); c' = ci + CI*mk
+                            const int mk0 = c0 / p.CI, ci0 = c0 % p.CI;
+#pragma unroll
+                            for (int j = 0; j < Cfg::kBoxesMn; ++j)
+                                ptx::tma_load_5d(sb + j * Cfg::kBoxBytesMn, &p.mapB, &full_bar[s],
+                                                 n0 + j * Cfg::kBoxElemsMn, ci0 % p.CII, tap, ci0 / p.CII, mk0);
+                        }
+                    } else {
+                        // MTTKRP: tensor (l, i, k); this CTA's split walks k-blocks [nb*num_kb, (nb+1)*num_kb)
+                        const int g = nb * p.num_kb + kb;
+                        const int lb = g / p.Kdim, k = g % p.Kdim;
+                        ptx::tma_load_3d(sa, &p.mapA[0], &full_bar[s], lb * AT::kBlockK, m0, k);
+                    }
+                }
+            }
+            if (!ok) {
+                // Give copies already in flight a bounded chance to land before the CTA exits.
+                for (int s = 0; s < STAGES; ++s) {
+                    const int last = it - 1 - ((it - 1 - s) % STAGES + STAGES) % STAGES;
+                    if (last >= 0) {
+                        for (int spin = 0; spin < 100000; ++spin)
+                            if (ptx::mbar_try_wait(&full_bar[s], (last / STAGES) & 1)) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            int it = 0, lt = 0;
+            bool ok = true;
+            constexpr uint32_t kStepK = 32 >> 4;                                           // K-major: 32 B per UMMA
+            constexpr uint32_t kStepMn = (AT::kUmmaK * 128) >> 4;                          // MN-major: kUmmaK rows
+            constexpr uint32_t kStepB = Cfg::kBMnMajor ? kStepMn : kStepK;
+            constexpr uint32_t kLboB = Cfg::kBMnMajor ? Cfg::kBoxBytesMn : 16;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+                const int acc = lt & 1;
+                if (!bounded_wait(&tempty_bar[acc], ((lt >> 1) & 1) ^ 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
+                ptx::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                const int nkb = kb_count<OP>(p, (OP == OP_MTTKRP) ? t / p.tiles_m : 0);
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    uint64_t* go = Cfg::kX3 ? &ready_bar[s] : &full_bar[s];
+                    if (!bounded_wait(go, ph, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t sa = ptx::smem_u32(smem + s * Cfg::kStageBytes);
+                    const uint32_t sb = sa + Cfg::kABytes;
+                    const uint64_t da = ptx::make_smem_desc(sa, 16, 1024);
+                    const uint64_t db = ptx::make_smem_desc(sb, kLboB, 1024);
+                    if constexpr (Cfg::kX3) {
+                        const uint64_t dal = ptx::make_smem_desc(sb + Cfg::kBBytes, 16, 1024);
+                        const uint64_t dbl = ptx::make_smem_desc(sb + Cfg::kBBytes + Cfg::kABytes, kLboB, 1024);
+#pragma unroll
+                        for (int j = 0; j < AT::kBlockK / AT::kUmmaK; ++j) {
+                            const uint32_t first = (kb | j) ? 1u : 0u;
+                            ptx::umma<AT::kKind, 1>(d_tmem, dal + j * kStepK, db + j * kStepB, p.idesc, first);
+                            ptx::umma<AT::kKind, 1>(d_tmem, da + j * kStepK, dbl + j * kStepB, p.idesc, 1u);
+                            ptx::umma<AT::kKind, 1>(d_tmem, da + j * kStepK, db + j * kStepB, p.idesc, 1u);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < AT::kBlockK / AT::kUmmaK; ++j)
+                            ptx::umma<AT::kKind, 1>(d_tmem, da + j * kStepK, db + j * kStepB, p.idesc,
+                                                    (kb | j) ? 1u : 0u);
+                    }
+                    ptx::umma_commit(&empty_bar[s]);
+                }
+                if (ok) ptx::umma_commit(&tfull_bar[acc]);
+            }
+        }
+    } else if (warp < 6) {
+        // ------------------------------------------------------------ epilogue (TMEM -> global)
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        int lt = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+            int mb, nb;
+            if constexpr (OP == OP_MTTKRP) { mb = t % p.tiles_m; nb = t / p.tiles_m; }
+            else tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+            const int acc = lt & 1;
+            const int row = q * 32 + lane;
+            const int m = mb * p.tile_rows + row;
+            const int n0 = (OP == OP_MTTKRP) ? 0 : nb * BN;
+            long long* ntab = ntable + (warp - 2) * 256;
+            long long offm = 0;
+            if (p.epi == EPI_SCATTER) {
+                __syncwarp();
+                for (int j = lane; j < BN; j += 32) ntab[j] = digits_offset(p.dn, n0 + j);
+                offm = digits_offset(p.dm, m);
+                __syncwarp();
+            }
+            if (!bounded_wait_warp(&tfull_bar[acc], (lt >> 1) & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
+            ptx::tc_fence_after_sync();
+            uint32_t* out32 = reinterpret_cast<uint32_t*>(p.out);
+            if constexpr (OP == OP_MTTKRP) out32 += static_cast<long long>(nb) * p.M * p.N;  // partial slab of this split
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, r);
+                ptx::tmem_ld_wait();
+                const int nc = n0 + c * 32;
+                if (row < p.tile_rows && m < p.M && nc < p.N) {
+                    if (p.epi == EPI_ROWMAJOR) {
+                        uint32_t* dst = out32 + static_cast<long long>(m) * p.ldo + nc;
+                        if (nc + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (nc + j < p.N) dst[j] = r[j];
+                        }
+                    } else if (p.epi == EPI_COLMAJOR) {
+                        uint32_t* dst = out32 + static_cast<long long>(nc) * p.ldo + m;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (nc + j < p.N) dst[static_cast<long long>(j) * p.ldo] = r[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (nc + j < p.N) out32[offm + ntab[c * 32 + j]] = r[j];
+                    }
+                }
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&tempty_bar[acc]);
+        }
+    } else {
+        // ------------------------------------------------------------ 3xTF32 splitter (and MTTKRP B generator)
+        if constexpr (Cfg::kX3) {
+            const int st = (warp - 6) * 32 + lane;
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int nb = (OP == OP_MTTKRP) ? t / p.tiles_m : 0;
+                const int nkb = kb_count<OP>(p, nb);
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    uint8_t* hi = smem + s * Cfg::kStageBytes;
+                    uint8_t* lo = hi + Cfg::kABytes + Cfg::kBBytes;
+                    if constexpr (Cfg::kBGenerated) {
+                        // The B tile is the Khatri-Rao slab KR[(l,k), r] = c(l,r) * b(k,r) for this
+                        // k-block, written K-major with the 128-byte swizzle; it can be built while
+                        // the A tile is still in flight, but only once the stage is free.
+                        if (!bounded_wait_warp(&empty_bar[s], ph ^ 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
+                        const int g = nb * p.num_kb + kb;
+                        const int lb = g / p.Kdim, k = g % p.Kdim;
+                        // each thread builds 16-byte chunks: row r of the tile, 4 consecutive l values
+                        for (int idx = st; idx < BN * 8; idx += 128) {
+                            const int r = idx >> 3, ch = idx & 7;
+                            float v[4] = {0.f, 0.f, 0.f, 0.f};
+                            if (r < p.R) {
+                                const int l = lb * 32 + ch * 4;
+                                const float* cp = p.fc + static_cast<long long>(r) * p.ldfc + l;
+                                const float bv = __ldg(p.fb + static_cast<long long>(r) * p.ldfb + k);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    if (l + e < p.L) v[e] = __ldg(cp + e) * bv;
+                            }
+                            float h[4], l4[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                uint32_t hb;
+                                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(v[e]));
+                                h[e] = __uint_as_float(hb);
+                                l4[e] = v[e] - h[e];
+                            }
+                            const int off = Cfg::kABytes + r * 128 + ((ch ^ (r & 7)) << 4);
+                            *reinterpret_cast<float4*>(hi + off) = make_float4(h[0], h[1], h[2], h[3]);
+                            *reinterpret_cast<float4*>(lo + off) = make_float4(l4[0], l4[1], l4[2], l4[3]);
+                        }
+                    }
+                    if (!bounded_wait_warp(&full_bar[s], ph, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
+                    constexpr int kSplitBytes = Cfg::kBGenerated ? Cfg::kABytes : (Cfg::kABytes + Cfg::kBBytes);
+                    // A stage holds [A_hi | B_hi | A_lo | B_lo]; the lo half mirrors the hi half, so one
+                    // flat loop over the hi bytes splits both operands.
+#pragma unroll 4
+                    for (int off = st * 16; off < kSplitBytes; off += 128 * 16) {
+                        const float4 v = *reinterpret_cast<const float4*>(hi + off);
+                        float x[4] = {v.x, v.y, v.z, v.w}, h[4], l4[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            uint32_t hb;
+                            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x[e]));
+                            h[e] = __uint_as_float(hb);
+                            l4[e] = x[e] - h[e];
+                        }
+                        *reinterpret_cast<float4*>(hi + off) = make_float4(h[0], h[1], h[2], h[3]);
+                        *reinterpret_cast<float4*>(lo + off) = make_float4(l4[0], l4[1], l4[2], l4[3]);
+                    }
+                    ptx::fence_proxy_async_smem();
+                    ptx::mbar_arrive(&ready_bar[s]);
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (*abort_slot) __nanosleep(200000);  // let stray UMMAs / copies retire before TMEM goes away
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc<1>(tmem_base, Cfg::kTmemCols);
+    }
+}
+
+}  // namespace t2sp

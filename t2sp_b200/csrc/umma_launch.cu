@@ -1,0 +1,96 @@
+// Instantiations of the contraction kernel and their launch table.
+#include "umma_core.cuh"
+#include "umma_launch.h"
+
+namespace t2sp {
+
+namespace {
+
+template <int ARITH, int OP, int BN, int STAGES>
+cudaError_t launch_one(const CoreParams& p, int grid, cudaStream_t stream) {
+    using Cfg = CoreCfg<ARITH, OP, BN, STAGES>;
+    auto kern = umma_contract_kernel<ARITH, OP, BN, STAGES>;
+    static bool configured[16] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 16 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
+__global__ void reduce_partials_kernel(const float* __restrict__ partials, float* __restrict__ out, long long elems,
+                                       int splits) {
+    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (i >= elems) return;
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += partials[s * elems + i];
+    out[i] = acc;
+}
+
+}  // namespace
+
+int core_sm_count() {
+    static int cached[16] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 16) dev = 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+int core_pick_bn(int arith, int op, int n_extent) {
+    switch (arith) {
+        case AR_F16:
+        case AR_I8:
+            if (op == OP_GEMM || op == OP_TTM) return n_extent > 128 ? 256 : 128;
+            return 0;
+        case AR_TF32X3:
+            if (op == OP_MTTKRP) return n_extent <= 64 ? 64 : (n_extent <= 128 ? 128 : 0);
+            if (op == OP_GEMM || op == OP_TTM || op == OP_CONV || op == OP_CAPSULE) return n_extent > 64 ? 128 : 64;
+            return 0;
+    }
+    return 0;
+}
+
+cudaError_t core_launch(int arith, int op, int bn, const CoreParams& p, int grid, cudaStream_t stream) {
+#define T2SP_CASE(AR, OPC, BNV, ST) \
+    if (arith == AR && op == OPC && bn == BNV) return launch_one<AR, OPC, BNV, ST>(p, grid, stream)
+    T2SP_CASE(AR_F16, OP_GEMM, 256, 4);
+    T2SP_CASE(AR_F16, OP_GEMM, 128, 6);
+    T2SP_CASE(AR_F16, OP_TTM, 256, 4);
+    T2SP_CASE(AR_F16, OP_TTM, 128, 6);
+    T2SP_CASE(AR_I8, OP_GEMM, 256, 4);
+    T2SP_CASE(AR_I8, OP_GEMM, 128, 6);
+    T2SP_CASE(AR_I8, OP_TTM, 256, 4);
+    T2SP_CASE(AR_I8, OP_TTM, 128, 6);
+    T2SP_CASE(AR_TF32X3, OP_GEMM, 128, 3);
+    T2SP_CASE(AR_TF32X3, OP_GEMM, 64, 4);
+    T2SP_CASE(AR_TF32X3, OP_TTM, 128, 3);
+    T2SP_CASE(AR_TF32X3, OP_TTM, 64, 4);
+    T2SP_CASE(AR_TF32X3, OP_CONV, 128, 3);
+    T2SP_CASE(AR_TF32X3, OP_CONV, 64, 4);
+    T2SP_CASE(AR_TF32X3, OP_CAPSULE, 128, 3);
+    T2SP_CASE(AR_TF32X3, OP_CAPSULE, 64, 4);
+    T2SP_CASE(AR_TF32X3, OP_MTTKRP, 64, 4);
+    T2SP_CASE(AR_TF32X3, OP_MTTKRP, 128, 3);
+#undef T2SP_CASE
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t reduce_partials_launch(const float* partials, float* out, long long elems, int splits,
+                                   cudaStream_t stream) {
+    const int threads = 256;
+    const long long blocks = (elems + threads - 1) / threads;
+    reduce_partials_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(partials, out, elems, splits);
+    return cudaGetLastError();
+}
+
+}  // namespace t2sp

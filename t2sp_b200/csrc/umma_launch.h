@@ -1,0 +1,25 @@
+// Host entry to the contraction kernel family (definitions in umma_launch.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+#include "umma_params.h"
+
+namespace t2sp {
+
+// Column-tile widths compiled for each arithmetic/operator pair; 0 terminates.
+// Returns the tile width to use for an N-extent, or 0 when the pair is not compiled.
+int core_pick_bn(int arith, int op, int n_extent);
+
+// Launches umma_contract_kernel<arith, op, bn, stages> with `grid` persistent CTAs.
+// Returns cudaSuccess or the launch error.
+cudaError_t core_launch(int arith, int op, int bn, const CoreParams& p, int grid, cudaStream_t stream);
+
+// Number of SMs of the current device (cached).
+int core_sm_count();
+
+// Sums `splits` partial slabs of `elems` fp32 values each into `out` in slab order
+// (deterministic), used by the split-K MTTKRP.
+cudaError_t reduce_partials_launch(const float* partials, float* out, long long elems, int splits,
+                                   cudaStream_t stream);
+
+}  // namespace t2sp

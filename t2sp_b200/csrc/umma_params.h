@@ -1,0 +1,84 @@
+// Parameter block shared by the host lowering code and the contraction kernel.
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+namespace t2sp {
+
+enum : int { AR_F16 = 0, AR_TF32X3 = 1, AR_I8 = 2 };
+enum : int { OP_GEMM = 0, OP_TTM = 1, OP_CONV = 2, OP_CAPSULE = 3, OP_MTTKRP = 4 };
+enum : int { EPI_ROWMAJOR = 0, EPI_COLMAJOR = 1, EPI_SCATTER = 2 };
+
+// Status bits written by a kernel whose wait ran out (which role gave up).
+enum : unsigned {
+    ST_TIMEOUT_PRODUCER = 1u,
+    ST_TIMEOUT_MMA = 2u,
+    ST_TIMEOUT_EPILOGUE = 4u,
+    ST_TIMEOUT_SPLITTER = 8u,
+};
+
+constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s
+constexpr int kBlockM = 128;
+constexpr int kMaxDigits = 8;
+
+// offset(x) = sum_i ((((x / div[i]) % mod[i]) / div2[i]) % mod2[i]) * stride[i]
+// (the second stage lets a digit be taken of a sub-index such as the pixel number inside a row index)
+struct Digits {
+    int n;
+    int div[kMaxDigits];
+    int mod[kMaxDigits];
+    int div2[kMaxDigits];
+    int mod2[kMaxDigits];
+    long long stride[kMaxDigits];
+};
+
+// 32-bit tcgen05 instruction descriptor for kind::f16 / kind::tf32 / kind::i8:
+//   [4,6) D format (0 f16, 1 f32, 2 s32)   [7,10) A format   [10,13) B format
+//   (f16 kind: 0 f16, 1 bf16; tf32 kind: 2; i8 kind: 0 u8, 1 s8)
+//   [15] A is MN-major   [16] B is MN-major   [17,23) N>>3   [24,29) M>>4
+constexpr uint32_t make_instr_desc(uint32_t d_fmt, uint32_t ab_fmt, bool a_mn_major, bool b_mn_major, uint32_t m,
+                                   uint32_t n) {
+    return (d_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | (uint32_t(a_mn_major) << 15) |
+           (uint32_t(b_mn_major) << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// How the GEMM row index decomposes into up to four nested tensor coordinates
+// (ext[0] fastest) and how a 128-row tile is cut into TMA boxes.
+struct RowSpace {
+    int nd;
+    int ext[4];
+    int rows_per_box;    // rows one TMA box brings (divides 128, or the whole row space if smaller)
+    int boxes_per_tile;  // boxes issued per 128-row tile
+};
+
+struct CoreParams {
+    CUtensorMap mapA[4];
+    CUtensorMap mapB;
+    int M, N;         // GEMM-view extents of the output
+    int tile_rows;    // output rows per tile (128 unless the row boxes cannot fill a tile)
+    int num_kb;       // k-blocks per output tile (per split for MTTKRP)
+    int total_kb;     // MTTKRP: k-blocks over all splits (the last split may get fewer)
+    int tiles_m, tiles_n;
+    uint32_t idesc;   // tcgen05 instruction descriptor
+    int epi;          // EPI_*
+    void* out;        // fp32 or int32 elements
+    long long ldo;    // EPI_ROWMAJOR: row pitch; EPI_COLMAJOR: column pitch (elements)
+    Digits dm, dn;    // EPI_SCATTER
+    RowSpace rows;    // OP_CONV / OP_CAPSULE
+    // convolution-style k-block walk: kb -> (tap, channel block)
+    int cblks;        // channel blocks per filter tap
+    int KY, KX;       // filter taps (tap = ky + KY*kx)
+    int stride;       // capsule spatial stride (1 or 2)
+    // capsule weight box walk: channel block -> (cii0, cio0, mk0)
+    int CI, CII;
+    // MTTKRP
+    int splits;       // split-K factor (tiles_n is reused for it)
+    int lblks;        // l-blocks per k slice
+    const float* fc;  // c(l,r), l fastest, column pitch ldfc
+    const float* fb;  // b(k,r), k fastest, column pitch ldfb
+    long long ldfc, ldfb;
+    int L, Kdim, R;
+    unsigned* status;
+};
+
+}  // namespace t2sp
