@@ -71,6 +71,7 @@ typedef struct t2sp_gemm_desc {
     int32_t layout;
     int32_t JJJ, III, JJ, II; /* layout 1: inner tile extents (0 = read them from C) */
     int32_t precision;        /* enum t2sp_precision */
+    int32_t trans_b;          /* 1: B is stored transposed, 2-D (K_tot, J_tot) with k innermost */
 } t2sp_gemm_desc;
 int t2sp_b200_gemm(halide_buffer_t *A, halide_buffer_t *B, halide_buffer_t *C, const t2sp_gemm_desc *desc);
 

@@ -16,7 +16,7 @@ _lib = None
 
 
 class GemmDesc(ctypes.Structure):
-    _fields_ = [(n, ctypes.c_int32) for n in ("layout", "JJJ", "III", "JJ", "II", "precision")]
+    _fields_ = [(n, ctypes.c_int32) for n in ("layout", "JJJ", "III", "JJ", "II", "precision", "trans_b")]
 
 
 class ConvDesc(ctypes.Structure):

@@ -311,8 +311,10 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
     for (auto& a : args)
         if (int e = check_extents_nonneg(a)) return e;
 
-    const int K = A->dim[0].extent, M = A->dim[1].extent, N = B->dim[0].extent;
-    if (B->dim[1].extent != K) return constraint("B.extent.1", B->dim[1].extent, "A.extent.0", K);
+    const bool trans_b = desc && desc->trans_b;
+    const int K = A->dim[0].extent, M = A->dim[1].extent, N = B->dim[trans_b ? 1 : 0].extent;
+    if (B->dim[trans_b ? 0 : 1].extent != K)
+        return constraint(trans_b ? "B.extent.0" : "B.extent.1", B->dim[trans_b ? 0 : 1].extent, "A.extent.0", K);
 
     // ---- output coverage
     int JJJ = 1, III = 1, JJ = 1, II = 1;
@@ -362,7 +364,8 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         const int arith = arith_for(in_t);
         if (arith == AR_TF32X3) resolve_precision(desc ? desc->precision : 0);
         const int bk = block_k_for(arith);
-        const int bn = core_pick_bn(arith, OP_GEMM, N);
+        const int op = trans_b ? OP_TTM : OP_GEMM;  // OP_TTM is the "both operands K-major" loader
+        const int bn = core_pick_bn(arith, op, N);
         const int64_t lda = int64_t(A->dim[1].stride) * es, ldb = int64_t(B->dim[1].stride) * es;
         if (!tma_ok(pa, {lda})) return tma_unsupported("A");
         if (!tma_ok(pb, {ldb})) return tma_unsupported("B");
@@ -373,15 +376,19 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
             uint32_t box[2] = {uint32_t(bk), uint32_t(kBlockM)};
             if (!rt_encode_tmap(&p.mapA[0], tmap_type(in_t), 2, pa, dims, str, box)) return tma_unsupported("A");
         }
-        {
+        if (trans_b) {
+            uint64_t dims[2] = {uint64_t(K), uint64_t(N)}, str[2] = {uint64_t(es), uint64_t(ldb)};
+            uint32_t box[2] = {uint32_t(bk), uint32_t(bn)};
+            if (!rt_encode_tmap(&p.mapB, tmap_type(in_t), 2, pb, dims, str, box)) return tma_unsupported("B");
+        } else {
             uint64_t dims[2] = {uint64_t(N), uint64_t(K)}, str[2] = {uint64_t(es), uint64_t(ldb)};
             uint32_t box[2] = {uint32_t(128 / es), uint32_t(bk)};
-            if (!rt_encode_tmap(&p.mapB, tmap_type(in_t), 2, pb, dims, str, box)) return tma_unsupported("B");
+            if (!rt_encode_tmap(&p.mapB, tmap_type(in_t), 2, pb, dims, str, box, arith == AR_TF32X3)) return tma_unsupported("B");
         }
-        p.M = M; p.N = N; p.tile_rows = kBlockM;
+        p.M = M; p.N = N; p.tile_rows = kBlockM; p.a_tx_bytes = kBlockM * 128;
         p.num_kb = (K + bk - 1) / bk; p.total_kb = p.num_kb;
         p.tiles_m = (M + kBlockM - 1) / kBlockM; p.tiles_n = (N + bn - 1) / bn;
-        p.idesc = idesc_for(arith, in_t, true, bn);
+        p.idesc = idesc_for(arith, in_t, !trans_b, bn);
         p.out = pc;
         if (layout == 0) {
             p.epi = EPI_ROWMAJOR;
@@ -395,7 +402,7 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
             add_digit(p.dn, JJJ, JJ, C->dim[2].stride);
             add_digit(p.dn, JJJ * JJ, 1 << 30, C->dim[4].stride);
         }
-        if (int e = run_core("gemm", arith, OP_GEMM, bn, p, sync_after)) return e;
+        if (int e = run_core("gemm", arith, op, bn, p, sync_after)) return e;
     }
     if (int e = rt_finish_output(C, "C", &vw.v[2])) return e;
     return finish_call("gemm", "kernel_Out", sync_after);
@@ -488,7 +495,7 @@ extern "C" int t2sp_b200_ttm(halide_buffer_t* a, halide_buffer_t* b, halide_buff
             uint32_t box[2] = {32, uint32_t(bn)};
             if (!rt_encode_tmap(&p.mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, pb, dims, str, box)) return tma_unsupported("b");
         }
-        p.M = M; p.N = N; p.tile_rows = kBlockM;
+        p.M = M; p.N = N; p.tile_rows = kBlockM; p.a_tx_bytes = kBlockM * 128;
         p.num_kb = (L + 31) / 32; p.total_kb = p.num_kb;
         p.tiles_m = (M + kBlockM - 1) / kBlockM; p.tiles_n = (N + bn - 1) / bn;
         p.idesc = idesc_for(AR_TF32X3, kF32, false, bn);
@@ -622,10 +629,11 @@ extern "C" int t2sp_b200_conv(halide_buffer_t* I, halide_buffer_t* K, halide_buf
         uint64_t dims[4] = {uint64_t(CO), uint64_t(KX), uint64_t(CI), uint64_t(KY)};
         uint64_t str[4] = {4, uint64_t(CO) * 4, uint64_t(t1), uint64_t(CI) * uint64_t(t1)};
         uint32_t box[4] = {32, 1, 32, 1};
-        if (!rt_encode_tmap(&p.mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, pk, dims, str, box)) return tma_unsupported("K");
+        if (!rt_encode_tmap(&p.mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, pk, dims, str, box, true)) return tma_unsupported("K");
     }
     p.M = static_cast<int>(Mrows); p.N = CO;
     p.tile_rows = p.rows.rows_per_box * p.rows.boxes_per_tile;
+    p.a_tx_bytes = p.tile_rows * 128;
     p.cblks = (CI + 31) / 32; p.KY = KY; p.KX = KX; p.stride = 1;
     p.num_kb = KY * KX * p.cblks; p.total_kb = p.num_kb;
     p.tiles_m = (p.M + p.tile_rows - 1) / p.tile_rows; p.tiles_n = (CO + bn - 1) / bn;
@@ -782,10 +790,11 @@ extern "C" int t2sp_b200_capsule(halide_buffer_t* P, halide_buffer_t* W, halide_
         uint64_t str[5] = {4, uint64_t(t1), uint64_t(CII) * uint64_t(t1), uint64_t(CII) * KY * KX * uint64_t(t1),
                            uint64_t(CI) * KY * KX * uint64_t(t1)};
         uint32_t box[5] = {32, uint32_t(bcii), 1, uint32_t(bcio), uint32_t(bmk)};
-        if (!rt_encode_tmap(&p.mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, pw, dims, str, box)) return tma_unsupported("W");
+        if (!rt_encode_tmap(&p.mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 5, pw, dims, str, box, true)) return tma_unsupported("W");
     }
     p.M = static_cast<int>(Mrows); p.N = NW;
     p.tile_rows = p.rows.rows_per_box * p.rows.boxes_per_tile;
+    p.a_tx_bytes = p.tile_rows * 128;
     p.cblks = (CP + 31) / 32; p.KY = KY; p.KX = KX; p.stride = s; p.CI = CI; p.CII = CII;
     p.num_kb = KY * KX * p.cblks; p.total_kb = p.num_kb;
     p.tiles_m = (p.M + p.tile_rows - 1) / p.tile_rows; p.tiles_n = (NW + bn - 1) / bn;
@@ -843,7 +852,7 @@ int mttkrp_launch(const char* who, float* pa, int64_t lda1, int64_t lda2, const 
         if (!rt_encode_tmap(&p.mapA[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, pa, dims, str, box)) return tma_unsupported("a");
     }
     const int lblks = (L + 31) / 32;
-    p.M = I; p.N = R; p.tile_rows = kBlockM;
+    p.M = I; p.N = R; p.tile_rows = kBlockM; p.a_tx_bytes = kBlockM * 128;
     p.total_kb = lblks * Kd;
     p.num_kb = num_kb;
     p.tiles_m = (I + kBlockM - 1) / kBlockM;

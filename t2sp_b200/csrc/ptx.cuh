@@ -220,6 +220,15 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -228,19 +237,23 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // 64-bit shared-memory matrix descriptor (sm_100 "version 1"):
 //   [0,14)  start address >> 4        [16,30) leading-dimension byte offset >> 4
 //   [32,46) stride-dimension byte offset >> 4      [46,48) version = 1
-//   [61,64) swizzle mode: 0 none, 2 = 128-byte, 4 = 64-byte, 6 = 32-byte
+//   [61,64) swizzle mode: 0 none, 1 = 128-byte span / 32-byte atoms, 2 = 128-byte, 4 = 64-byte, 6 = 32-byte
 // With the 128-byte swizzle the operand tile is a stack of 1024-byte atoms
 // (8 rows x 128 bytes). K-major operand: rows are M/N indices, SBO is the step between
 // 8-row groups, LBO is unused (encoded 1). MN-major operand: rows are K indices, each
 // 128-byte row holds consecutive M/N elements; LBO is the step between 128-byte-wide
 // column blocks along M/N and SBO the step between 8-row groups along K.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// MN-major 32-bit (tf32) operands exist only in the "128-byte span, 32-byte atom" swizzle
+// (mode 1, TMA's SWIZZLE_128B_ATOM_32B): atoms are 4 rows x 128 bytes = 512 bytes, so SBO
+// is the step between 4-row groups.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                                   uint32_t swizzle_mode = 2) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
     d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
     d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
+    d |= static_cast<uint64_t>(swizzle_mode) << 61;
     return d;
 }
 

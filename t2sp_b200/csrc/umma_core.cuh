@@ -11,7 +11,11 @@
 // Arithmetic variants: 16-bit floats (bf16/f16, fp32 accumulate), int8 (int32 accumulate,
 // exact) and "3xTF32" for fp32 data: every fp32 tile is split in shared memory into
 // hi = round_to_tf32(x) and lo = x - hi, and three TF32 MMAs (lo*hi, hi*lo, hi*hi) are
-// accumulated so the product keeps ~fp32 accuracy.
+// accumulated so the product keeps ~fp32 accuracy. The tensor core adds into its fp32
+// accumulator with truncation, a bias that grows with the number of accumulate steps, so the
+// 3xTF32 path (a) sums the small cross terms in an accumulator of their own and (b) lets
+// the hi*hi accumulator run for only kChunkKb k-blocks before the epilogue warps add it,
+// round-to-nearest, into fp32 registers.
 //
 // Every wait on an mbarrier is bounded: after kWaitTimeoutNs the waiting thread raises a
 // status bit in global memory, tells the rest of the CTA to stop, and the CTA drains and
@@ -39,6 +43,9 @@ struct CoreCfg {
     static constexpr bool kX3 = (ARITH == AR_TF32X3);
     static constexpr bool kBMnMajor = (OP == OP_GEMM || OP == OP_CONV || OP == OP_CAPSULE);
     static constexpr bool kBGenerated = (OP == OP_MTTKRP);
+    // MN-major fp32 tiles use the 32-byte-atom flavour of the 128-byte swizzle (4-row atoms).
+    static constexpr uint32_t kBSwizzle = (kBMnMajor && ARITH == AR_TF32X3) ? 1u : 2u;
+    static constexpr uint32_t kBSbo = (kBMnMajor && ARITH == AR_TF32X3) ? 512u : 1024u;
     static constexpr int kABytes = kBlockM * 128;
     static constexpr int kBBytes = BN * 128;
     static constexpr int kStageBytes = (kABytes + kBBytes) * (kX3 ? 2 : 1);
@@ -47,11 +54,15 @@ struct CoreCfg {
     static constexpr int kBoxElemsMn = 128 / AT::kElem;             // N elements per MN-major box
     static constexpr int kWarps = 2 + 4 + (kX3 ? 4 : 0);
     static constexpr int kThreads = kWarps * 32;
-    static constexpr int kTmemCols = 2 * BN;
-    static constexpr int kNumBars = 3 * STAGES + 4;
+    // 16-bit / int8: two whole-tile accumulators (tile t+1 accumulates while tile t drains).
+    // 3xTF32: two chunk accumulators for the hi*hi products plus one for the small cross terms.
+    static constexpr int kTmemCols = kX3 ? (3 * BN <= 256 ? 256 : 512) : 2 * BN;
+    static constexpr int kChunkKb = 8;  // 3xTF32: k-blocks summed inside TMEM before an fp32 drain
+    static constexpr int kNumBars = 3 * STAGES + 5;
     static constexpr int kTailBytes = kNumBars * 8 + 16 + 4 * 256 * 8;
     static constexpr int kSmemBytes = STAGES * kStageBytes + kTailBytes + 1024;
     static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "TMEM columns must be a power of two");
+    static_assert(!kX3 || 3 * BN <= 512, "3xTF32 needs three accumulators in TMEM");
     static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
 };
 
@@ -113,6 +124,33 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     nb = r / gm;
 }
 
+// Writes 32 consecutive output columns [nc, nc+32) of row m held in r[] (raw 32-bit words).
+__device__ __forceinline__ void store_row_chunk(const CoreParams& p, uint32_t* out32, int m, int nc,
+                                                const uint32_t (&r)[32], long long offm, const long long* ntab) {
+    if (nc >= p.N) return;
+    if (p.epi == EPI_ROWMAJOR) {
+        uint32_t* dst = out32 + static_cast<long long>(m) * p.ldo + nc;
+        if (nc + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (nc + j < p.N) dst[j] = r[j];
+        }
+    } else if (p.epi == EPI_COLMAJOR) {
+        uint32_t* dst = out32 + static_cast<long long>(nc) * p.ldo + m;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (nc + j < p.N) dst[static_cast<long long>(j) * p.ldo] = r[j];
+    } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (nc + j < p.N) out32[offm + ntab[j]] = r[j];
+    }
+}
+
 template <int ARITH, int OP, int BN, int STAGES>
 __global__ void __launch_bounds__(CoreCfg<ARITH, OP, BN, STAGES>::kThreads, 1)
 umma_contract_kernel(const __grid_constant__ CoreParams p) {
@@ -126,7 +164,8 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
     uint64_t* empty_bar = ready_bar + STAGES;                // MMAs that read the stage retired
     uint64_t* tfull_bar = empty_bar + STAGES;                // accumulator complete (2)
     uint64_t* tempty_bar = tfull_bar + 2;                    // accumulator drained (2)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+    uint64_t* sempty_bar = tempty_bar + 2;                   // 3xTF32: cross-term accumulator drained
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sempty_bar + 1);
     uint32_t* abort_slot = tmem_slot + 1;
     long long* ntable = reinterpret_cast<long long*>(tmem_slot + 4);  // one 256-entry scatter table per epilogue warp
 
@@ -145,6 +184,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
             ptx::mbar_init(&tfull_bar[a], 1);
             ptx::mbar_init(&tempty_bar[a], 4);
         }
+        ptx::mbar_init(sempty_bar, 4);
         *abort_slot = 0u;
         ptx::fence_mbar_init();
     }
@@ -180,7 +220,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                     if (!bounded_wait(&empty_bar[s], ph ^ 1, ab, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
                     uint8_t* sa = smem + s * Cfg::kStageBytes;
                     uint8_t* sb = sa + Cfg::kABytes;
-                    ptx::mbar_expect_tx(&full_bar[s], Cfg::kABytes + (Cfg::kBGenerated ? 0 : Cfg::kBBytes));
+                    ptx::mbar_expect_tx(&full_bar[s], p.a_tx_bytes + (Cfg::kBGenerated ? 0 : Cfg::kBBytes));
                     if constexpr (OP == OP_GEMM || OP == OP_TTM) {
                         ptx::tma_load_2d(sa, &p.mapA[0], &full_bar[s], kb * AT::kBlockK, m0);
                         if constexpr (OP == OP_TTM) {
@@ -256,53 +296,79 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
             constexpr uint32_t kStepMn = (AT::kUmmaK * 128) >> 4;                          // MN-major: kUmmaK rows
             constexpr uint32_t kStepB = Cfg::kBMnMajor ? kStepMn : kStepK;
             constexpr uint32_t kLboB = Cfg::kBMnMajor ? Cfg::kBoxBytesMn : 16;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
-                const int acc = lt & 1;
-                if (!bounded_wait(&tempty_bar[acc], ((lt >> 1) & 1) ^ 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
-                ptx::tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + acc * BN;
-                const int nkb = kb_count<OP>(p, (OP == OP_MTTKRP) ? t / p.tiles_m : 0);
-                for (int kb = 0; kb < nkb; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
-                    uint64_t* go = Cfg::kX3 ? &ready_bar[s] : &full_bar[s];
-                    if (!bounded_wait(go, ph, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
-                    ptx::tc_fence_after_sync();
-                    const uint32_t sa = ptx::smem_u32(smem + s * Cfg::kStageBytes);
-                    const uint32_t sb = sa + Cfg::kABytes;
-                    const uint64_t da = ptx::make_smem_desc(sa, 16, 1024);
-                    const uint64_t db = ptx::make_smem_desc(sb, kLboB, 1024);
-                    if constexpr (Cfg::kX3) {
-                        const uint64_t dal = ptx::make_smem_desc(sb + Cfg::kBBytes, 16, 1024);
-                        const uint64_t dbl = ptx::make_smem_desc(sb + Cfg::kBBytes + Cfg::kABytes, kLboB, 1024);
+            if constexpr (Cfg::kX3) {
+                int gch = 0;
+                const uint32_t d_small = tmem_base + 2 * BN;
+                for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+                    if (!bounded_wait(sempty_bar, (lt & 1) ^ 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
+                    const int nkb = kb_count<OP>(p, (OP == OP_MTTKRP) ? t / p.tiles_m : 0);
+                    for (int kb0 = 0; kb0 < nkb && ok; kb0 += Cfg::kChunkKb, ++gch) {
+                        const int b = gch & 1;
+                        if (!bounded_wait(&tempty_bar[b], ((gch >> 1) & 1) ^ 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
+                        ptx::tc_fence_after_sync();
+                        const uint32_t d_main = tmem_base + b * BN;
+                        const int kend = min(kb0 + Cfg::kChunkKb, nkb);
+                        for (int kb = kb0; kb < kend; ++kb, ++it) {
+                            const int s = it % STAGES;
+                            const uint32_t ph = (it / STAGES) & 1;
+                            if (!bounded_wait(&ready_bar[s], ph, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
+                            ptx::tc_fence_after_sync();
+                            const uint32_t sa = ptx::smem_u32(smem + s * Cfg::kStageBytes);
+                            const uint32_t sb = sa + Cfg::kABytes;
+                            const uint64_t da = ptx::make_smem_desc(sa, 16, 1024);
+                            const uint64_t db = ptx::make_smem_desc(sb, kLboB, Cfg::kBSbo, Cfg::kBSwizzle);
+                            const uint64_t dal = ptx::make_smem_desc(sb + Cfg::kBBytes, 16, 1024);
+                            const uint64_t dbl =
+                                ptx::make_smem_desc(sb + Cfg::kBBytes + Cfg::kABytes, kLboB, Cfg::kBSbo, Cfg::kBSwizzle);
 #pragma unroll
-                        for (int j = 0; j < AT::kBlockK / AT::kUmmaK; ++j) {
-                            const uint32_t first = (kb | j) ? 1u : 0u;
-                            ptx::umma<AT::kKind, 1>(d_tmem, dal + j * kStepK, db + j * kStepB, p.idesc, first);
-                            ptx::umma<AT::kKind, 1>(d_tmem, da + j * kStepK, dbl + j * kStepB, p.idesc, 1u);
-                            ptx::umma<AT::kKind, 1>(d_tmem, da + j * kStepK, db + j * kStepB, p.idesc, 1u);
+                            for (int j = 0; j < AT::kBlockK / AT::kUmmaK; ++j) {
+                                ptx::umma<AT::kKind, 1>(d_small, dal + j * kStepK, db + j * kStepB, p.idesc,
+                                                        (kb | j) ? 1u : 0u);
+                                ptx::umma<AT::kKind, 1>(d_small, da + j * kStepK, dbl + j * kStepB, p.idesc, 1u);
+                                ptx::umma<AT::kKind, 1>(d_main, da + j * kStepK, db + j * kStepB, p.idesc,
+                                                        ((kb - kb0) | j) ? 1u : 0u);
+                            }
+                            ptx::umma_commit(&empty_bar[s]);
                         }
-                    } else {
+                        if (ok) ptx::umma_commit(&tfull_bar[b]);
+                    }
+                }
+            } else {
+                for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
+                    const int acc = lt & 1;
+                    if (!bounded_wait(&tempty_bar[acc], ((lt >> 1) & 1) ^ 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t d_tmem = tmem_base + acc * BN;
+                    const int nkb = kb_count<OP>(p, 0);
+                    for (int kb = 0; kb < nkb; ++kb, ++it) {
+                        const int s = it % STAGES;
+                        const uint32_t ph = (it / STAGES) & 1;
+                        if (!bounded_wait(&full_bar[s], ph, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
+                        ptx::tc_fence_after_sync();
+                        const uint32_t sa = ptx::smem_u32(smem + s * Cfg::kStageBytes);
+                        const uint32_t sb = sa + Cfg::kABytes;
+                        const uint64_t da = ptx::make_smem_desc(sa, 16, 1024);
+                        const uint64_t db = ptx::make_smem_desc(sb, kLboB, Cfg::kBSbo, Cfg::kBSwizzle);
 #pragma unroll
                         for (int j = 0; j < AT::kBlockK / AT::kUmmaK; ++j)
                             ptx::umma<AT::kKind, 1>(d_tmem, da + j * kStepK, db + j * kStepB, p.idesc,
                                                     (kb | j) ? 1u : 0u);
+                        ptx::umma_commit(&empty_bar[s]);
                     }
-                    ptx::umma_commit(&empty_bar[s]);
+                    if (ok) ptx::umma_commit(&tfull_bar[acc]);
                 }
-                if (ok) ptx::umma_commit(&tfull_bar[acc]);
             }
         }
     } else if (warp < 6) {
         // ------------------------------------------------------------ epilogue (TMEM -> global)
         const int q = warp & 3;  // TMEM lane quarter this warp may read
-        int lt = 0;
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+        int lt = 0, gch = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
             int mb, nb;
             if constexpr (OP == OP_MTTKRP) { mb = t % p.tiles_m; nb = t / p.tiles_m; }
             else tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
-            const int acc = lt & 1;
             const int row = q * 32 + lane;
             const int m = mb * p.tile_rows + row;
             const int n0 = (OP == OP_MTTKRP) ? 0 : nb * BN;
@@ -314,43 +380,65 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                 offm = digits_offset(p.dm, m);
                 __syncwarp();
             }
-            if (!bounded_wait_warp(&tfull_bar[acc], (lt >> 1) & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
-            ptx::tc_fence_after_sync();
             uint32_t* out32 = reinterpret_cast<uint32_t*>(p.out);
             if constexpr (OP == OP_MTTKRP) out32 += static_cast<long long>(nb) * p.M * p.N;  // partial slab of this split
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, r);
-                ptx::tmem_ld_wait();
-                const int nc = n0 + c * 32;
-                if (row < p.tile_rows && m < p.M && nc < p.N) {
-                    if (p.epi == EPI_ROWMAJOR) {
-                        uint32_t* dst = out32 + static_cast<long long>(m) * p.ldo + nc;
-                        if (nc + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+            const bool row_ok = row < p.tile_rows && m < p.M;
+            if constexpr (Cfg::kX3) {
+                float sum[BN];
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<uint4*>(dst + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-                        } else {
+                for (int j = 0; j < BN; ++j) sum[j] = 0.f;
+                const int nkb = kb_count<OP>(p, nb);
+                for (int kb0 = 0; kb0 < nkb && ok; kb0 += Cfg::kChunkKb, ++gch) {
+                    const int b = gch & 1;
+                    if (!bounded_wait_warp(&tfull_bar[b], (gch >> 1) & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
+                    ptx::tc_fence_after_sync();
 #pragma unroll
-                            for (int j = 0; j < 32; ++j)
-                                if (nc + j < p.N) dst[j] = r[j];
-                        }
-                    } else if (p.epi == EPI_COLMAJOR) {
-                        uint32_t* dst = out32 + static_cast<long long>(nc) * p.ldo + m;
+                    for (int c = 0; c < BN / 16; ++c) {
+                        uint32_t r[16];
+                        ptx::tmem_ld_32x16(lane_base + b * BN + c * 16, r);
+                        ptx::tmem_ld_wait();
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (nc + j < p.N) dst[static_cast<long long>(j) * p.ldo] = r[j];
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (nc + j < p.N) out32[offm + ntab[c * 32 + j]] = r[j];
+                        for (int j = 0; j < 16; ++j) sum[c * 16 + j] += __uint_as_float(r[j]);
                     }
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(&tempty_bar[b]);
                 }
+                if (!ok) break;
+                // The last chunk's commit also covers every cross-term MMA of this tile.
+#pragma unroll
+                for (int c = 0; c < BN / 16; ++c) {
+                    uint32_t r[16];
+                    ptx::tmem_ld_32x16(lane_base + 2 * BN + c * 16, r);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) sum[c * 16 + j] += __uint_as_float(r[j]);
+                }
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(sempty_bar);
+#pragma unroll
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sum[c * 32 + j]);
+                    if (row_ok) store_row_chunk(p, out32, m, n0 + c * 32, r, offm, ntab + c * 32);
+                }
+            } else {
+                const int acc = lt & 1;
+                if (!bounded_wait_warp(&tfull_bar[acc], (lt >> 1) & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
+                ptx::tc_fence_after_sync();
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32(lane_base + acc * BN + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    if (row_ok) store_row_chunk(p, out32, m, n0 + c * 32, r, offm, ntab + c * 32);
+                }
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&tempty_bar[acc]);
             }
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&tempty_bar[acc]);
         }
     } else {
         // ------------------------------------------------------------ 3xTF32 splitter (and MTTKRP B generator)

@@ -56,6 +56,7 @@ struct CoreParams {
     CUtensorMap mapB;
     int M, N;         // GEMM-view extents of the output
     int tile_rows;    // output rows per tile (128 unless the row boxes cannot fill a tile)
+    int a_tx_bytes;   // bytes the A-operand TMA boxes of one stage deliver (tile_rows * 128, or 16384)
     int num_kb;       // k-blocks per output tile (per split for MTTKRP)
     int total_kb;     // MTTKRP: k-blocks over all splits (the last split may get fewer)
     int tiles_m, tiles_n;

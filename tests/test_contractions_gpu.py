@@ -1,0 +1,94 @@
+"""TTM and MTTKRP parity on the GPU through the C ABI against the CPU oracle."""
+import numpy as np
+import pytest
+
+import t2sp_b200
+from t2sp_b200 import Buffer
+from tests import oracle_lib as O
+from tests.util import TOL_FP32, componentwise, normwise
+
+pytestmark = pytest.mark.gpu
+
+
+def run_ttm(a, b, tiled=None):
+    J, I, L = a.shape
+    K = b.shape[0]
+    if tiled is None:
+        c = np.full((K, J, I), np.nan, np.float32)
+    else:
+        JJ, KK, II, KKK, JJJ, III = tiled
+        c = np.full((I // (III * II), J // (JJJ * JJ), K // (KKK * KK), III, JJJ, KKK, II, KK, JJ), np.nan, np.float32)
+    cb = Buffer.from_numpy(c)
+    rc = t2sp_b200.ttm(Buffer.from_numpy(a), Buffer.from_numpy(b), cb)
+    return rc, cb.keepalive
+
+
+def test_ttm_known_answer(lib):
+    # SEQUENTIAL fixtures of t2s/tests/correctness/buffer/tmm_small.cpp:131-132 at its 8x8x8x8
+    # size: a(l,i,j) = l + i + j, b(l,k) = l + k + 1 (util.h:52-65,100-114); exact integers.
+    L = I = J = K = 8
+    l = np.arange(L)
+    a = (np.arange(J)[:, None, None] + np.arange(I)[None, :, None] + l[None, None, :]).astype(np.float32)
+    b = (np.arange(K)[:, None] + l[None, :] + 1).astype(np.float32)
+    rc, c = run_ttm(a, b)
+    assert rc == 0
+    ref = np.einsum("jil,kl->kji", a.astype(np.float64), b.astype(np.float64))
+    assert np.array_equal(c, ref.astype(np.float32))
+    # and the 9-D device layout of the same test (tmm_small.cpp:116-129), all tile extents 2
+    rc, c9 = run_ttm(a, b, tiled=(2, 2, 2, 2, 2, 2))
+    assert rc == 0
+    assert np.array_equal(c9, O.ttm_tile_layout(ref.astype(np.float32), 2, 2, 2, 2, 2, 2))
+
+
+@pytest.mark.parametrize("L,I,J,K", [(256, 64, 48, 256), (100, 24, 10, 72), (64, 128, 128, 64)])
+def test_ttm_random(lib, L, I, J, K):
+    a = O.uniform(0, 1, (J, I, L))
+    b = O.uniform(0, 2, (K, L))
+    rc, c = run_ttm(a, b)
+    assert rc == 0
+    assert not np.isnan(c).any()
+    truth = O.ttm_f32(a, b, acc64=True)
+    absprod = O.ttm_f32(np.abs(a), np.abs(b), acc64=True)
+    print(f"ttm L{L} I{I} J{J} K{K}: normwise {normwise(c, truth):.3e} componentwise {componentwise(c, truth, absprod):.3e}")
+    assert normwise(c, truth) <= TOL_FP32 and componentwise(c, truth, absprod) <= TOL_FP32
+    assert normwise(c, O.ttm_f32(a, b)) <= TOL_FP32
+
+
+def run_mttkrp(a, b, c, splits=0):
+    K, I, L = a.shape
+    R = b.shape[0]
+    d = np.full((R, I), np.nan, np.float32)
+    db = Buffer.from_numpy(d)
+    desc = t2sp_b200.MttkrpDesc(0, splits)
+    rc = t2sp_b200.mttkrp(Buffer.from_numpy(a), Buffer.from_numpy(b), Buffer.from_numpy(c), db, desc)
+    return rc, db.keepalive
+
+
+def test_mttkrp_known_answer(lib):
+    # SEQUENTIAL-style integer data: exact under any association of the sums.
+    L, I, K, R = 8, 8, 8, 8
+    a = (np.arange(K)[:, None, None] + np.arange(I)[None, :, None] + np.arange(L)[None, None, :]).astype(np.float32)
+    b = (np.arange(R)[:, None] + np.arange(K)[None, :] + 1).astype(np.float32)
+    c = (np.arange(R)[:, None] + np.arange(L)[None, :] + 1).astype(np.float32)
+    rc, d = run_mttkrp(a, b, c)
+    assert rc == 0
+    ref = np.einsum("kil,rl,rk->ri", a.astype(np.float64), c.astype(np.float64), b.astype(np.float64))
+    assert np.array_equal(d, ref.astype(np.float32))
+
+
+@pytest.mark.parametrize("L,I,K,R,splits", [(64, 128, 32, 64, 0), (96, 200, 17, 40, 5), (128, 256, 64, 64, 1), (32, 64, 8, 128, 3)])
+def test_mttkrp_random(lib, L, I, K, R, splits):
+    a = O.uniform(0, 1, (K, I, L))
+    b = O.uniform(0, 2, (R, K))
+    c = O.uniform(0, 3, (R, L))
+    rc, d = run_mttkrp(a, b, c, splits)
+    assert rc == 0
+    assert not np.isnan(d).any()
+    truth = O.mttkrp_f32(a, b, c, acc64=True)
+    absprod = O.mttkrp_f32(np.abs(a), np.abs(b), np.abs(c), acc64=True)
+    print(f"mttkrp L{L} I{I} K{K} R{R}: normwise {normwise(d, truth):.3e} componentwise {componentwise(d, truth, absprod):.3e}")
+    assert normwise(d, truth) <= TOL_FP32 and componentwise(d, truth, absprod) <= TOL_FP32
+    assert normwise(d, O.mttkrp_f32(a, b, c)) <= TOL_FP32
+    # deterministic: the split partial sums are added in a fixed order
+    rc2, d2 = run_mttkrp(a, b, c, splits)
+    assert rc2 == 0 and np.array_equal(d, d2)

@@ -1,0 +1,143 @@
+"""2-D convolution and capsule convolution parity on the GPU through the C ABI against the
+CPU oracle, at the reference's TINY and GPU design constants
+(t2s/tests/performance/{conv,capsule}/const-parameters.h) and at scaled-down BASELINE shapes."""
+import numpy as np
+import pytest
+
+import t2sp_b200
+from t2sp_b200 import Buffer, CapsuleDesc, ConvDesc
+from tests import oracle_lib as O
+from tests.util import TOL_FP32, componentwise, normwise
+
+pytestmark = pytest.mark.gpu
+
+
+def conv_inputs(seed, N, CI, CO, KY, KX, OY, OX):
+    IY, IX = OY + KY - 1, OX + KX - 1
+    I2 = O.uniform(seed, 1, (IY * IX, CI * N))
+    K2 = O.normal(seed, 2, (CI * KY, CO * KX), (1.0 / (KY * KX * CI)) ** 0.5)
+    return I2, K2
+
+
+def run_conv(I2, K2, N, CI, CO, KY, KX, OY, OX, tiles=None):
+    d = ConvDesc()
+    d.CI, d.CO, d.KY, d.KX, d.OY, d.OX = CI, CO, KY, KX, OY, OX
+    if tiles is None:
+        out = np.full((OY * OX, CO * N), np.nan, np.float32)
+    else:
+        COOO, YYY, XXX, COO, YY, XX, Y, X = tiles
+        d.layout = 1
+        d.COOO, d.YYY, d.XXX, d.COO, d.YY, d.XX, d.Y, d.X = tiles
+        out = np.full((N, CO // (COOO * COO), X, Y, XX, YY, COO, XXX, YYY, COOO), np.nan, np.float32)
+    ob = Buffer.from_numpy(out)
+    rc = t2sp_b200.conv(Buffer.from_numpy(I2), Buffer.from_numpy(K2), ob, d)
+    return rc, ob.keepalive
+
+
+CONV_CASES = [
+    # N, CI, CO, KY, KX, OY, OX
+    (4, 16, 64, 3, 3, 4, 4),      # TINY constants (CII*CI = 16, COOO*COO*CO = 64, 4x4 output)
+    (8, 64, 128, 3, 3, 14, 14),   # BASELINE config 2 scaled down in batch and channels
+    (64, 32, 64, 3, 3, 6, 4),     # batch 64: one TMA box = 64 images x 2 rows
+    (3, 40, 72, 3, 2, 5, 7),      # ragged: channel counts not multiples of the tile sizes
+    (2, 32, 32, 1, 1, 8, 8),      # 1x1 filter
+]
+
+
+@pytest.mark.parametrize("N,CI,CO,KY,KX,OY,OX", CONV_CASES)
+def test_conv_plain(lib, N, CI, CO, KY, KX, OY, OX):
+    I2, K2 = conv_inputs(0, N, CI, CO, KY, KX, OY, OX)
+    rc, out = run_conv(I2, K2, N, CI, CO, KY, KX, OY, OX)
+    assert rc == 0
+    assert not np.isnan(out).any(), "unwritten output elements"
+    truth = O.conv_f32(I2, K2, N, CI, CO, KY, KX, OY, OX, acc64=True)
+    absprod = O.conv_f32(np.abs(I2), np.abs(K2), N, CI, CO, KY, KX, OY, OX, acc64=True)
+    print(f"conv N{N} CI{CI} CO{CO} {KY}x{KX} {OY}x{OX}: normwise {normwise(out, truth):.3e} componentwise {componentwise(out, truth, absprod):.3e}")
+    assert normwise(out, truth) <= TOL_FP32 and componentwise(out, truth, absprod) <= TOL_FP32
+    assert normwise(out, O.conv_f32(I2, K2, N, CI, CO, KY, KX, OY, OX, CII=min(CI, 8) if CI % 8 == 0 else 0)) <= TOL_FP32
+
+
+def test_conv_tiled_output_tiny(lib):
+    # 10-D output of conv-run-fpga.cpp:68 with the TINY constants (const-parameters.h:38-49)
+    N, CI, CO, KY, KX, OY, OX = 4, 16, 64, 3, 3, 4, 4
+    tiles = (4, 4, 4, 4, 1, 1, 1, 1)
+    I2, K2 = conv_inputs(1, N, CI, CO, KY, KX, OY, OX)
+    rc, out = run_conv(I2, K2, N, CI, CO, KY, KX, OY, OX, tiles)
+    assert rc == 0 and not np.isnan(out).any()
+    truth = O.conv_f32(I2, K2, N, CI, CO, KY, KX, OY, OX, acc64=True)
+    ref10 = O.conv_tile_layout(truth, N, 4, 4, 4, 4, 1, 1, 1, 1, 4)
+    assert normwise(out, ref10) <= TOL_FP32
+
+
+def test_conv_tiled_output_general(lib):
+    # every tile extent > 1 so each digit of the 10-D address map is exercised
+    N, CI, CO, KY, KX = 2, 32, 32, 3, 3
+    COOO, YYY, XXX, COO, YY, XX, Y, X = 4, 2, 3, 2, 2, 2, 3, 2
+    OY, OX = YYY * YY * Y, XXX * XX * X
+    I2, K2 = conv_inputs(2, N, CI, CO, KY, KX, OY, OX)
+    rc, out = run_conv(I2, K2, N, CI, CO, KY, KX, OY, OX, (COOO, YYY, XXX, COO, YY, XX, Y, X))
+    assert rc == 0 and not np.isnan(out).any()
+    truth = O.conv_f32(I2, K2, N, CI, CO, KY, KX, OY, OX, acc64=True)
+    ref10 = O.conv_tile_layout(truth, N, COOO, YYY, XXX, COO, YY, XX, Y, X, CO // (COOO * COO))
+    assert normwise(out, ref10) <= TOL_FP32
+
+
+def capsule_inputs(seed, N, NN, CI, CO, KY, KX, OY, OX, MY, MX, MK, s):
+    IY, IX = s * OY + KY - s, s * OX + KX - s
+    P2 = O.normal(seed, 1, (IY * IX * N, CI * MK * MX * NN), 0.1)
+    W2 = O.normal(seed, 2, (CI * KY * KX * MK, CO * MY), 0.1)
+    return P2, W2
+
+
+def run_capsule(P2, W2, N, NN, CI, CII, CO, KY, KX, OY, OX, s, tiles=None, M=4):
+    d = CapsuleDesc()
+    d.CI, d.CII, d.CO, d.KY, d.KX, d.OY, d.OX = CI, CII, CO, KY, KX, OY, OX
+    d.MY = d.MX = d.MK = M
+    d.NN, d.stride = NN, s
+    if tiles is None:
+        out = np.full((OY * OX * N, CO * M * M * NN), np.nan, np.float32)
+    else:
+        COOO, YYY_XXX, YY_XX, Y_X, COO = tiles
+        d.layout = 1
+        d.COOO, d.YYY_XXX, d.YY_XX, d.Y_X, d.COO = tiles
+        out = np.full((N, CO // (COOO * COO), NN, COO, M, M, Y_X, YY_XX, YYY_XXX, COOO), np.nan, np.float32)
+    ob = Buffer.from_numpy(out)
+    rc = t2sp_b200.capsule(Buffer.from_numpy(P2), Buffer.from_numpy(W2), ob, d)
+    return rc, ob.keepalive
+
+
+CAPSULE_CASES = [
+    # N, NN, CI, CII, CO, KY, KX, OY, OX, stride
+    (4, 1, 16, 4, 16, 3, 3, 7, 7, 2),    # TINY constants (capsule/const-parameters.h:46-55)
+    (2, 16, 32, 4, 32, 3, 3, 7, 7, 2),   # GPU constants with a smaller batch
+    (2, 4, 32, 32, 32, 3, 3, 8, 8, 1),   # BASELINE config 4 (stride 1) scaled down
+    (2, 4, 32, 16, 32, 3, 3, 7, 7, 2),   # A10 constants (CII 16)
+    (1, 2, 16, 4, 8, 2, 3, 3, 5, 1),     # ragged spatial extents, non-square filter
+]
+
+
+@pytest.mark.parametrize("N,NN,CI,CII,CO,KY,KX,OY,OX,s", CAPSULE_CASES)
+def test_capsule_plain(lib, N, NN, CI, CII, CO, KY, KX, OY, OX, s):
+    P2, W2 = capsule_inputs(0, N, NN, CI, CO, KY, KX, OY, OX, 4, 4, 4, s)
+    rc, out = run_capsule(P2, W2, N, NN, CI, CII, CO, KY, KX, OY, OX, s)
+    assert rc == 0
+    assert not np.isnan(out).any(), "unwritten output elements"
+    truth = O.capsule_f32(P2, W2, N, NN, CI, CII, CO, KY, KX, OY, OX, 4, 4, 4, s, acc64=True)
+    absprod = O.capsule_f32(np.abs(P2), np.abs(W2), N, NN, CI, CII, CO, KY, KX, OY, OX, 4, 4, 4, s, acc64=True)
+    print(f"capsule N{N} NN{NN} CI{CI}/{CII} CO{CO} s{s}: normwise {normwise(out, truth):.3e} componentwise {componentwise(out, truth, absprod):.3e}")
+    assert normwise(out, truth) <= TOL_FP32 and componentwise(out, truth, absprod) <= TOL_FP32
+    assert normwise(out, O.capsule_f32(P2, W2, N, NN, CI, CII, CO, KY, KX, OY, OX, 4, 4, 4, s)) <= TOL_FP32
+
+
+@pytest.mark.parametrize("tiles,NN,CI,CII,CO", [((4, 7, 1, 7, 4), 1, 16, 4, 16), ((8, 10, 1, 5, 4), 4, 32, 16, 32)])
+def test_capsule_tiled_output(lib, tiles, NN, CI, CII, CO):
+    # 10-D output of capsule-run-fpga.cpp:73: TINY constants, and the A10 constants whose
+    # 10*1*5 = 50 pixel slots exceed the 49 pixels (slot 49 must be written as 0).
+    N, KY, KX, OY, OX, s = 2, 3, 3, 7, 7, 2
+    P2, W2 = capsule_inputs(3, N, NN, CI, CO, KY, KX, OY, OX, 4, 4, 4, s)
+    rc, out = run_capsule(P2, W2, N, NN, CI, CII, CO, KY, KX, OY, OX, s, tiles)
+    assert rc == 0 and not np.isnan(out).any()
+    truth = O.capsule_f32(P2, W2, N, NN, CI, CII, CO, KY, KX, OY, OX, 4, 4, 4, s, acc64=True)
+    COOO, YYY_XXX, YY_XX, Y_X, COO = tiles
+    ref10 = O.capsule_tile_layout(truth, N, NN, COOO, COO, CO // (COOO * COO), YYY_XXX, YY_XX, Y_X, 4, 4, OY, OX)
+    assert normwise(out, ref10) <= TOL_FP32

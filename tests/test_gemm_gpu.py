@@ -1,0 +1,141 @@
+"""GEMM parity on the GPU through the C ABI (host buffers in, host buffers out) against the CPU
+oracle: known-answer cases with the reference's deterministic fixtures, seeded random cases for
+every arithmetic, ragged sizes, and the tiled 6-D output layout of the FPGA drivers."""
+import numpy as np
+import pytest
+
+from tests import oracle_lib as O
+from tests.util import TOL_BF16, TOL_FP32, call_gemm, componentwise, normwise
+
+pytestmark = pytest.mark.gpu
+
+
+def test_bf16_known_answer_single_tile(lib):
+    # ina(k,i) = k + i, inb(j,k) = j - k pattern of t2s/tests/correctness/aot/gemm-run.cpp:50-59,
+    # reduced mod 8 so every product and partial sum is an integer that bf16/fp32 hold exactly.
+    M, N, K = 128, 256, 64
+    i, k, j = np.arange(M)[:, None], np.arange(K)[None, :], np.arange(N)[None, :]
+    A = ((k + i) % 8).astype(np.float32)
+    B = ((j - np.arange(K)[:, None]) % 8 - 4).astype(np.float32)
+    rc, C = call_gemm(O.to_bf16(A), O.to_bf16(B), "bf16")
+    assert rc == 0
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    bad = np.argwhere(C != ref)
+    assert bad.size == 0, f"{len(bad)} mismatches, first {bad[:5].tolist()} got {C[tuple(bad[0])]} want {ref[tuple(bad[0])]}"
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 512), (256, 512, 1024), (200, 136, 72), (1024, 1024, 1024)])
+def test_bf16_random(lib, M, N, K):
+    A = O.to_bf16(O.uniform(0, 1, (M, K)))
+    B = O.to_bf16(O.uniform(0, 2, (K, N)))
+    rc, C = call_gemm(A, B, "bf16")
+    assert rc == 0
+    truth = O.gemm_h16(A, B, 0, acc64=True)
+    err = normwise(C, truth)
+    spec = normwise(O.gemm_h16(A, B, 0), truth)
+    print(f"bf16 {M}x{N}x{K}: kernel vs truth {err:.3e}; spec-order oracle vs truth {spec:.3e}")
+    assert err <= TOL_BF16
+    absprod = O.gemm_f32(np.abs(O.bf16_to_f32(A)), np.abs(O.bf16_to_f32(B)), acc64=True)
+    assert componentwise(C, truth, absprod) <= TOL_BF16
+
+
+def test_f16_random(lib):
+    M, N, K = 256, 256, 256
+    A = O.uniform(3, 1, (M, K)).astype(np.float16)
+    B = O.uniform(3, 2, (K, N)).astype(np.float16)
+    rc, C = call_gemm(A, B, "f16")
+    assert rc == 0
+    truth = O.gemm_h16(A.view(np.uint16), B.view(np.uint16), 1, acc64=True)
+    assert normwise(C, truth) <= TOL_BF16
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (256, 512, 1024), (136, 144, 80), (1024, 1024, 2048)])
+def test_int8_bit_exact(lib, M, N, K):
+    A = O.int8(1, 1, (M, K))
+    B = O.int8(1, 2, (K, N))
+    rc, C = call_gemm(A, B, "i8", out_dtype=np.int32)
+    assert rc == 0
+    ref = O.gemm_i8(A, B)
+    bad = np.argwhere(C != ref)
+    assert bad.size == 0, f"{len(bad)} mismatches, first {bad[:5].tolist()}"
+
+
+def test_fp32_known_answer(lib):
+    # SEQUENTIAL fixture of t2s/tests/correctness/util/util.h:52-65 (value i + j + 1): integers,
+    # so the 3xTF32 product must be exact.
+    M, N, K = 64, 64, 64
+    A = (np.arange(M)[:, None] + np.arange(K)[None, :] + 1).astype(np.float32)
+    B = (np.arange(K)[:, None] + np.arange(N)[None, :] + 1).astype(np.float32)
+    rc, C = call_gemm(A, B, "f32")
+    assert rc == 0
+    ref = (A.astype(np.float64) @ B.astype(np.float64)).astype(np.float32)
+    assert np.array_equal(C, ref)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (1024, 1024, 1024), (100, 68, 36)])
+def test_fp32_random(lib, M, N, K):
+    A = O.uniform(2, 1, (M, K))
+    B = O.uniform(2, 2, (K, N))
+    rc, C = call_gemm(A, B, "f32")
+    assert rc == 0
+    truth = O.gemm_f32(A, B, acc64=True)
+    absprod = O.gemm_f32(np.abs(A), np.abs(B), acc64=True)
+    spec_c = O.gemm_f32(A, B)
+    err, cw = normwise(C, truth), componentwise(C, truth, absprod)
+    print(f"fp32 {M}x{N}x{K}: kernel vs truth normwise {err:.3e} componentwise {cw:.3e}; "
+          f"spec-order oracle vs truth {normwise(spec_c, truth):.3e} / {componentwise(spec_c, truth, absprod):.3e}; "
+          f"kernel vs spec-order oracle {normwise(C, spec_c):.3e}")
+    assert err <= TOL_FP32 and cw <= TOL_FP32
+    assert normwise(C, spec_c) <= TOL_FP32
+
+
+def test_fp32_positive_inputs_strict(lib):
+    # The reference drivers fill inputs with non-negative random() values
+    # (gemm-run-fpga.cpp:60,65), where the strict elementwise relative error is well behaved.
+    M, N, K = 256, 256, 512
+    A = np.abs(O.uniform(4, 1, (M, K))) * 1000.0
+    B = np.abs(O.uniform(4, 2, (K, N))) * 1000.0
+    rc, C = call_gemm(A, B, "f32")
+    assert rc == 0
+    truth = O.gemm_f32(A, B, acc64=True)
+    assert O.rel_err(C, truth, 0.0) <= TOL_FP32
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_tiled_output_layout(lib, dtype):
+    # 6-D output c(JJJ,III,JJ,II,J,I) of the FPGA driver (gemm-run-fpga.cpp:69), GPU-variant
+    # tile extents (const-parameters.h:24-29) on a 256 x 256 x 128 problem.
+    JJJ, III, JJ, II = 8, 16, 2, 4
+    M, N, K = III * II * 4, JJJ * JJ * 16, 128
+    A = O.uniform(5, 1, (M, K))
+    B = O.uniform(5, 2, (K, N))
+    if dtype == "bf16":
+        Ab, Bb = O.to_bf16(A), O.to_bf16(B)
+        rc, C6 = call_gemm(Ab, Bb, "bf16", tiled=(JJJ, III, JJ, II))
+        plain = O.gemm_h16(Ab, Bb, 0, acc64=True)
+    else:
+        rc, C6 = call_gemm(A, B, "f32", tiled=(JJJ, III, JJ, II))
+        plain = O.gemm_f32(A, B, acc64=True)
+    assert rc == 0
+    ref6 = O.gemm_tile_layout(plain, JJJ, III, JJ, II)
+    assert not np.isnan(C6).any(), "some tiled output elements were never written"
+    assert normwise(C6, ref6) <= (TOL_BF16 if dtype == "bf16" else TOL_FP32)
+
+
+def test_repeatable_and_deterministic(lib):
+    M, N, K = 256, 256, 256
+    A = O.to_bf16(O.uniform(6, 1, (M, K)))
+    B = O.to_bf16(O.uniform(6, 2, (K, N)))
+    rc1, C1 = call_gemm(A, B, "bf16")
+    rc2, C2 = call_gemm(A, B, "bf16")
+    assert rc1 == 0 and rc2 == 0
+    assert np.array_equal(C1, C2)
+
+
+def test_empty_contraction_and_empty_output(lib):
+    A = np.zeros((64, 0), np.float32)
+    B = np.zeros((0, 64), np.float32)
+    rc, C = call_gemm(A, B, "f32")
+    assert rc == 0 and np.array_equal(C, np.zeros((64, 64), np.float32))
+    rc, C = call_gemm(np.zeros((0, 32), np.float32), np.zeros((32, 64), np.float32), "f32")
+    assert rc == 0 and C.size == 0
