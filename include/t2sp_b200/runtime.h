@@ -134,6 +134,29 @@ typedef struct t2sp_mttkrp_desc {
 int t2sp_b200_mttkrp(halide_buffer_t *a, halide_buffer_t *b, halide_buffer_t *c, halide_buffer_t *d,
                      const t2sp_mttkrp_desc *desc);
 
+/* ---- MTTKRP without any allocation ---------------------------------------------------
+ * No counterpart in the reference (its runtime allocates per call,
+ * syrk-interface.cpp:951-966). For callers that must not allocate device memory while they
+ * run: services with a fixed memory pool, loops that cannot take cudaMalloc's implicit device
+ * synchronisation, code under a framework allocator that owns all of HBM.
+ * Same contraction and layouts as t2sp_b200_mttkrp, but every pointer is a CUDA device
+ * pointer (element strides given explicitly, innermost stride 1), and the split partial
+ * sums use a fixed array of T2SP_B200_NOALLOC_SCRATCH_BYTES inside the loaded module instead
+ * of the library's allocator. The call performs no cudaMalloc/cudaFree and no host staging.
+ *  - limit: 4*I*R bytes (one partial slab) must fit in the array, else
+ *    halide_error_code_buffer_allocation_too_large; R <= 128; `a` 16-byte aligned with
+ *    strides that are multiples of 4 elements.
+ *  - every GPU that loads the library holds the array until the process exits; all calls on
+ *    a device share it (contents of the previous call remain; nothing has to be cleared
+ *    because each split rewrites its slab), so calls that overlap on the GPU race.
+ *  - the first call on each device looks up the array's address; make it outside stream capture.
+ *  - sync != 0: waits for `cuda_stream` and returns the kernels' status; sync == 0: returns
+ *    after enqueueing on `cuda_stream` (NULL = default stream).                            */
+#define T2SP_B200_NOALLOC_SCRATCH_BYTES (16u << 20)
+int t2sp_b200_mttkrp_noalloc(const float *a, int64_t a_stride_i, int64_t a_stride_k, const float *b,
+                             int64_t b_stride_r, const float *c, int64_t c_stride_r, float *d, int64_t d_stride_r,
+                             int32_t L, int32_t I, int32_t K, int32_t R, void *cuda_stream, int32_t sync);
+
 /* ---- device residency --------------------------------------------------------------
  * Counterpart of halide_device_malloc / halide_copy_to_device / halide_copy_to_host /
  * halide_device_free in t2s/src/AOT-OpenCL-Runtime.cpp:74-117,402-441, and of

@@ -67,6 +67,9 @@ def lib():
                      "t2sp_b200_copy_to_host", "t2sp_b200_detach_device_ptr"):
             getattr(L, name).argtypes = [P]
             getattr(L, name).restype = ctypes.c_int
+        i64, i32 = ctypes.c_int64, ctypes.c_int32
+        L.t2sp_b200_mttkrp_noalloc.argtypes = [P, i64, i64, P, i64, P, i64, P, i64, i32, i32, i32, i32, P, i32]
+        L.t2sp_b200_mttkrp_noalloc.restype = ctypes.c_int
         L.t2sp_b200_wrap_device_ptr.argtypes = [P, ctypes.c_uint64]
         L.t2sp_b200_wrap_device_ptr.restype = ctypes.c_int
         L.t2sp_b200_device_interface.restype = P
