@@ -1,0 +1,35 @@
+#!/bin/bash
+# Compiles the reference's UNMODIFIED host drivers, where they lie in the mounted reference tree,
+#  (1) against the CPU oracle exposed under the interface symbols -> oracle/_ref/pin_*   (pins the oracle)
+#  (2) against the per-design stubs + libt2sp_b200.so            -> tests/_bin/*         (GPU acceptance tests)
+# No reference source is copied; only binaries are written, and both output folders are git-ignored.
+set -e
+HERE="$(cd "$(dirname "$0")" && pwd)"
+ROOT="$(dirname "$HERE")"
+REF="${T2SP_REFERENCE:-/root/reference}"
+PERF="$REF/t2s/tests/performance"
+HAL="$REF/Halide/src/runtime"
+CXX="${CXX:-g++}"
+FLAGS="-O2 -std=c++17 -w -I $ROOT/include -I $HAL -I $REF/t2s/src"
+mkdir -p "$HERE/_ref" "$ROOT/tests/_bin"
+[ -d "$PERF" ] || { echo "reference tree not mounted at $REF"; exit 0; }
+
+ORACLE_SRC="$HERE/oracle.cpp"
+OFLAGS="-O3 -march=x86-64-v3 -ffp-contract=off -pthread"
+
+# (1) oracle pins, CPU only
+$CXX $FLAGS $OFLAGS -DTINY -DREF_GEMM    -I $PERF/gemm    $PERF/gemm/gemm-run-fpga.cpp       $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_gemm_tiny
+$CXX $FLAGS $OFLAGS -DTINY -DREF_CONV    -I $PERF/conv    $PERF/conv/conv-run-fpga.cpp       $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_conv_tiny
+$CXX $FLAGS $OFLAGS -DTINY -DREF_CAPSULE -I $PERF/capsule $PERF/capsule/capsule-run-fpga.cpp $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_capsule_tiny
+$CXX $FLAGS $OFLAGS -DREF_AOT_GEMM $REF/t2s/tests/correctness/aot/gemm-run.cpp $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_aot_gemm
+
+# (2) the same drivers against the product
+LINK="-L $ROOT/t2sp_b200 -lt2sp_b200 -Wl,-rpath,\$ORIGIN/../../t2sp_b200"
+STUBS="$ROOT/t2sp_b200/csrc/stubs"
+if [ -f "$ROOT/t2sp_b200/libt2sp_b200.so" ]; then
+  $CXX $FLAGS -DTINY -I $PERF/gemm    $PERF/gemm/gemm-run-fpga.cpp       $STUBS/gemm-interface.cpp    $LINK -o $ROOT/tests/_bin/gemm_tiny
+  $CXX $FLAGS -DTINY -I $PERF/conv    $PERF/conv/conv-run-fpga.cpp       $STUBS/conv-interface.cpp    $LINK -o $ROOT/tests/_bin/conv_tiny
+  $CXX $FLAGS -DTINY -I $PERF/capsule $PERF/capsule/capsule-run-fpga.cpp $STUBS/capsule-interface.cpp $LINK -o $ROOT/tests/_bin/capsule_tiny
+  $CXX $FLAGS $REF/t2s/tests/correctness/aot/gemm-run.cpp $STUBS/host.cpp $LINK -o $ROOT/tests/_bin/aot_gemm
+fi
+echo "reference drivers built"

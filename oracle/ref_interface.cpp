@@ -1,0 +1,70 @@
+// TEST INFRASTRUCTURE ONLY: exposes the CPU oracle under the symbols of the reference's
+// generated host interface (gemm / conv / capsule / GEMM), so that the reference's own,
+// unmodified host drivers (t2s/tests/performance/*/*-run-fpga.cpp with -DTINY,
+// t2s/tests/correctness/aot/gemm-run.cpp) can be linked against it and their in-driver golden
+// loops validate the oracle and its tiled output layouts. Built per kernel with
+// -DREF_GEMM / -DREF_AOT_GEMM / -DREF_CONV / -DREF_CAPSULE and the design's include path.
+// Never part of libt2sp_b200.so.
+#include <stdint.h>
+#include <string.h>
+
+#include <vector>
+
+#include "t2sp_b200/abi.h"
+
+extern "C" {
+void oracle_gemm_f32(const float*, const float*, float*, int, int, int, int);
+void oracle_gemm_tile_layout(const float*, float*, int, int, int, int, int, int);
+void oracle_conv_f32(const float*, const float*, float*, int, int, int, int, int, int, int, int, int);
+void oracle_conv_tile_layout(const float*, float*, int, int, int, int, int, int, int, int, int, int);
+void oracle_capsule_f32(const float*, const float*, float*, int, int, int, int, int, int, int, int, int, int, int, int,
+                        int, int);
+void oracle_capsule_tile_layout(const float*, float*, int, int, int, int, int, int, int, int, int, int, int, int);
+}
+
+#if defined(REF_GEMM) || defined(REF_AOT_GEMM)
+#ifdef REF_GEMM
+#include "const-parameters.h"
+#define REF_NAME gemm
+#else
+#define III 2
+#define JJJ 4
+#define II 4
+#define JJ 4
+#define REF_NAME GEMM
+#endif
+extern "C" int REF_NAME(halide_buffer_t* A, halide_buffer_t* B, halide_buffer_t* C) {
+    const int K = A->dim[0].extent, M = A->dim[1].extent, N = B->dim[0].extent;
+    std::vector<float> plain(size_t(M) * N);
+    oracle_gemm_f32(reinterpret_cast<const float*>(A->host), reinterpret_cast<const float*>(B->host), plain.data(), M,
+                    N, K, 0);
+    oracle_gemm_tile_layout(plain.data(), reinterpret_cast<float*>(C->host), JJJ, III, JJ, II, N / (JJJ * JJ),
+                            M / (III * II));
+    return 0;
+}
+#endif
+
+#ifdef REF_CONV
+#include "const-parameters.h"
+extern "C" int conv(halide_buffer_t* I, halide_buffer_t* K, halide_buffer_t* O) {
+    const int N = I->dim[0].extent / (TOTAL_CI);
+    std::vector<float> plain(size_t(TOTAL_CO) * N * (TOTAL_OY) * (TOTAL_OX));
+    oracle_conv_f32(reinterpret_cast<const float*>(I->host), reinterpret_cast<const float*>(K->host), plain.data(), N,
+                    TOTAL_CI, TOTAL_CO, KY, KX, TOTAL_OY, TOTAL_OX, CII, 0);
+    oracle_conv_tile_layout(plain.data(), reinterpret_cast<float*>(O->host), N, COOO, YYY, XXX, COO, YY, XX, Y, X, CO);
+    return 0;
+}
+#endif
+
+#ifdef REF_CAPSULE
+#include "const-parameters.h"
+extern "C" int capsule(halide_buffer_t* P, halide_buffer_t* W, halide_buffer_t* V) {
+    const int N = P->dim[1].extent / ((TOTAL_IY) * (TOTAL_IX));
+    std::vector<float> plain(size_t(TOTAL_CO) * MY * MX * NN * OY * OX * N);
+    oracle_capsule_f32(reinterpret_cast<const float*>(P->host), reinterpret_cast<const float*>(W->host), plain.data(),
+                       N, NN, TOTAL_CI, CII, TOTAL_CO, KY, KX, OY, OX, MY, MX, MK, 2, 0);
+    oracle_capsule_tile_layout(plain.data(), reinterpret_cast<float*>(V->host), N, NN, COOO, COO, CO, YYY_XXX, YY_XX,
+                               Y_X, MY, MX, OY, OX);
+    return 0;
+}
+#endif

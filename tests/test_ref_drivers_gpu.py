@@ -1,0 +1,102 @@
+"""Acceptance tests on the GPU with the reference's own material:
+ - its unmodified host drivers (gemm/conv/capsule `*-run-fpga.cpp -DTINY`, `aot/gemm-run.cpp`),
+   built here against the per-design stubs and libt2sp_b200.so by oracle/build_ref_drivers.sh
+   (the binaries travel with the repository; the reference tree itself is not needed to run them);
+   each validates the result with its own golden loop and prints `Success`;
+ - the reference's deterministic fixtures from tests/golden/kat.npz through the C ABI;
+ - device-resident buffers and the exec_time.txt report."""
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+import t2sp_b200
+from t2sp_b200 import Buffer
+from tests.util import call_gemm
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+KAT = np.load(os.path.join(ROOT, "tests", "golden", "kat.npz"))
+
+
+@pytest.mark.parametrize("name", ["gemm_tiny", "conv_tiny", "capsule_tiny", "aot_gemm"])
+def test_unmodified_reference_driver(lib, name):
+    exe = os.path.join(ROOT, "tests", "_bin", name)
+    if not os.path.exists(exe):
+        pytest.skip("driver binary not built (needs the reference tree at build time)")
+    res = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, (res.stdout[-300:], res.stderr[-500:])
+    assert res.stdout.strip().splitlines()[-1].startswith("Success")
+
+
+def test_golden_aot_gemm_fixture(lib):
+    a, b, exact = KAT["aot_gemm_a"], KAT["aot_gemm_b"], KAT["aot_gemm_c_exact"].astype(np.float64)
+    rc, C6 = call_gemm(a, b, "f32", tiled=(4, 2, 4, 4))
+    assert rc == 0
+    # undo the tiling: element (jjj,iii,jj,ii,j,i) holds C[iii + 2*ii + 8*i, jjj + 4*jj + 16*j]
+    C = C6.transpose(0, 2, 4, 1, 3, 5).reshape(16, 32)
+    nz = np.abs(exact) > 0
+    assert np.all(np.abs(C.astype(np.float64) - exact)[nz] < 0.005 * np.abs(exact)[nz])   # aot/gemm-run.cpp:78
+    assert np.max(np.abs(C - exact)) / np.max(np.abs(exact)) < 1e-5
+
+
+def test_golden_sequential_fixtures_exact(lib):
+    rc, C = call_gemm(KAT["seq_gemm_a"], KAT["seq_gemm_b"], "f32")
+    assert rc == 0 and np.array_equal(C, KAT["seq_gemm_c_exact"].astype(np.float32))
+    c = np.zeros((8, 8, 8), np.float32)
+    cb = Buffer.from_numpy(c)
+    assert t2sp_b200.ttm(Buffer.from_numpy(KAT["seq_ttm_a"]), Buffer.from_numpy(KAT["seq_ttm_b"]), cb) == 0
+    assert np.array_equal(cb.keepalive, KAT["seq_ttm_c_exact"].astype(np.float32))
+    d = np.zeros((8, 8), np.float32)
+    db = Buffer.from_numpy(d)
+    assert t2sp_b200.mttkrp(Buffer.from_numpy(KAT["seq_mttkrp_a"]), Buffer.from_numpy(KAT["seq_mttkrp_b"]),
+                            Buffer.from_numpy(KAT["seq_mttkrp_c"]), db) == 0
+    assert np.array_equal(db.keepalive, KAT["seq_mttkrp_d_exact"].astype(np.float32))
+
+
+def test_device_resident_buffers_and_exec_time(lib, tmp_path):
+    """halide_device_malloc / copy_to_device / copy_to_host protocol: inputs copied once, the
+    result stays on the device until asked for; exec_time.txt is written like the reference's."""
+    M = N = K = 256
+    A = (np.arange(M * K) % 7 - 3).astype(np.float32).reshape(M, K)
+    B = (np.arange(K * N) % 5 - 2).astype(np.float32).reshape(K, N)
+    C = np.zeros((M, N), np.float32)
+    a, b, c = Buffer.from_numpy(A), Buffer.from_numpy(B), Buffer.from_numpy(C)
+    for x in (a, b):
+        assert lib.t2sp_b200_copy_to_device(x.ptr) == 0
+    assert lib.t2sp_b200_device_malloc(c.ptr) == 0
+    os.environ["T2SP_B200_EXEC_TIME_FILE"] = str(tmp_path / "exec_time.txt")
+    try:
+        assert t2sp_b200.gemm(a, b, c) == 0
+    finally:
+        del os.environ["T2SP_B200_EXEC_TIME_FILE"]
+    assert c.raw.flags & 2 and not np.any(C)              # device_dirty set, host copy untouched
+    assert lib.t2sp_b200_copy_to_host(c.ptr) == 0
+    assert np.array_equal(c.keepalive, (A.astype(np.float64) @ B.astype(np.float64)).astype(np.float32))
+    lines = (tmp_path / "exec_time.txt").read_text().split()
+    assert float(lines[0]) > 0 and "kernel_unloader" in lines
+    assert lib.t2sp_b200_last_kernel_ns() > 0
+    for x in (a, b, c):
+        assert lib.t2sp_b200_device_free(x.ptr) == 0 and x.raw.device == 0
+
+
+def test_injected_allocation_failure_is_an_error_code(lib):
+    A = np.ones((512, 512), np.float32)
+    C = np.zeros((512, 512), np.float32)
+    os.environ["T2SP_B200_FAIL_ALLOC_ABOVE"] = "1"
+    try:
+        rc = t2sp_b200.gemm(Buffer.from_numpy(A), Buffer.from_numpy(A), Buffer.from_numpy(C))
+    finally:
+        del os.environ["T2SP_B200_FAIL_ALLOC_ABOVE"]
+    assert rc == -16                                       # halide_error_code_device_malloc_failed
+    rc = t2sp_b200.gemm(Buffer.from_numpy(A), Buffer.from_numpy(A), Buffer.from_numpy(C))
+    assert rc == 0                                         # the library stays usable
+
+
+def test_unaligned_rows_are_rejected_not_misread(lib):
+    # TMA needs 16-byte aligned row pitches: K = 30 fp32 elements is 120 bytes
+    A, B = np.ones((64, 30), np.float32), np.ones((30, 64), np.float32)
+    rc, _ = call_gemm(A, B, "f32")
+    assert rc == -8
