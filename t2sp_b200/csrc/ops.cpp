@@ -195,14 +195,15 @@ struct Timing {
 };
 
 // Runs one lowered contraction: launch, optional timing, status check.
-int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool sync_after) {
+int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool sync_after, bool pair = false) {
     ThreadState& ts = tls();
     cudaStream_t s = rt_stream();
     p.status = rt_status_word();
     const int tiles = p.tiles_m * p.tiles_n;
-    const int grid = std::max(1, std::min(tiles, core_sm_count()));
+    int grid = std::max(1, std::min(tiles, core_sm_count()));
+    if (pair) grid = 2 * std::max(1, std::min(tiles, core_sm_count() / 2));  // one cluster of 2 CTAs per tile slot
     if (sync_after) cudaEventRecord(rt_event(0), s);
-    cudaError_t e = core_launch(arith, op, bn, p, grid, s);
+    cudaError_t e = pair ? pair_launch(arith, op, p, grid, s) : core_launch(arith, op, bn, p, grid, s);
     if (e != cudaSuccess) {
         fprintf(stderr, "t2sp_b200: %s: kernel launch failed: %s\n", who, cudaGetErrorString(e));
         return halide_error_code_device_run_failed;
@@ -365,7 +366,9 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         if (arith == AR_TF32X3) resolve_precision(desc ? desc->precision : 0);
         const int bk = block_k_for(arith);
         const int op = trans_b ? OP_TTM : OP_GEMM;  // OP_TTM is the "both operands K-major" loader
-        const int bn = core_pick_bn(arith, op, N);
+        // Large 16-bit / 8-bit problems run on CTA pairs with 256 x 256 tiles.
+        const bool pair = arith != AR_TF32X3 && M >= 512 && N >= 512 && !getenv("T2SP_B200_NO_PAIR");
+        const int bn = pair ? 256 : core_pick_bn(arith, op, N);
         const int64_t lda = int64_t(A->dim[1].stride) * es, ldb = int64_t(B->dim[1].stride) * es;
         if (!tma_ok(pa, {lda})) return tma_unsupported("A");
         if (!tma_ok(pb, {ldb})) return tma_unsupported("B");
@@ -378,7 +381,7 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         }
         if (trans_b) {
             uint64_t dims[2] = {uint64_t(K), uint64_t(N)}, str[2] = {uint64_t(es), uint64_t(ldb)};
-            uint32_t box[2] = {uint32_t(bk), uint32_t(bn)};
+            uint32_t box[2] = {uint32_t(bk), uint32_t(pair ? 128 : bn)};
             if (!rt_encode_tmap(&p.mapB, tmap_type(in_t), 2, pb, dims, str, box)) return tma_unsupported("B");
         } else {
             uint64_t dims[2] = {uint64_t(N), uint64_t(K)}, str[2] = {uint64_t(es), uint64_t(ldb)};
@@ -389,6 +392,11 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         p.num_kb = (K + bk - 1) / bk; p.total_kb = p.num_kb;
         p.tiles_m = (M + kBlockM - 1) / kBlockM; p.tiles_n = (N + bn - 1) / bn;
         p.idesc = idesc_for(arith, in_t, !trans_b, bn);
+        if (pair) {
+            p.tiles_m = (M + 255) / 256;
+            p.idesc = make_instr_desc(arith == AR_I8 ? 2 : 1, arith == AR_I8 ? 1 : (in_t == kBF16 ? 1 : 0), false, !trans_b,
+                                      256, 256);
+        }
         p.out = pc;
         if (layout == 0) {
             p.epi = EPI_ROWMAJOR;
@@ -402,7 +410,7 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
             add_digit(p.dn, JJJ, JJ, C->dim[2].stride);
             add_digit(p.dn, JJJ * JJ, 1 << 30, C->dim[4].stride);
         }
-        if (int e = run_core("gemm", arith, op, bn, p, sync_after)) return e;
+        if (int e = run_core("gemm", arith, op, bn, p, sync_after, pair)) return e;
     }
     if (int e = rt_finish_output(C, "C", &vw.v[2])) return e;
     return finish_call("gemm", "kernel_Out", sync_after);

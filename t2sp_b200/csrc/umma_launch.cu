@@ -1,5 +1,6 @@
 // Instantiations of the contraction kernel and their launch table.
 #include "umma_core.cuh"
+#include "umma_pair.cuh"
 #include "umma_launch.h"
 
 namespace t2sp {
@@ -10,6 +11,22 @@ template <int ARITH, int OP, int BN, int STAGES>
 cudaError_t launch_one(const CoreParams& p, int grid, cudaStream_t stream) {
     using Cfg = CoreCfg<ARITH, OP, BN, STAGES>;
     auto kern = umma_contract_kernel<ARITH, OP, BN, STAGES>;
+    static bool configured[16] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 16 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <int ARITH, int OP, int STAGES>
+cudaError_t launch_pair(const CoreParams& p, int grid, cudaStream_t stream) {
+    using Cfg = PairCfg<ARITH, OP, STAGES>;
+    auto kern = umma_pair_kernel<ARITH, OP, STAGES>;
     static bool configured[16] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -82,6 +99,14 @@ cudaError_t core_launch(int arith, int op, int bn, const CoreParams& p, int grid
     T2SP_CASE(AR_TF32X3, OP_MTTKRP, 64, 4);
     T2SP_CASE(AR_TF32X3, OP_MTTKRP, 128, 3);
 #undef T2SP_CASE
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t pair_launch(int arith, int op, const CoreParams& p, int grid, cudaStream_t stream) {
+    if (arith == AR_F16 && op == OP_GEMM) return launch_pair<AR_F16, OP_GEMM, 6>(p, grid, stream);
+    if (arith == AR_F16 && op == OP_TTM) return launch_pair<AR_F16, OP_TTM, 6>(p, grid, stream);
+    if (arith == AR_I8 && op == OP_GEMM) return launch_pair<AR_I8, OP_GEMM, 6>(p, grid, stream);
+    if (arith == AR_I8 && op == OP_TTM) return launch_pair<AR_I8, OP_TTM, 6>(p, grid, stream);
     return cudaErrorInvalidValue;
 }
 

@@ -14,6 +14,11 @@ int core_pick_bn(int arith, int op, int n_extent);
 // Returns cudaSuccess or the launch error.
 cudaError_t core_launch(int arith, int op, int bn, const CoreParams& p, int grid, cudaStream_t stream);
 
+// Launches the two-CTA (cluster of 2, 256 x 256 tiles) GEMM kernel for the 16-bit and 8-bit
+// arithmetics; `grid` must be even. p.tiles_m / p.tiles_n count 256 x 256 tiles and p.idesc
+// describes a 256 x 256 MMA. B is MN-major for OP_GEMM and K-major for OP_TTM.
+cudaError_t pair_launch(int arith, int op, const CoreParams& p, int grid, cudaStream_t stream);
+
 // Number of SMs of the current device (cached).
 int core_sm_count();
 

@@ -139,3 +139,35 @@ def test_empty_contraction_and_empty_output(lib):
     assert rc == 0 and np.array_equal(C, np.zeros((64, 64), np.float32))
     rc, C = call_gemm(np.zeros((0, 32), np.float32), np.zeros((32, 64), np.float32), "f32")
     assert rc == 0 and C.size == 0
+
+
+@pytest.mark.parametrize("dtype,M,N,K,trans_b", [
+    ("bf16", 1024, 1024, 512, 0), ("bf16", 640, 768, 256, 0), ("bf16", 1000, 520, 136, 0), ("bf16", 768, 512, 320, 1),
+    ("i8", 1024, 768, 512, 0), ("i8", 520, 1040, 144, 0), ("i8", 512, 512, 256, 1),
+])
+def test_cta_pair_kernel(lib, dtype, M, N, K, trans_b):
+    """Problems of at least 512 x 512 outputs run on CTA pairs (256 x 256 tiles, cta_group::2);
+    ragged edges are zero-filled by TMA on the way in and masked on the way out."""
+    import t2sp_b200
+    from t2sp_b200 import Buffer, GemmDesc
+    if dtype == "i8":
+        A, B = O.int8(7, 1, (M, K)), O.int8(7, 2, (K, N))
+        ref = O.gemm_i8(A, B)
+        C = np.full((M, N), -1, np.int32)
+    else:
+        A, B = O.to_bf16(O.uniform(7, 1, (M, K))), O.to_bf16(O.uniform(7, 2, (K, N)))
+        ref = O.gemm_h16(A, B, 0, acc64=True)
+        C = np.full((M, N), np.nan, np.float32)
+    d = GemmDesc()
+    d.trans_b = trans_b
+    cb = Buffer.from_numpy(C)
+    rc = t2sp_b200.gemm(Buffer.from_numpy(A, dtype=dtype),
+                        Buffer.from_numpy(np.ascontiguousarray(B.T) if trans_b else B, dtype=dtype), cb, d)
+    assert rc == 0
+    if dtype == "i8":
+        bad = np.argwhere(cb.keepalive != ref)
+        assert bad.size == 0, f"{len(bad)} mismatches, first {bad[:5].tolist()}"
+    else:
+        assert not np.isnan(cb.keepalive).any()
+        assert normwise(cb.keepalive, ref) <= TOL_BF16
+        assert normwise(cb.keepalive, ref) <= 1e-5   # bf16 products are exact; only the fp32 summation order differs
