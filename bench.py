@@ -396,7 +396,11 @@ def main():
 
     pk = peaks()
     kernel_ms = statistics.mean(step_ms)
-    hbm_bound = kind in ("ttm", "mttkrp")
+    # fp32 contractions run as 3xTF32: their tensor ceiling is the bf16 peak / 2 / 3. The bound is
+    # whichever of (bytes / HBM bandwidth) and (FLOPs / tensor ceiling) is the longer time.
+    t_hbm = abytes / (pk["hbm"] * 1e9)
+    t_tensor = flops / (pk["burst"] * {"bf16": 1.0, "f16": 1.0, "i8": 2.0, "f32": 1.0 / 6.0}[w.get("dtype", "f32")] * 1e12)
+    hbm_bound = t_hbm > t_tensor
     if hbm_bound:
         achieved, peak, unit = abytes / (kernel_ms * 1e-3) / 1e9, pk["hbm"], "GB/s"
         peak_note = f"{pk['src']} HBM copy bandwidth"

@@ -57,7 +57,8 @@ enum halide_error_code_t {
 /* How fp32 inputs are multiplied on the tensor cores. */
 enum t2sp_precision {
     T2SP_PRECISION_DEFAULT = 0, /* $T2SP_B200_PRECISION if set, else TF32X3 */
-    T2SP_PRECISION_TF32X3 = 1   /* three TF32 MMAs per product, ~fp32 accuracy */
+    T2SP_PRECISION_TF32X3 = 1,  /* three TF32 MMAs per product, ~fp32 accuracy */
+    T2SP_PRECISION_TF32 = 2     /* one TF32 MMA per product: 10-bit mantissas, ~1e-3 accuracy, about 3x faster */
 };
 
 /* ---- GEMM:  C[i,j] = sum_k A[i,k] * B[k,j]          (t2s/tests/performance/gemm/gemm.cpp:30-63)

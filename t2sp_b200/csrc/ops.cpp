@@ -162,11 +162,12 @@ void add_digit(Digits& d, int div, int mod, long long stride) { add_digit2(d, di
 int resolve_precision(int p) {
     if (p == T2SP_PRECISION_DEFAULT) {
         const char* e = getenv("T2SP_B200_PRECISION");
+        if (e && strcmp(e, "tf32") == 0) return T2SP_PRECISION_TF32;
         if (e && strcmp(e, "tf32x3") != 0 && strcmp(e, "") != 0)
             fprintf(stderr, "t2sp_b200: unknown T2SP_B200_PRECISION '%s', using tf32x3\n", e);
         return T2SP_PRECISION_TF32X3;
     }
-    return p;
+    return p == T2SP_PRECISION_TF32 ? T2SP_PRECISION_TF32 : T2SP_PRECISION_TF32X3;
 }
 
 // Cuts the row space (ext[0] fastest) into TMA boxes: whole leading dimensions, then a divisor
@@ -363,12 +364,12 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         cudaMemsetAsync(vw.v[2].ptr, 0, vw.v[2].bytes, rt_stream());
     } else {
         const int arith = arith_for(in_t);
-        if (arith == AR_TF32X3) resolve_precision(desc ? desc->precision : 0);
+        const int prec = arith == AR_TF32X3 ? resolve_precision(desc ? desc->precision : 0) : 0;
         const int bk = block_k_for(arith);
         const int op = trans_b ? OP_TTM : OP_GEMM;  // OP_TTM is the "both operands K-major" loader
         // Large 16-bit / 8-bit problems run on CTA pairs with 256 x 256 tiles.
         const bool pair = arith != AR_TF32X3 && M >= 512 && N >= 512 && !getenv("T2SP_B200_NO_PAIR");
-        const int bn = pair ? 256 : core_pick_bn(arith, op, N);
+        const int bn = pair ? 256 : core_pick_bn(arith, op, N, M);
         const int64_t lda = int64_t(A->dim[1].stride) * es, ldb = int64_t(B->dim[1].stride) * es;
         if (!tma_ok(pa, {lda})) return tma_unsupported("A");
         if (!tma_ok(pb, {ldb})) return tma_unsupported("B");
@@ -389,6 +390,7 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
             if (!rt_encode_tmap(&p.mapB, tmap_type(in_t), 2, pb, dims, str, box, arith == AR_TF32X3)) return tma_unsupported("B");
         }
         p.M = M; p.N = N; p.tile_rows = kBlockM; p.a_tx_bytes = kBlockM * 128;
+        p.single_pass = prec == T2SP_PRECISION_TF32;
         p.num_kb = (K + bk - 1) / bk; p.total_kb = p.num_kb;
         p.tiles_m = (M + kBlockM - 1) / kBlockM; p.tiles_n = (N + bn - 1) / bn;
         p.idesc = idesc_for(arith, in_t, !trans_b, bn);
@@ -485,9 +487,9 @@ extern "C" int t2sp_b200_ttm(halide_buffer_t* a, halide_buffer_t* b, halide_buff
     if (L == 0) {
         cudaMemsetAsync(vw.v[2].ptr, 0, vw.v[2].bytes, rt_stream());
     } else {
-        resolve_precision(desc ? desc->precision : 0);
+        const int prec = resolve_precision(desc ? desc->precision : 0);
         const int M = static_cast<int>(Mrows), N = Kn;
-        const int bn = core_pick_bn(AR_TF32X3, OP_TTM, N);
+        const int bn = core_pick_bn(AR_TF32X3, OP_TTM, N, M);
         const int64_t lda = int64_t(a->dim[1].stride) * 4, ldb = int64_t(b->dim[1].stride) * 4;
         if (!tma_ok(pa, {lda})) return tma_unsupported("a");
         if (!tma_ok(pb, {ldb})) return tma_unsupported("b");
@@ -504,6 +506,7 @@ extern "C" int t2sp_b200_ttm(halide_buffer_t* a, halide_buffer_t* b, halide_buff
             if (!rt_encode_tmap(&p.mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, pb, dims, str, box)) return tma_unsupported("b");
         }
         p.M = M; p.N = N; p.tile_rows = kBlockM; p.a_tx_bytes = kBlockM * 128;
+        p.single_pass = prec == T2SP_PRECISION_TF32;
         p.num_kb = (L + 31) / 32; p.total_kb = p.num_kb;
         p.tiles_m = (M + kBlockM - 1) / kBlockM; p.tiles_n = (N + bn - 1) / bn;
         p.idesc = idesc_for(AR_TF32X3, kF32, false, bn);
@@ -613,9 +616,9 @@ extern "C" int t2sp_b200_conv(halide_buffer_t* I, halide_buffer_t* K, halide_buf
     char* pi = static_cast<char*>(vw.v[0].ptr) + origin_offset(I) * 4;
     char* pk = static_cast<char*>(vw.v[1].ptr) + origin_offset(K) * 4;
     uint32_t* po = static_cast<uint32_t*>(vw.v[2].ptr) + origin_offset(O);
-    resolve_precision(desc->precision);
+    const int prec = resolve_precision(desc->precision);
 
-    const int bn = core_pick_bn(AR_TF32X3, OP_CONV, CO);
+    const int bn = core_pick_bn(AR_TF32X3, OP_CONV, CO, Mrows);
     const int64_t s1 = int64_t(I->dim[1].stride) * 4, t1 = int64_t(K->dim[1].stride) * 4;
     if (!tma_ok(pi, {int64_t(CI) * 4, s1})) return tma_unsupported("I");
     if (!tma_ok(pk, {int64_t(CO) * 4, t1})) return tma_unsupported("K");
@@ -642,6 +645,7 @@ extern "C" int t2sp_b200_conv(halide_buffer_t* I, halide_buffer_t* K, halide_buf
     p.M = static_cast<int>(Mrows); p.N = CO;
     p.tile_rows = p.rows.rows_per_box * p.rows.boxes_per_tile;
     p.a_tx_bytes = p.tile_rows * 128;
+    p.single_pass = prec == T2SP_PRECISION_TF32;
     p.cblks = (CI + 31) / 32; p.KY = KY; p.KX = KX; p.stride = 1;
     p.num_kb = KY * KX * p.cblks; p.total_kb = p.num_kb;
     p.tiles_m = (p.M + p.tile_rows - 1) / p.tile_rows; p.tiles_n = (CO + bn - 1) / bn;
@@ -768,9 +772,9 @@ extern "C" int t2sp_b200_capsule(halide_buffer_t* P, halide_buffer_t* W, halide_
     char* pp = static_cast<char*>(vw.v[0].ptr) + origin_offset(P) * 4;
     char* pw = static_cast<char*>(vw.v[1].ptr) + origin_offset(W) * 4;
     uint32_t* pv = static_cast<uint32_t*>(vw.v[2].ptr) + origin_offset(V);
-    resolve_precision(desc->precision);
+    const int prec = resolve_precision(desc->precision);
 
-    const int bn = core_pick_bn(AR_TF32X3, OP_CAPSULE, NW);
+    const int bn = core_pick_bn(AR_TF32X3, OP_CAPSULE, NW, Mrows);
     const int64_t s1 = int64_t(P->dim[1].stride) * 4, t1 = int64_t(W->dim[1].stride) * 4;
     if (!tma_ok(pp, {int64_t(CP) * 4, s1})) return tma_unsupported("P");
     if (!tma_ok(pw, {t1})) return tma_unsupported("W");
@@ -803,6 +807,7 @@ extern "C" int t2sp_b200_capsule(halide_buffer_t* P, halide_buffer_t* W, halide_
     p.M = static_cast<int>(Mrows); p.N = NW;
     p.tile_rows = p.rows.rows_per_box * p.rows.boxes_per_tile;
     p.a_tx_bytes = p.tile_rows * 128;
+    p.single_pass = prec == T2SP_PRECISION_TF32;
     p.cblks = (CP + 31) / 32; p.KY = KY; p.KX = KX; p.stride = s; p.CI = CI; p.CII = CII;
     p.num_kb = KY * KX * p.cblks; p.total_kb = p.num_kb;
     p.tiles_m = (p.M + p.tile_rows - 1) / p.tile_rows; p.tiles_n = (NW + bn - 1) / bn;
@@ -847,7 +852,7 @@ namespace t2sp {
 // (splits * I * R floats) followed by the ordered reduction. Shared by the allocating entry.
 int mttkrp_launch(const char* who, float* pa, int64_t lda1, int64_t lda2, const float* pb, int64_t ldb,
                   const float* pc, int64_t ldc, float* pd, int64_t ldd, int L, int I, int Kd, int R, int splits,
-                  int num_kb, float* scratch, bool sync_after) {
+                  int num_kb, float* scratch, bool sync_after, bool single_pass) {
     const int bn = core_pick_bn(AR_TF32X3, OP_MTTKRP, R);
     if (bn == 0) return constraint("d.extent.1", R, "at most", 128);
     if (!tma_ok(pa, {lda1 * 4, lda2 * 4})) return tma_unsupported("a");
@@ -871,6 +876,7 @@ int mttkrp_launch(const char* who, float* pa, int64_t lda1, int64_t lda2, const 
     p.out = scratch;
     p.fc = pc; p.fb = pb; p.ldfc = ldc; p.ldfb = ldb;
     p.L = L; p.Kdim = Kd; p.R = R;
+    p.single_pass = single_pass;
     if (int e = run_core(who, AR_TF32X3, OP_MTTKRP, bn, p, sync_after)) return e;
     if (ldd == I) {
         if (reduce_partials_launch(scratch, pd, int64_t(I) * R, splits, rt_stream()) != cudaSuccess)
@@ -951,13 +957,14 @@ extern "C" int t2sp_b200_mttkrp(halide_buffer_t* a, halide_buffer_t* b, halide_b
     if (L == 0 || Kd == 0) {
         cudaMemsetAsync(vw.v[3].ptr, 0, vw.v[3].bytes, rt_stream());
     } else {
-        resolve_precision(desc ? desc->precision : 0);
+        const int prec = resolve_precision(desc ? desc->precision : 0);
         int splits = 0, num_kb = 0;
         mttkrp_plan(L, I, Kd, desc ? desc->splits : 0, &splits, &num_kb);
         float* scratch = static_cast<float*>(rt_alloc(size_t(splits) * I * R * sizeof(float)));
         if (!scratch) return halide_error_code_device_malloc_failed;
         int rc = mttkrp_launch("mttkrp", pa, a->dim[1].stride, a->dim[2].stride, pb, b->dim[1].stride, pc,
-                               c->dim[1].stride, pd, d->dim[1].stride, L, I, Kd, R, splits, num_kb, scratch, sync_after);
+                               c->dim[1].stride, pd, d->dim[1].stride, L, I, Kd, R, splits, num_kb, scratch, sync_after,
+                               prec == T2SP_PRECISION_TF32);
         // Stream order keeps the scratch block safe: a later call on this stream that reuses it
         // runs after this call's kernels.
         rt_free(scratch);

@@ -9,8 +9,9 @@
 // scatter for the tiled systolic-array layouts).
 //
 // Arithmetic variants: 16-bit floats (bf16/f16, fp32 accumulate), int8 (int32 accumulate,
-// exact) and "3xTF32" for fp32 data: every fp32 tile is split in shared memory into
-// hi = round_to_tf32(x) and lo = x - hi, and three TF32 MMAs (lo*hi, hi*lo, hi*hi) are
+// exact) and "3xTF32" for fp32 data: kind::tf32 reads only the top 19 bits of each fp32 word
+// (measured: it truncates), so the raw tile is the hi operand, lo = x - trunc(x) is computed
+// into a second tile in shared memory, and three TF32 MMAs (lo*hi, hi*lo, hi*hi) are
 // accumulated so the product keeps ~fp32 accuracy. The tensor core adds into its fp32
 // accumulator with truncation, a bias that grows with the number of accumulate steps, so the
 // 3xTF32 path (a) sums the small cross terms in an accumulator of their own and (b) lets
@@ -48,21 +49,25 @@ struct CoreCfg {
     static constexpr uint32_t kBSbo = (kBMnMajor && ARITH == AR_TF32X3) ? 512u : 1024u;
     static constexpr int kABytes = kBlockM * 128;
     static constexpr int kBBytes = BN * 128;
-    static constexpr int kStageBytes = (kABytes + kBBytes) * (kX3 ? 2 : 1);
+    static constexpr int kStageBytes = kABytes + kBBytes;    // one ring stage: [A | B] as TMA delivers them
+    // 3xTF32: the raw fp32 tiles double as the hi operands (the tensor core reads only the top 19
+    // bits of each word); the lo tiles live in a short ring of their own, [A_lo | B_lo] per slot.
+    static constexpr int kLoSlots = kX3 ? 2 : 0;
     static constexpr int kBoxBytesMn = AT::kBlockK * 128;           // one MN-major box: kBlockK rows of 128 B
     static constexpr int kBoxesMn = kBBytes / kBoxBytesMn;          // boxes per MN-major B tile
     static constexpr int kBoxElemsMn = 128 / AT::kElem;             // N elements per MN-major box
     static constexpr int kWarps = 2 + 4 + (kX3 ? 4 : 0);
     static constexpr int kThreads = kWarps * 32;
     // 16-bit / int8: two whole-tile accumulators (tile t+1 accumulates while tile t drains).
-    // 3xTF32: two chunk accumulators for the hi*hi products plus one for the small cross terms.
-    static constexpr int kTmemCols = kX3 ? (3 * BN <= 256 ? 256 : 512) : 2 * BN;
+    // 3xTF32: two chunk accumulators for the hi*hi products plus two (one per tile in flight) for the
+    // small cross terms.
+    static constexpr int kTmemCols = kX3 ? (4 * BN <= 256 ? 256 : 512) : 2 * BN;
     static constexpr int kChunkKb = 8;  // 3xTF32: k-blocks summed inside TMEM before an fp32 drain
-    static constexpr int kNumBars = 3 * STAGES + 5;
+    static constexpr int kNumBars = 2 * STAGES + 10;
     static constexpr int kTailBytes = kNumBars * 8 + 16 + 4 * 256 * 8;
-    static constexpr int kSmemBytes = STAGES * kStageBytes + kTailBytes + 1024;
+    static constexpr int kSmemBytes = (STAGES + kLoSlots) * kStageBytes + kTailBytes + 1024;
     static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "TMEM columns must be a power of two");
-    static_assert(!kX3 || 3 * BN <= 512, "3xTF32 needs three accumulators in TMEM");
+    static_assert(!kX3 || 4 * BN <= 512, "3xTF32 needs four accumulators in TMEM");
     static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
 };
 
@@ -158,14 +163,16 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
     using AT = typename Cfg::AT;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* tail = smem + STAGES * Cfg::kStageBytes;
+    uint8_t* lo_ring = smem + STAGES * Cfg::kStageBytes;     // 3xTF32: kLoSlots x [A_lo | B_lo]
+    uint8_t* tail = lo_ring + Cfg::kLoSlots * Cfg::kStageBytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);  // TMA data landed
-    uint64_t* ready_bar = full_bar + STAGES;                 // 3xTF32: hi/lo split done
-    uint64_t* empty_bar = ready_bar + STAGES;                // MMAs that read the stage retired
-    uint64_t* tfull_bar = empty_bar + STAGES;                // accumulator complete (2)
+    uint64_t* empty_bar = full_bar + STAGES;                 // MMAs that read the stage retired
+    uint64_t* ready_bar = empty_bar + STAGES;                // 3xTF32: lo slot written (2)
+    uint64_t* lofree_bar = ready_bar + 2;                    // 3xTF32: MMAs that read the lo slot retired (2)
+    uint64_t* tfull_bar = lofree_bar + 2;                    // accumulator complete (2)
     uint64_t* tempty_bar = tfull_bar + 2;                    // accumulator drained (2)
-    uint64_t* sempty_bar = tempty_bar + 2;                   // 3xTF32: cross-term accumulator drained
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sempty_bar + 1);
+    uint64_t* sempty_bar = tempty_bar + 2;                   // 3xTF32: cross-term accumulator drained (2)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sempty_bar + 2);
     uint32_t* abort_slot = tmem_slot + 1;
     long long* ntable = reinterpret_cast<long long*>(tmem_slot + 4);  // one 256-entry scatter table per epilogue warp
 
@@ -177,14 +184,18 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(&full_bar[s], 1);
-            ptx::mbar_init(&ready_bar[s], 128);
             ptx::mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(&ready_bar[a], 128);
+            ptx::mbar_init(&lofree_bar[a], 1);
         }
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(&tfull_bar[a], 1);
             ptx::mbar_init(&tempty_bar[a], 4);
         }
-        ptx::mbar_init(sempty_bar, 4);
+        ptx::mbar_init(&sempty_bar[0], 4);
+        ptx::mbar_init(&sempty_bar[1], 4);
         *abort_slot = 0u;
         ptx::fence_mbar_init();
     }
@@ -298,9 +309,9 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
             constexpr uint32_t kLboB = Cfg::kBMnMajor ? Cfg::kBoxBytesMn : 16;
             if constexpr (Cfg::kX3) {
                 int gch = 0;
-                const uint32_t d_small = tmem_base + 2 * BN;
                 for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
-                    if (!bounded_wait(sempty_bar, (lt & 1) ^ 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
+                    const uint32_t d_small = tmem_base + (2 + (lt & 1)) * BN;
+                    if (!bounded_wait(&sempty_bar[lt & 1], ((lt >> 1) & 1) ^ 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
                     const int nkb = kb_count<OP>(p, (OP == OP_MTTKRP) ? t / p.tiles_m : 0);
                     for (int kb0 = 0; kb0 < nkb && ok; kb0 += Cfg::kChunkKb, ++gch) {
                         const int b = gch & 1;
@@ -310,25 +321,30 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                         const int kend = min(kb0 + Cfg::kChunkKb, nkb);
                         for (int kb = kb0; kb < kend; ++kb, ++it) {
                             const int s = it % STAGES;
-                            const uint32_t ph = (it / STAGES) & 1;
-                            if (!bounded_wait(&ready_bar[s], ph, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
+                            const int ls = it & 1;
+                            // the splitter arrives on ready[ls] after it has seen full[s], so this
+                            // wait covers the raw tiles too
+                            if (!bounded_wait(&ready_bar[ls], (it >> 1) & 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
                             ptx::tc_fence_after_sync();
                             const uint32_t sa = ptx::smem_u32(smem + s * Cfg::kStageBytes);
                             const uint32_t sb = sa + Cfg::kABytes;
+                            const uint32_t la = ptx::smem_u32(lo_ring + ls * Cfg::kStageBytes);
                             const uint64_t da = ptx::make_smem_desc(sa, 16, 1024);
                             const uint64_t db = ptx::make_smem_desc(sb, kLboB, Cfg::kBSbo, Cfg::kBSwizzle);
-                            const uint64_t dal = ptx::make_smem_desc(sb + Cfg::kBBytes, 16, 1024);
-                            const uint64_t dbl =
-                                ptx::make_smem_desc(sb + Cfg::kBBytes + Cfg::kABytes, kLboB, Cfg::kBSbo, Cfg::kBSwizzle);
+                            const uint64_t dal = ptx::make_smem_desc(la, 16, 1024);
+                            const uint64_t dbl = ptx::make_smem_desc(la + Cfg::kABytes, kLboB, Cfg::kBSbo, Cfg::kBSwizzle);
 #pragma unroll
                             for (int j = 0; j < AT::kBlockK / AT::kUmmaK; ++j) {
-                                ptx::umma<AT::kKind, 1>(d_small, dal + j * kStepK, db + j * kStepB, p.idesc,
-                                                        (kb | j) ? 1u : 0u);
-                                ptx::umma<AT::kKind, 1>(d_small, da + j * kStepK, dbl + j * kStepB, p.idesc, 1u);
+                                if (!p.single_pass) {
+                                    ptx::umma<AT::kKind, 1>(d_small, dal + j * kStepK, db + j * kStepB, p.idesc,
+                                                            (kb | j) ? 1u : 0u);
+                                    ptx::umma<AT::kKind, 1>(d_small, da + j * kStepK, dbl + j * kStepB, p.idesc, 1u);
+                                }
                                 ptx::umma<AT::kKind, 1>(d_main, da + j * kStepK, db + j * kStepB, p.idesc,
                                                         ((kb - kb0) | j) ? 1u : 0u);
                             }
                             ptx::umma_commit(&empty_bar[s]);
+                            ptx::umma_commit(&lofree_bar[ls]);
                         }
                         if (ok) ptx::umma_commit(&tfull_bar[b]);
                     }
@@ -384,21 +400,28 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
             if constexpr (OP == OP_MTTKRP) out32 += static_cast<long long>(nb) * p.M * p.N;  // partial slab of this split
             const bool row_ok = row < p.tile_rows && m < p.M;
             if constexpr (Cfg::kX3) {
-                float sum[BN];
-#pragma unroll
-                for (int j = 0; j < BN; ++j) sum[j] = 0.f;
+                uint32_t sum[BN];  // fp32 running sums of this thread's output row, kept as raw bits
                 const int nkb = kb_count<OP>(p, nb);
                 for (int kb0 = 0; kb0 < nkb && ok; kb0 += Cfg::kChunkKb, ++gch) {
                     const int b = gch & 1;
                     if (!bounded_wait_warp(&tfull_bar[b], (gch >> 1) & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
                     ptx::tc_fence_after_sync();
+                    if (kb0 == 0) {
+                        // first chunk of the tile: load straight into the sums, all loads in flight at once
 #pragma unroll
-                    for (int c = 0; c < BN / 16; ++c) {
-                        uint32_t r[16];
-                        ptx::tmem_ld_32x16(lane_base + b * BN + c * 16, r);
+                        for (int c = 0; c < BN / 32; ++c)
+                            ptx::tmem_ld_32x32(lane_base + b * BN + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sum[c * 32]));
                         ptx::tmem_ld_wait();
+                    } else {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) sum[c * 16 + j] += __uint_as_float(r[j]);
+                        for (int c = 0; c < BN / 32; ++c) {
+                            uint32_t r[32];
+                            ptx::tmem_ld_32x32(lane_base + b * BN + c * 32, r);
+                            ptx::tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                sum[c * 32 + j] = __float_as_uint(__uint_as_float(sum[c * 32 + j]) + __uint_as_float(r[j]));
+                        }
                     }
                     ptx::tc_fence_before_sync();
                     __syncwarp();
@@ -406,23 +429,23 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                 }
                 if (!ok) break;
                 // The last chunk's commit also covers every cross-term MMA of this tile.
+                if (!p.single_pass) {
 #pragma unroll
-                for (int c = 0; c < BN / 16; ++c) {
-                    uint32_t r[16];
-                    ptx::tmem_ld_32x16(lane_base + 2 * BN + c * 16, r);
-                    ptx::tmem_ld_wait();
+                    for (int c = 0; c < BN / 32; ++c) {
+                        uint32_t r[32];
+                        ptx::tmem_ld_32x32(lane_base + (2 + (lt & 1)) * BN + c * 32, r);
+                        ptx::tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) sum[c * 16 + j] += __uint_as_float(r[j]);
+                        for (int j = 0; j < 32; ++j)
+                            sum[c * 32 + j] = __float_as_uint(__uint_as_float(sum[c * 32 + j]) + __uint_as_float(r[j]));
+                    }
                 }
                 ptx::tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(sempty_bar);
+                if (lane == 0) ptx::mbar_arrive(&sempty_bar[lt & 1]);
 #pragma unroll
                 for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t r[32];
-#pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sum[c * 32 + j]);
-                    if (row_ok) store_row_chunk(p, out32, m, n0 + c * 32, r, offm, ntab + c * 32);
+                    if (row_ok) store_row_chunk(p, out32, m, n0 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sum[c * 32]), offm, ntab + c * 32);
                 }
             } else {
                 const int acc = lt & 1;
@@ -446,40 +469,56 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
             const int st = (warp - 6) * 32 + lane;
             int it = 0;
             bool ok = true;
+            constexpr int kGenPos = BN * 8 / 128;  // MTTKRP: 16-byte chunks of the generated tile per thread
+            float gen_c[kGenPos][4];
+            int gen_lb = -1;
+            (void)gen_c; (void)gen_lb;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 const int nb = (OP == OP_MTTKRP) ? t / p.tiles_m : 0;
                 const int nkb = kb_count<OP>(p, nb);
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
+                    const int ls = it & 1;
                     uint8_t* hi = smem + s * Cfg::kStageBytes;
-                    uint8_t* lo = hi + Cfg::kABytes + Cfg::kBBytes;
+                    uint8_t* lo = lo_ring + ls * Cfg::kStageBytes;
+                    // the lo slot is free once the MMAs of two k-blocks ago have read it
+                    if (!bounded_wait_warp(&lofree_bar[ls], ((it >> 1) & 1) ^ 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
                     if constexpr (Cfg::kBGenerated) {
                         // The B tile is the Khatri-Rao slab KR[(l,k), r] = c(l,r) * b(k,r) for this
                         // k-block, written K-major with the 128-byte swizzle; it can be built while
-                        // the A tile is still in flight, but only once the stage is free.
+                        // the A tile is still in flight, but only once the stage is free. Each thread
+                        // owns kGenPos 16-byte chunks (row r of the tile, 4 consecutive l values); its
+                        // c values stay in registers while consecutive k-blocks share the same l-block.
                         if (!bounded_wait_warp(&empty_bar[s], ph ^ 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
                         const int g = nb * p.num_kb + kb;
                         const int lb = g / p.Kdim, k = g % p.Kdim;
-                        // each thread builds 16-byte chunks: row r of the tile, 4 consecutive l values
-                        for (int idx = st; idx < BN * 8; idx += 128) {
-                            const int r = idx >> 3, ch = idx & 7;
-                            float v[4] = {0.f, 0.f, 0.f, 0.f};
-                            if (r < p.R) {
+                        if (lb != gen_lb) {
+                            gen_lb = lb;
+#pragma unroll
+                            for (int i = 0; i < kGenPos; ++i) {
+                                const int idx = st + 128 * i, r = idx >> 3, ch = idx & 7;
                                 const int l = lb * 32 + ch * 4;
                                 const float* cp = p.fc + static_cast<long long>(r) * p.ldfc + l;
-                                const float bv = __ldg(p.fb + static_cast<long long>(r) * p.ldfb + k);
 #pragma unroll
-                                for (int e = 0; e < 4; ++e)
-                                    if (l + e < p.L) v[e] = __ldg(cp + e) * bv;
+                                for (int e = 0; e < 4; ++e) gen_c[i][e] = (r < p.R && l + e < p.L) ? __ldg(cp + e) : 0.f;
                             }
+                        }
+                        float bv[kGenPos];
+#pragma unroll
+                        for (int i = 0; i < kGenPos; ++i) {
+                            const int r = (st + 128 * i) >> 3;
+                            bv[i] = r < p.R ? __ldg(p.fb + static_cast<long long>(r) * p.ldfb + k) : 0.f;
+                        }
+#pragma unroll
+                        for (int i = 0; i < kGenPos; ++i) {
+                            const int idx = st + 128 * i, r = idx >> 3, ch = idx & 7;
                             float h[4], l4[4];
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
-                                uint32_t hb;
-                                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(v[e]));
-                                h[e] = __uint_as_float(hb);
-                                l4[e] = v[e] - h[e];
+                                const float v = gen_c[i][e] * bv[i];
+                                h[e] = v;
+                                l4[e] = v - __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
                             }
                             const int off = Cfg::kABytes + r * 128 + ((ch ^ (r & 7)) << 4);
                             *reinterpret_cast<float4*>(hi + off) = make_float4(h[0], h[1], h[2], h[3]);
@@ -488,24 +527,22 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                     }
                     if (!bounded_wait_warp(&full_bar[s], ph, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
                     constexpr int kSplitBytes = Cfg::kBGenerated ? Cfg::kABytes : (Cfg::kABytes + Cfg::kBBytes);
-                    // A stage holds [A_hi | B_hi | A_lo | B_lo]; the lo half mirrors the hi half, so one
-                    // flat loop over the hi bytes splits both operands.
+                    // lo = x - trunc_tf32(x): exact in fp32, at most 13 significant bits. The raw
+                    // tiles are left as they are: the tensor core ignores their low 13 mantissa bits.
+                    if (!p.single_pass) {
 #pragma unroll 4
-                    for (int off = st * 16; off < kSplitBytes; off += 128 * 16) {
-                        const float4 v = *reinterpret_cast<const float4*>(hi + off);
-                        float x[4] = {v.x, v.y, v.z, v.w}, h[4], l4[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            uint32_t hb;
-                            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hb) : "f"(x[e]));
-                            h[e] = __uint_as_float(hb);
-                            l4[e] = x[e] - h[e];
+                        for (int off = st * 16; off < kSplitBytes; off += 128 * 16) {
+                            const float4 v = *reinterpret_cast<const float4*>(hi + off);
+                            float4 l;
+                            l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
+                            l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
+                            l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
+                            l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
+                            *reinterpret_cast<float4*>(lo + off) = l;
                         }
-                        *reinterpret_cast<float4*>(hi + off) = make_float4(h[0], h[1], h[2], h[3]);
-                        *reinterpret_cast<float4*>(lo + off) = make_float4(l4[0], l4[1], l4[2], l4[3]);
                     }
                     ptx::fence_proxy_async_smem();
-                    ptx::mbar_arrive(&ready_bar[s]);
+                    ptx::mbar_arrive(&ready_bar[ls]);
                 }
             }
         }

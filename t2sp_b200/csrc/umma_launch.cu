@@ -63,15 +63,18 @@ int core_sm_count() {
     return cached[dev];
 }
 
-int core_pick_bn(int arith, int op, int n_extent) {
+int core_pick_bn(int arith, int op, int n_extent, long long m_extent) {
+    const long long tiles_m = (m_extent + kBlockM - 1) / kBlockM;
+    auto fills = [&](int bn) { return tiles_m * ((n_extent + bn - 1) / bn) >= core_sm_count(); };
     switch (arith) {
         case AR_F16:
         case AR_I8:
-            if (op == OP_GEMM || op == OP_TTM) return n_extent > 128 ? 256 : 128;
+            if (op == OP_GEMM || op == OP_TTM) return (n_extent > 128 && fills(256)) ? 256 : 128;
             return 0;
         case AR_TF32X3:
             if (op == OP_MTTKRP) return n_extent <= 64 ? 64 : (n_extent <= 128 ? 128 : 0);
-            if (op == OP_GEMM || op == OP_TTM || op == OP_CONV || op == OP_CAPSULE) return n_extent > 64 ? 128 : 64;
+            if (op == OP_GEMM || op == OP_TTM || op == OP_CONV || op == OP_CAPSULE)
+                return (n_extent > 64 && fills(128)) ? 128 : 64;
             return 0;
     }
     return 0;
@@ -88,16 +91,16 @@ cudaError_t core_launch(int arith, int op, int bn, const CoreParams& p, int grid
     T2SP_CASE(AR_I8, OP_GEMM, 128, 6);
     T2SP_CASE(AR_I8, OP_TTM, 256, 4);
     T2SP_CASE(AR_I8, OP_TTM, 128, 6);
-    T2SP_CASE(AR_TF32X3, OP_GEMM, 128, 3);
-    T2SP_CASE(AR_TF32X3, OP_GEMM, 64, 4);
-    T2SP_CASE(AR_TF32X3, OP_TTM, 128, 3);
-    T2SP_CASE(AR_TF32X3, OP_TTM, 64, 4);
-    T2SP_CASE(AR_TF32X3, OP_CONV, 128, 3);
-    T2SP_CASE(AR_TF32X3, OP_CONV, 64, 4);
-    T2SP_CASE(AR_TF32X3, OP_CAPSULE, 128, 3);
-    T2SP_CASE(AR_TF32X3, OP_CAPSULE, 64, 4);
-    T2SP_CASE(AR_TF32X3, OP_MTTKRP, 64, 4);
-    T2SP_CASE(AR_TF32X3, OP_MTTKRP, 128, 3);
+    T2SP_CASE(AR_TF32X3, OP_GEMM, 128, 4);
+    T2SP_CASE(AR_TF32X3, OP_GEMM, 64, 6);
+    T2SP_CASE(AR_TF32X3, OP_TTM, 128, 4);
+    T2SP_CASE(AR_TF32X3, OP_TTM, 64, 6);
+    T2SP_CASE(AR_TF32X3, OP_CONV, 128, 4);
+    T2SP_CASE(AR_TF32X3, OP_CONV, 64, 6);
+    T2SP_CASE(AR_TF32X3, OP_CAPSULE, 128, 4);
+    T2SP_CASE(AR_TF32X3, OP_CAPSULE, 64, 6);
+    T2SP_CASE(AR_TF32X3, OP_MTTKRP, 64, 6);
+    T2SP_CASE(AR_TF32X3, OP_MTTKRP, 128, 4);
 #undef T2SP_CASE
     return cudaErrorInvalidValue;
 }

@@ -7,8 +7,9 @@
 namespace t2sp {
 
 // Column-tile widths compiled for each arithmetic/operator pair; 0 terminates.
-// Returns the tile width to use for an N-extent, or 0 when the pair is not compiled.
-int core_pick_bn(int arith, int op, int n_extent);
+// Returns the tile width to use for an N-extent (narrower tiles when the wide ones would leave
+// SMs without work for the given M-extent), or 0 when the pair is not compiled.
+int core_pick_bn(int arith, int op, int n_extent, long long m_extent = 1 << 30);
 
 // Launches umma_contract_kernel<arith, op, bn, stages> with `grid` persistent CTAs.
 // Returns cudaSuccess or the launch error.

@@ -79,6 +79,7 @@ struct CoreParams {
     const float* fb;  // b(k,r), k fastest, column pitch ldfb
     long long ldfc, ldfb;
     int L, Kdim, R;
+    int single_pass;  // fp32 data: 1 = one TF32 MMA per product (raw tiles, no hi/lo split)
     unsigned* status;
 };
 
