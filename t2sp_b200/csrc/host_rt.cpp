@@ -190,7 +190,7 @@ void rt_count_launch(int n) { g_launches.fetch_add(static_cast<uint64_t>(n)); }
 uint64_t rt_launch_count() { return g_launches.load(); }
 
 bool rt_encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, void* base, const uint64_t* dims,
-                    const uint64_t* strides_bytes, const uint32_t* box, bool atom32) {
+                    const uint64_t* strides_bytes, const uint32_t* box, bool atom32, bool promote256) {
     if (!g_encode) return false;
     cuuint64_t gdim[5];
     cuuint64_t gstr[4];
@@ -205,7 +205,8 @@ bool rt_encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, void*
     CUresult r = g_encode(out, dtype, static_cast<cuuint32_t>(rank), base, gdim, gstr, bdim, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE,
                           atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
-                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                          promote256 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         if (getenv("T2SP_B200_LOG"))
             fprintf(stderr, "t2sp_b200: cuTensorMapEncodeTiled failed (%d) rank=%d base=%p dims0=%llu box0=%u\n", (int)r,

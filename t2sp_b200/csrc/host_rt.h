@@ -47,9 +47,11 @@ uint64_t rt_launch_count();
 // Encodes a tiled TMA descriptor. dims/strides innermost first; strides in bytes for
 // dims 1..rank-1 (stride of dim 0 is the element size). The shared-memory side uses the 128-byte
 // swizzle, with 32-byte atoms when `atom32` (the layout MN-major fp32 UMMA operands need).
-// Returns false when the driver rejects it.
+// `promote256` lets L2 fetch 256-byte lines (good when the neighbouring 128 bytes are wanted next,
+// wasteful when they are not). Returns false when the driver rejects it.
 bool rt_encode_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, void* base, const uint64_t* dims,
-                    const uint64_t* strides_bytes, const uint32_t* box, bool atom32 = false);
+                    const uint64_t* strides_bytes, const uint32_t* box, bool atom32 = false,
+                    bool promote256 = true);
 
 void rt_write_exec_time(const char* kernel_name, double ns);
 

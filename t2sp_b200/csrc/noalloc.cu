@@ -124,7 +124,7 @@ extern "C" int t2sp_b200_mttkrp_noalloc(const float* a, int64_t a_stride_i, int6
         cuuint32_t box[3] = {32, cuuint32_t(kBlockM), 1};
         cuuint32_t estr[3] = {1, 1, 1};
         if (g_encode_fn(&p.mapA[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(a), gdim, gstr, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return fail(halide_error_code_constraint_violated, "the tensor `a` cannot be described to TMA (alignment or size)");
     }

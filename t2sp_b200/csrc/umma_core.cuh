@@ -470,9 +470,9 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
             int it = 0;
             bool ok = true;
             constexpr int kGenPos = BN * 8 / 128;  // MTTKRP: 16-byte chunks of the generated tile per thread
-            float gen_c[kGenPos][4];
-            int gen_lb = -1;
-            (void)gen_c; (void)gen_lb;
+            float gen_c[kGenPos][4], gen_b[kGenPos];
+            int gen_lb = -1, gen_g = -1;
+            (void)gen_c; (void)gen_b; (void)gen_lb; (void)gen_g;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 const int nb = (OP == OP_MTTKRP) ? t / p.tiles_m : 0;
                 const int nkb = kb_count<OP>(p, nb);
@@ -504,11 +504,26 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                                 for (int e = 0; e < 4; ++e) gen_c[i][e] = (r < p.R && l + e < p.L) ? __ldg(cp + e) : 0.f;
                             }
                         }
+                        // b(k, r) for this k-block was fetched one iteration ago; fetch the next one now
                         float bv[kGenPos];
+                        if (gen_g != g) {
 #pragma unroll
-                        for (int i = 0; i < kGenPos; ++i) {
-                            const int r = (st + 128 * i) >> 3;
-                            bv[i] = r < p.R ? __ldg(p.fb + static_cast<long long>(r) * p.ldfb + k) : 0.f;
+                            for (int i = 0; i < kGenPos; ++i) {
+                                const int r = (st + 128 * i) >> 3;
+                                gen_b[i] = r < p.R ? __ldg(p.fb + static_cast<long long>(r) * p.ldfb + k) : 0.f;
+                            }
+                        }
+#pragma unroll
+                        for (int i = 0; i < kGenPos; ++i) bv[i] = gen_b[i];
+                        {
+                            const int g1 = min(g + 1, p.total_kb - 1);
+                            const int k1 = g1 % p.Kdim;
+                            gen_g = g1;
+#pragma unroll
+                            for (int i = 0; i < kGenPos; ++i) {
+                                const int r = (st + 128 * i) >> 3;
+                                gen_b[i] = r < p.R ? __ldg(p.fb + static_cast<long long>(r) * p.ldfb + k1) : 0.f;
+                            }
                         }
 #pragma unroll
                         for (int i = 0; i < kGenPos; ++i) {
