@@ -138,6 +138,7 @@ extern "C" int t2sp_b200_mttkrp_noalloc(const float* a, int64_t a_stride_i, int6
     p.fc = c; p.fb = b; p.ldfc = c_stride_r; p.ldfb = b_stride_r;
     p.L = L; p.Kdim = K; p.R = R;
     p.status = g_status_addr[dev];
+    p.group_m = 16;
 
     const int tiles = p.tiles_m * p.tiles_n;
     const int sms = core_sm_count();

@@ -148,6 +148,19 @@ int tma_unsupported(const char* name) {
     return halide_error_code_constraint_violated;
 }
 
+// Row-major fp32/int32 output [M][N] with row pitch `ld` elements: use the TMA-store epilogue when
+// the pitch and base allow a tensor map, otherwise plain vector stores.
+void set_rowmajor_epilogue(CoreParams& p, void* out, int M, int N, int64_t ld) {
+    p.epi = EPI_ROWMAJOR;
+    p.ldo = ld;
+    if (getenv("T2SP_B200_NO_TMA_STORE")) return;
+    if (p.tile_rows != kBlockM) return;  // a warp's 32-row store would spill into the next tile's rows
+    if ((reinterpret_cast<uintptr_t>(out) & 15) || (ld * 4) % 16 || ld <= 0) return;
+    uint64_t dims[2] = {uint64_t(N), uint64_t(M)}, str[2] = {4, uint64_t(ld) * 4};
+    uint32_t box[2] = {32, 32};
+    if (rt_encode_tmap(&p.mapC, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, out, dims, str, box)) p.epi = EPI_TMA;
+}
+
 void add_digit2(Digits& d, int div, int mod, int div2, int mod2, long long stride) {
     if (d.n >= kMaxDigits) return;
     d.div[d.n] = div;
@@ -200,6 +213,8 @@ int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool syn
     ThreadState& ts = tls();
     cudaStream_t s = rt_stream();
     p.status = rt_status_word();
+    if (p.group_m <= 0) p.group_m = pair ? 8 : 16;
+    if (const char* g = getenv("T2SP_B200_GROUP_M")) p.group_m = std::max(1, atoi(g));
     const int tiles = p.tiles_m * p.tiles_n;
     int grid = std::max(1, std::min(tiles, core_sm_count()));
     if (pair) grid = 2 * std::max(1, std::min(tiles, core_sm_count() / 2));  // one cluster of 2 CTAs per tile slot
@@ -401,8 +416,7 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         }
         p.out = pc;
         if (layout == 0) {
-            p.epi = EPI_ROWMAJOR;
-            p.ldo = C->dim[1].stride;
+            set_rowmajor_epilogue(p, pc, M, N, C->dim[1].stride);
         } else {
             p.epi = EPI_SCATTER;
             add_digit(p.dm, 1, III, C->dim[1].stride);
@@ -654,8 +668,7 @@ extern "C" int t2sp_b200_conv(halide_buffer_t* I, halide_buffer_t* K, halide_buf
     if (layout == 0) {
         const int64_t so = O->dim[1].stride;
         if (so == int64_t(CO) * N) {
-            p.epi = EPI_ROWMAJOR;
-            p.ldo = CO;
+            set_rowmajor_epilogue(p, po, p.M, CO, CO);
         } else {
             p.epi = EPI_SCATTER;
             add_digit(p.dm, 1, N, CO);
@@ -816,8 +829,7 @@ extern "C" int t2sp_b200_capsule(halide_buffer_t* P, halide_buffer_t* W, halide_
     if (layout == 0) {
         const int64_t so = V->dim[1].stride;
         if (so == int64_t(NW) * Q) {
-            p.epi = EPI_ROWMAJOR;
-            p.ldo = NW;
+            set_rowmajor_epilogue(p, pv, p.M, NW, NW);
         } else {
             p.epi = EPI_SCATTER;
             add_digit(p.dm, 1, Q, NW);

@@ -127,6 +127,21 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const void* map, uin
         : "memory");
 }
 
+// ---------------------------------------------------------------- TMA stores (shared -> global, tiled mode)
+// The box is clipped to the tensor's extents, so ragged edges need no masking. The issuing
+// thread tracks completion through its bulk async-groups.
+__device__ __forceinline__ void tma_store_2d(const void* map, const void* src, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(smem_u32(src)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until the shared-memory sources of all committed bulk groups have been read.
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Wait until all committed bulk groups have completed (their global writes are done).
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---------------------------------------------------------------- tcgen05: TMEM management
 template <int CTA_GROUP>
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t ncols) {

@@ -65,7 +65,7 @@ struct CoreCfg {
     static constexpr int kChunkKb = 8;  // 3xTF32: k-blocks summed inside TMEM before an fp32 drain
     static constexpr int kNumBars = 2 * STAGES + 10;
     static constexpr int kTailBytes = kNumBars * 8 + 16 + 4 * 256 * 8;
-    static constexpr int kSmemBytes = (STAGES + kLoSlots) * kStageBytes + kTailBytes + 1024;
+    static constexpr int kSmemBytes = (STAGES + kLoSlots) * kStageBytes + kCStageBytes + kTailBytes + 1024;
     static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "TMEM columns must be a power of two");
     static_assert(!kX3 || 4 * BN <= 512, "3xTF32 needs four accumulators in TMEM");
     static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
@@ -118,15 +118,34 @@ __device__ __forceinline__ int kb_count(const CoreParams& p, int nb) {
     else return p.num_kb;
 }
 
-__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& mb, int& nb) {
-    // Groups of 16 row-blocks sweep all column-blocks, rows fastest inside a group, so the
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int G, int& mb, int& nb) {
+    // Groups of G row-blocks sweep all column-blocks, rows fastest inside a group, so the
     // CTAs running at the same time share a small set of A and B panels in L2.
-    constexpr int G = 16;
     const int per_group = G * tiles_n;
     const int g = t / per_group, r = t % per_group;
     const int gm = min(G, tiles_m - g * G);
     mb = g * G + r % gm;
     nb = r / gm;
+}
+
+
+// EPI_TMA: the warp's 32 rows x 32 columns go through a swizzled shared-memory tile and leave as
+// one TMA store (full 128-byte lines instead of 32 scattered 16-byte pieces per instruction).
+// `buf` is this warp's 4 KiB tile (1024-byte aligned); lane = row within the tile.
+__device__ __forceinline__ void store_chunk_tma(const CoreParams& p, uint8_t* buf, int m_warp0, int nc,
+                                                const uint32_t (&r)[32], int lane) {
+    if (lane == 0) ptx::bulk_wait_read_all();  // the previous store has finished reading the tile
+    __syncwarp();
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+            make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0 && m_warp0 < p.M && nc < p.N) {
+        ptx::tma_store_2d(&p.mapC, buf, nc, m_warp0);
+        ptx::bulk_commit_group();
+    }
 }
 
 // Writes 32 consecutive output columns [nc, nc+32) of row m held in r[] (raw 32-bit words).
@@ -164,7 +183,8 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* lo_ring = smem + STAGES * Cfg::kStageBytes;     // 3xTF32: kLoSlots x [A_lo | B_lo]
-    uint8_t* tail = lo_ring + Cfg::kLoSlots * Cfg::kStageBytes;
+    uint8_t* cstage = lo_ring + Cfg::kLoSlots * Cfg::kStageBytes;  // EPI_TMA staging tiles
+    uint8_t* tail = cstage + kCStageBytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);  // TMA data landed
     uint64_t* empty_bar = full_bar + STAGES;                 // MMAs that read the stage retired
     uint64_t* ready_bar = empty_bar + STAGES;                // 3xTF32: lo slot written (2)
@@ -222,7 +242,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 int mb, nb;
                 if constexpr (OP == OP_MTTKRP) { mb = t % p.tiles_m; nb = t / p.tiles_m; }
-                else tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+                else tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
                 const int m0 = mb * p.tile_rows, n0 = nb * BN;
                 const int nkb = kb_count<OP>(p, nb);
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
@@ -384,7 +404,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
         for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
             int mb, nb;
             if constexpr (OP == OP_MTTKRP) { mb = t % p.tiles_m; nb = t / p.tiles_m; }
-            else tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+            else tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
             const int row = q * 32 + lane;
             const int m = mb * p.tile_rows + row;
             const int n0 = (OP == OP_MTTKRP) ? 0 : nb * BN;
@@ -445,7 +465,11 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                 if (lane == 0) ptx::mbar_arrive(&sempty_bar[lt & 1]);
 #pragma unroll
                 for (int c = 0; c < BN / 32; ++c) {
-                    if (row_ok) store_row_chunk(p, out32, m, n0 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sum[c * 32]), offm, ntab + c * 32);
+                    if (p.epi == EPI_TMA)
+                        store_chunk_tma(p, cstage + (warp - 2) * 4096, mb * p.tile_rows + q * 32, n0 + c * 32,
+                                        *reinterpret_cast<uint32_t(*)[32]>(&sum[c * 32]), lane);
+                    else if (row_ok)
+                        store_row_chunk(p, out32, m, n0 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sum[c * 32]), offm, ntab + c * 32);
                 }
             } else {
                 const int acc = lt & 1;
@@ -456,7 +480,8 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                     uint32_t r[32];
                     ptx::tmem_ld_32x32(lane_base + acc * BN + c * 32, r);
                     ptx::tmem_ld_wait();
-                    if (row_ok) store_row_chunk(p, out32, m, n0 + c * 32, r, offm, ntab + c * 32);
+                    if (p.epi == EPI_TMA) store_chunk_tma(p, cstage + (warp - 2) * 4096, mb * p.tile_rows + q * 32, n0 + c * 32, r, lane);
+                    else if (row_ok) store_row_chunk(p, out32, m, n0 + c * 32, r, offm, ntab + c * 32);
                 }
                 ptx::tc_fence_before_sync();
                 __syncwarp();
@@ -564,6 +589,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
     }
 
     // ---------------------------------------------------------------- teardown
+    if (warp >= 2 && warp < 6 && lane == 0) ptx::bulk_wait_all();  // this warp's TMA stores are done
     ptx::tc_fence_before_sync();
     __syncthreads();
     if (*abort_slot) __nanosleep(200000);  // let stray UMMAs / copies retire before TMEM goes away

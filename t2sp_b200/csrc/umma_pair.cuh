@@ -30,7 +30,7 @@ struct PairCfg {
     static constexpr int kTmemCols = 512;         // two 256-column accumulators
     static constexpr int kNumBars = 2 * STAGES + 4;
     static constexpr int kTailBytes = kNumBars * 8 + 16 + 4 * 256 * 8;
-    static constexpr int kSmemBytes = STAGES * kStageBytes + kTailBytes + 1024;
+    static constexpr int kSmemBytes = STAGES * kStageBytes + kCStageBytes + kTailBytes + 1024;
     static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
 };
 
@@ -42,7 +42,8 @@ umma_pair_kernel(const __grid_constant__ CoreParams p) {
     extern __shared__ uint8_t smem_raw[];
     // Both CTAs must place their tiles and barriers at the same shared-memory offsets.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* tail = smem + STAGES * Cfg::kStageBytes;
+    uint8_t* cstage = smem + STAGES * Cfg::kStageBytes;  // EPI_TMA staging tiles, one per epilogue warp
+    uint8_t* tail = cstage + kCStageBytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);  // leader's: both CTAs' TMA data landed
     uint64_t* empty_bar = full_bar + STAGES;                 // per CTA: MMAs that read the stage retired
     uint64_t* tfull_bar = empty_bar + STAGES;                // per CTA: accumulator complete (2)
@@ -89,7 +90,7 @@ umma_pair_kernel(const __grid_constant__ CoreParams p) {
             bool ok = true;
             for (int t = pair; t < num_tiles && ok; t += num_pairs) {
                 int mb, nb;
-                tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+                tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
                 const int m0 = mb * 256 + static_cast<int>(rank) * kBlockM;
                 const int n0 = nb * Cfg::kUmmaN + static_cast<int>(rank) * Cfg::kHalfN;
                 for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
@@ -155,7 +156,7 @@ umma_pair_kernel(const __grid_constant__ CoreParams p) {
         bool ok = true;
         for (int t = pair; t < num_tiles && ok; t += num_pairs, ++lt) {
             int mb, nb;
-            tile_coords(t, p.tiles_m, p.tiles_n, mb, nb);
+            tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
             const int acc = lt & 1;
             const int m = mb * 256 + static_cast<int>(rank) * kBlockM + q * 32 + lane;
             const int n0 = nb * Cfg::kUmmaN;
@@ -175,7 +176,11 @@ umma_pair_kernel(const __grid_constant__ CoreParams p) {
                 uint32_t r[32];
                 ptx::tmem_ld_32x32(lane_base + acc * Cfg::kUmmaN + c * 32, r);
                 ptx::tmem_ld_wait();
-                if (m < p.M) store_row_chunk(p, out32, m, n0 + c * 32, r, offm, ntab + c * 32);
+                if (p.epi == EPI_TMA)
+                    store_chunk_tma(p, cstage + (warp - 2) * 4096, mb * 256 + static_cast<int>(rank) * kBlockM + q * 32,
+                                    n0 + c * 32, r, lane);
+                else if (m < p.M)
+                    store_row_chunk(p, out32, m, n0 + c * 32, r, offm, ntab + c * 32);
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
@@ -184,6 +189,7 @@ umma_pair_kernel(const __grid_constant__ CoreParams p) {
     }
 
     // ---------------------------------------------------------------- teardown
+    if (warp >= 2 && lane == 0) ptx::bulk_wait_all();
     ptx::tc_fence_before_sync();
     __syncthreads();
     if (*abort_slot) __nanosleep(200000);

@@ -7,7 +7,7 @@ namespace t2sp {
 
 enum : int { AR_F16 = 0, AR_TF32X3 = 1, AR_I8 = 2 };
 enum : int { OP_GEMM = 0, OP_TTM = 1, OP_CONV = 2, OP_CAPSULE = 3, OP_MTTKRP = 4 };
-enum : int { EPI_ROWMAJOR = 0, EPI_COLMAJOR = 1, EPI_SCATTER = 2 };
+enum : int { EPI_ROWMAJOR = 0, EPI_COLMAJOR = 1, EPI_SCATTER = 2, EPI_TMA = 3 };
 
 // Status bits written by a kernel whose wait ran out (which role gave up).
 enum : unsigned {
@@ -20,6 +20,7 @@ enum : unsigned {
 constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s
 constexpr int kBlockM = 128;
 constexpr int kMaxDigits = 8;
+constexpr int kCStageBytes = 4 * 4096;  // EPI_TMA: one 32 x 32 fp32 staging tile per epilogue warp
 
 // offset(x) = sum_i ((((x / div[i]) % mod[i]) / div2[i]) % mod2[i]) * stride[i]
 // (the second stage lets a digit be taken of a sub-index such as the pixel number inside a row index)
@@ -54,12 +55,14 @@ struct RowSpace {
 struct CoreParams {
     CUtensorMap mapA[4];
     CUtensorMap mapB;
+    CUtensorMap mapC;  // EPI_TMA: row-major output as (N, M), box 32 columns x 32 rows, 128-byte swizzle
     int M, N;         // GEMM-view extents of the output
     int tile_rows;    // output rows per tile (128 unless the row boxes cannot fill a tile)
     int a_tx_bytes;   // bytes the A-operand TMA boxes of one stage deliver (tile_rows * 128, or 16384)
     int num_kb;       // k-blocks per output tile (per split for MTTKRP)
     int total_kb;     // MTTKRP: k-blocks over all splits (the last split may get fewer)
     int tiles_m, tiles_n;
+    int group_m;      // row-blocks per rasterisation group (tile order, L2 reuse)
     uint32_t idesc;   // tcgen05 instruction descriptor
     int epi;          // EPI_*
     void* out;        // fp32 or int32 elements
