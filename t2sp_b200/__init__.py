@@ -11,7 +11,8 @@ from . import halide
 from .halide import Buffer
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libt2sp_b200.so")
+# $T2SP_B200_LIBRARY selects another build of the same library (e.g. an instrumented one).
+LIB_PATH = os.environ.get("T2SP_B200_LIBRARY") or os.path.join(_HERE, "libt2sp_b200.so")
 _lib = None
 
 

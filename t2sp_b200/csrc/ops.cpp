@@ -214,6 +214,9 @@ int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool syn
     cudaStream_t s = rt_stream();
     p.status = rt_status_word();
     if (p.group_m <= 0) p.group_m = pair ? 8 : 16;
+#ifdef T2SP_DEBUG_KNOBS
+    if (const char* d = getenv("T2SP_B200_DEBUG")) p.debug = atoi(d);
+#endif
     if (const char* g = getenv("T2SP_B200_GROUP_M")) p.group_m = std::max(1, atoi(g));
     const int tiles = p.tiles_m * p.tiles_n;
     int grid = std::max(1, std::min(tiles, core_sm_count()));

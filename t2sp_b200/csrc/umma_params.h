@@ -83,6 +83,7 @@ struct CoreParams {
     long long ldfc, ldfb;
     int L, Kdim, R;
     int single_pass;  // fp32 data: 1 = one TF32 MMA per product (raw tiles, no hi/lo split)
+    int debug;        // only read by builds with T2SP_DEBUG_KNOBS (timing experiments)
     unsigned* status;
 };
 
