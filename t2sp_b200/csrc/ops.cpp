@@ -172,6 +172,18 @@ void add_digit2(Digits& d, int div, int mod, int div2, int mod2, long long strid
 }
 void add_digit(Digits& d, int div, int mod, long long stride) { add_digit2(d, div, mod, 1, 1 << 30, stride); }
 
+// fp32 contractions move to CTA pairs (256 x 256 or 256 x 128 tiles) when there are enough such tiles
+// to occupy most SM pairs; returns the pair tile width or 0.
+int x3_pair_width(long long M, int N, int tile_rows) {
+    // 256 x 128 pair tiles did not beat the single-CTA kernel (capsule, N = 128: 133 us vs 108 us), so
+    // pairs are used for wide outputs only unless $T2SP_B200_PAIR128 asks otherwise.
+    if (getenv("T2SP_B200_NO_PAIR") || tile_rows != kBlockM || N < 128) return 0;
+    if (N <= 128 && !getenv("T2SP_B200_PAIR128")) return 0;
+    const int un = N > 128 ? 256 : 128;
+    const long long tiles = ((M + 255) / 256) * ((N + un - 1) / un);
+    return tiles >= core_sm_count() / 4 ? un : 0;
+}
+
 int resolve_precision(int p) {
     if (p == T2SP_PRECISION_DEFAULT) {
         const char* e = getenv("T2SP_B200_PRECISION");
@@ -222,7 +234,8 @@ int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool syn
     int grid = std::max(1, std::min(tiles, core_sm_count()));
     if (pair) grid = 2 * std::max(1, std::min(tiles, core_sm_count() / 2));  // one cluster of 2 CTAs per tile slot
     if (sync_after) cudaEventRecord(rt_event(0), s);
-    cudaError_t e = pair ? pair_launch(arith, op, p, grid, s) : core_launch(arith, op, bn, p, grid, s);
+    cudaError_t e = !pair ? core_launch(arith, op, bn, p, grid, s)
+                          : (arith == AR_TF32X3 ? x3pair_launch(op, bn, p, grid, s) : pair_launch(arith, op, p, grid, s));
     if (e != cudaSuccess) {
         fprintf(stderr, "t2sp_b200: %s: kernel launch failed: %s\n", who, cudaGetErrorString(e));
         return halide_error_code_device_run_failed;
@@ -386,8 +399,9 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         const int bk = block_k_for(arith);
         const int op = trans_b ? OP_TTM : OP_GEMM;  // OP_TTM is the "both operands K-major" loader
         // Large 16-bit / 8-bit problems run on CTA pairs with 256 x 256 tiles.
-        const bool pair = arith != AR_TF32X3 && M >= 512 && N >= 512 && !getenv("T2SP_B200_NO_PAIR");
-        const int bn = pair ? 256 : core_pick_bn(arith, op, N, M);
+        const int x3un = arith == AR_TF32X3 ? x3_pair_width(M, N, kBlockM) : 0;
+        const bool pair = x3un || (arith != AR_TF32X3 && M >= 512 && N >= 512 && !getenv("T2SP_B200_NO_PAIR"));
+        const int bn = x3un ? x3un : (pair ? 256 : core_pick_bn(arith, op, N, M));
         const int64_t lda = int64_t(A->dim[1].stride) * es, ldb = int64_t(B->dim[1].stride) * es;
         if (!tma_ok(pa, {lda})) return tma_unsupported("A");
         if (!tma_ok(pb, {ldb})) return tma_unsupported("B");
@@ -400,7 +414,7 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         }
         if (trans_b) {
             uint64_t dims[2] = {uint64_t(K), uint64_t(N)}, str[2] = {uint64_t(es), uint64_t(ldb)};
-            uint32_t box[2] = {uint32_t(bk), uint32_t(pair ? 128 : bn)};
+            uint32_t box[2] = {uint32_t(bk), uint32_t(pair ? bn / 2 : bn)};
             if (!rt_encode_tmap(&p.mapB, tmap_type(in_t), 2, pb, dims, str, box)) return tma_unsupported("B");
         } else {
             uint64_t dims[2] = {uint64_t(N), uint64_t(K)}, str[2] = {uint64_t(es), uint64_t(ldb)};
@@ -414,8 +428,8 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         p.idesc = idesc_for(arith, in_t, !trans_b, bn);
         if (pair) {
             p.tiles_m = (M + 255) / 256;
-            p.idesc = make_instr_desc(arith == AR_I8 ? 2 : 1, arith == AR_I8 ? 1 : (in_t == kBF16 ? 1 : 0), false, !trans_b,
-                                      256, 256);
+            p.idesc = make_instr_desc(arith == AR_I8 ? 2 : 1, arith == AR_I8 ? 1 : (arith == AR_TF32X3 ? 2 : (in_t == kBF16 ? 1 : 0)),
+                                      false, !trans_b, 256, bn);
         }
         p.out = pc;
         if (layout == 0) {
@@ -506,7 +520,8 @@ extern "C" int t2sp_b200_ttm(halide_buffer_t* a, halide_buffer_t* b, halide_buff
     } else {
         const int prec = resolve_precision(desc ? desc->precision : 0);
         const int M = static_cast<int>(Mrows), N = Kn;
-        const int bn = core_pick_bn(AR_TF32X3, OP_TTM, N, M);
+        const int x3un = x3_pair_width(M, N, kBlockM);
+        const int bn = x3un ? x3un : core_pick_bn(AR_TF32X3, OP_TTM, N, M);
         const int64_t lda = int64_t(a->dim[1].stride) * 4, ldb = int64_t(b->dim[1].stride) * 4;
         if (!tma_ok(pa, {lda})) return tma_unsupported("a");
         if (!tma_ok(pb, {ldb})) return tma_unsupported("b");
@@ -519,7 +534,7 @@ extern "C" int t2sp_b200_ttm(halide_buffer_t* a, halide_buffer_t* b, halide_buff
         }
         {
             uint64_t dims[2] = {uint64_t(L), uint64_t(N)}, str[2] = {4, uint64_t(ldb)};
-            uint32_t box[2] = {32, uint32_t(bn)};
+            uint32_t box[2] = {32, uint32_t(x3un ? bn / 2 : bn)};
             if (!rt_encode_tmap(&p.mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, pb, dims, str, box)) return tma_unsupported("b");
         }
         p.M = M; p.N = N; p.tile_rows = kBlockM; p.a_tx_bytes = kBlockM * 128;
@@ -527,6 +542,10 @@ extern "C" int t2sp_b200_ttm(halide_buffer_t* a, halide_buffer_t* b, halide_buff
         p.num_kb = (L + 31) / 32; p.total_kb = p.num_kb;
         p.tiles_m = (M + kBlockM - 1) / kBlockM; p.tiles_n = (N + bn - 1) / bn;
         p.idesc = idesc_for(AR_TF32X3, kF32, false, bn);
+        if (x3un) {
+            p.tiles_m = (M + 255) / 256;
+            p.idesc = make_instr_desc(1, 2, false, false, 256, bn);
+        }
         p.out = pc;
         if (layout == 0) {
             if (c->dim[0].stride == 1 && (J == 1 || c->dim[1].stride == I)) {
@@ -550,7 +569,7 @@ extern "C" int t2sp_b200_ttm(halide_buffer_t* a, halide_buffer_t* b, halide_buff
             add_digit(p.dn, KKK, KK, c->dim[1].stride);
             add_digit(p.dn, KKK * KK, 1 << 30, c->dim[6].stride);
         }
-        if (int e = run_core("ttm", AR_TF32X3, OP_TTM, bn, p, sync_after)) return e;
+        if (int e = run_core("ttm", AR_TF32X3, OP_TTM, bn, p, sync_after, x3un != 0)) return e;
     }
     if (int e = rt_finish_output(c, "c", &vw.v[2])) return e;
     return finish_call("ttm", "kernel_unloader", sync_after);
@@ -635,7 +654,7 @@ extern "C" int t2sp_b200_conv(halide_buffer_t* I, halide_buffer_t* K, halide_buf
     uint32_t* po = static_cast<uint32_t*>(vw.v[2].ptr) + origin_offset(O);
     const int prec = resolve_precision(desc->precision);
 
-    const int bn = core_pick_bn(AR_TF32X3, OP_CONV, CO, Mrows);
+    int bn = core_pick_bn(AR_TF32X3, OP_CONV, CO, Mrows);
     const int64_t s1 = int64_t(I->dim[1].stride) * 4, t1 = int64_t(K->dim[1].stride) * 4;
     if (!tma_ok(pi, {int64_t(CI) * 4, s1})) return tma_unsupported("I");
     if (!tma_ok(pk, {int64_t(CO) * 4, t1})) return tma_unsupported("K");
@@ -665,8 +684,10 @@ extern "C" int t2sp_b200_conv(halide_buffer_t* I, halide_buffer_t* K, halide_buf
     p.single_pass = prec == T2SP_PRECISION_TF32;
     p.cblks = (CI + 31) / 32; p.KY = KY; p.KX = KX; p.stride = 1;
     p.num_kb = KY * KX * p.cblks; p.total_kb = p.num_kb;
-    p.tiles_m = (p.M + p.tile_rows - 1) / p.tile_rows; p.tiles_n = (CO + bn - 1) / bn;
-    p.idesc = idesc_for(AR_TF32X3, kF32, true, bn);
+    const int x3un = x3_pair_width(p.M, CO, p.tile_rows);
+    if (x3un) bn = x3un;
+    p.tiles_m = x3un ? (p.M + 255) / 256 : (p.M + p.tile_rows - 1) / p.tile_rows; p.tiles_n = (CO + bn - 1) / bn;
+    p.idesc = x3un ? make_instr_desc(1, 2, false, true, 256, bn) : idesc_for(AR_TF32X3, kF32, true, bn);
     p.out = po;
     if (layout == 0) {
         const int64_t so = O->dim[1].stride;
@@ -692,7 +713,7 @@ extern "C" int t2sp_b200_conv(halide_buffer_t* I, halide_buffer_t* K, halide_buf
         add_digit(p.dn, desc->COOO, desc->COO, d[3].stride);
         add_digit(p.dn, desc->COOO * desc->COO, 1 << 30, d[8].stride);
     }
-    if (int e = run_core("conv", AR_TF32X3, OP_CONV, bn, p, sync_after)) return e;
+    if (int e = run_core("conv", AR_TF32X3, OP_CONV, bn, p, sync_after, x3un != 0)) return e;
     if (int e = rt_finish_output(O, "O", &vw.v[2])) return e;
     return finish_call("conv", "kernel_unloader", sync_after);
 }
@@ -790,7 +811,7 @@ extern "C" int t2sp_b200_capsule(halide_buffer_t* P, halide_buffer_t* W, halide_
     uint32_t* pv = static_cast<uint32_t*>(vw.v[2].ptr) + origin_offset(V);
     const int prec = resolve_precision(desc->precision);
 
-    const int bn = core_pick_bn(AR_TF32X3, OP_CAPSULE, NW, Mrows);
+    int bn = core_pick_bn(AR_TF32X3, OP_CAPSULE, NW, Mrows);
     const int64_t s1 = int64_t(P->dim[1].stride) * 4, t1 = int64_t(W->dim[1].stride) * 4;
     if (!tma_ok(pp, {int64_t(CP) * 4, s1})) return tma_unsupported("P");
     if (!tma_ok(pw, {t1})) return tma_unsupported("W");
@@ -826,8 +847,10 @@ extern "C" int t2sp_b200_capsule(halide_buffer_t* P, halide_buffer_t* W, halide_
     p.single_pass = prec == T2SP_PRECISION_TF32;
     p.cblks = (CP + 31) / 32; p.KY = KY; p.KX = KX; p.stride = s; p.CI = CI; p.CII = CII;
     p.num_kb = KY * KX * p.cblks; p.total_kb = p.num_kb;
-    p.tiles_m = (p.M + p.tile_rows - 1) / p.tile_rows; p.tiles_n = (NW + bn - 1) / bn;
-    p.idesc = idesc_for(AR_TF32X3, kF32, true, bn);
+    const int x3un = x3_pair_width(p.M, NW, p.tile_rows);
+    if (x3un) bn = x3un;
+    p.tiles_m = x3un ? (p.M + 255) / 256 : (p.M + p.tile_rows - 1) / p.tile_rows; p.tiles_n = (NW + bn - 1) / bn;
+    p.idesc = x3un ? make_instr_desc(1, 2, false, true, 256, bn) : idesc_for(AR_TF32X3, kF32, true, bn);
     p.out = pv;
     if (layout == 0) {
         const int64_t so = V->dim[1].stride;
@@ -856,7 +879,7 @@ extern "C" int t2sp_b200_capsule(halide_buffer_t* P, halide_buffer_t* W, halide_
         add_digit(p.dn, desc->COOO * desc->COO, CO / (desc->COOO * desc->COO), d[8].stride);
         add_digit(p.dn, CO, 1 << 30, d[4].stride);
     }
-    if (int e = run_core("capsule", AR_TF32X3, OP_CAPSULE, bn, p, sync_after)) return e;
+    if (int e = run_core("capsule", AR_TF32X3, OP_CAPSULE, bn, p, sync_after, x3un != 0)) return e;
     if (int e = rt_finish_output(V, "V", &vw.v[2])) return e;
     return finish_call("capsule", "kernel_unloader", sync_after);
 }

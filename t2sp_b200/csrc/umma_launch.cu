@@ -1,6 +1,7 @@
 // Instantiations of the contraction kernel and their launch table.
 #include "umma_core.cuh"
 #include "umma_pair.cuh"
+#include "umma_x3pair.cuh"
 #include "umma_launch.h"
 
 namespace t2sp {
@@ -27,6 +28,22 @@ template <int ARITH, int OP, int STAGES>
 cudaError_t launch_pair(const CoreParams& p, int grid, cudaStream_t stream) {
     using Cfg = PairCfg<ARITH, OP, STAGES>;
     auto kern = umma_pair_kernel<ARITH, OP, STAGES>;
+    static bool configured[16] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 16 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <int OP, int UN, int STAGES>
+cudaError_t launch_x3pair(const CoreParams& p, int grid, cudaStream_t stream) {
+    using Cfg = X3PairCfg<OP, UN, STAGES>;
+    auto kern = umma_x3pair_kernel<OP, UN, STAGES>;
     static bool configured[16] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -110,6 +127,21 @@ cudaError_t pair_launch(int arith, int op, const CoreParams& p, int grid, cudaSt
     if (arith == AR_F16 && op == OP_TTM) return launch_pair<AR_F16, OP_TTM, 6>(p, grid, stream);
     if (arith == AR_I8 && op == OP_GEMM) return launch_pair<AR_I8, OP_GEMM, 6>(p, grid, stream);
     if (arith == AR_I8 && op == OP_TTM) return launch_pair<AR_I8, OP_TTM, 6>(p, grid, stream);
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t x3pair_launch(int op, int un, const CoreParams& p, int grid, cudaStream_t stream) {
+#define T2SP_X3(OPC, UNV, ST) \
+    if (op == OPC && un == UNV) return launch_x3pair<OPC, UNV, ST>(p, grid, stream)
+    T2SP_X3(OP_GEMM, 256, 4);
+    T2SP_X3(OP_GEMM, 128, 5);
+    T2SP_X3(OP_TTM, 256, 4);
+    T2SP_X3(OP_TTM, 128, 5);
+    T2SP_X3(OP_CONV, 256, 4);
+    T2SP_X3(OP_CONV, 128, 5);
+    T2SP_X3(OP_CAPSULE, 256, 4);
+    T2SP_X3(OP_CAPSULE, 128, 5);
+#undef T2SP_X3
     return cudaErrorInvalidValue;
 }
 

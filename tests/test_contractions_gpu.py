@@ -40,7 +40,8 @@ def test_ttm_known_answer(lib):
     assert np.array_equal(c9, O.ttm_tile_layout(ref.astype(np.float32), 2, 2, 2, 2, 2, 2))
 
 
-@pytest.mark.parametrize("L,I,J,K", [(256, 64, 48, 256), (100, 24, 10, 72), (64, 128, 128, 64)])
+@pytest.mark.parametrize("L,I,J,K", [(256, 64, 48, 256), (100, 24, 10, 72), (64, 128, 128, 64),
+                                     (96, 128, 100, 256), (64, 256, 64, 128)])  # the last two run on CTA pairs
 def test_ttm_random(lib, L, I, J, K):
     a = O.uniform(0, 1, (J, I, L))
     b = O.uniform(0, 2, (K, L))

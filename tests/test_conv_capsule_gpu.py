@@ -41,6 +41,8 @@ CONV_CASES = [
     (64, 32, 64, 3, 3, 6, 4),     # batch 64: one TMA box = 64 images x 2 rows
     (3, 40, 72, 3, 2, 5, 7),      # ragged: channel counts not multiples of the tile sizes
     (2, 32, 32, 1, 1, 8, 8),      # 1x1 filter
+    (64, 32, 256, 3, 3, 14, 14),  # BASELINE config 2 with fewer input channels: CTA-pair kernel, 256-wide tiles
+    (64, 64, 128, 3, 3, 14, 12),  # CTA-pair kernel, 128-wide tiles
 ]
 
 
@@ -113,6 +115,8 @@ CAPSULE_CASES = [
     (2, 4, 32, 32, 32, 3, 3, 8, 8, 1),   # BASELINE config 4 (stride 1) scaled down
     (2, 4, 32, 16, 32, 3, 3, 7, 7, 2),   # A10 constants (CII 16)
     (1, 2, 16, 4, 8, 2, 3, 3, 5, 1),     # ragged spatial extents, non-square filter
+    (2, 32, 32, 32, 32, 3, 3, 8, 10, 1), # BASELINE config 4 with fewer pixels: CTA-pair kernel (M = 20480 rows)
+    (8, 16, 16, 4, 32, 3, 3, 7, 7, 2),   # stride 2 on CTA pairs (two 64-row boxes per CTA)
 ]
 
 

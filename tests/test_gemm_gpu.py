@@ -171,3 +171,23 @@ def test_cta_pair_kernel(lib, dtype, M, N, K, trans_b):
         assert not np.isnan(cb.keepalive).any()
         assert normwise(cb.keepalive, ref) <= TOL_BF16
         assert normwise(cb.keepalive, ref) <= 1e-5   # bf16 products are exact; only the fp32 summation order differs
+
+
+@pytest.mark.parametrize("M,N,K,trans_b", [(2048, 2048, 512, 0), (2560, 1300, 200, 0), (4096, 128, 320, 0), (2304, 1024, 256, 1)])
+def test_fp32_cta_pair_kernel(lib, M, N, K, trans_b):
+    """fp32 problems with enough 256-row tiles run the 3xTF32 kernel on CTA pairs."""
+    import t2sp_b200
+    from t2sp_b200 import Buffer, GemmDesc
+    A, B = O.uniform(8, 1, (M, K)), O.uniform(8, 2, (K, N))
+    C = np.full((M, N), np.nan, np.float32)
+    cb = Buffer.from_numpy(C)
+    d = GemmDesc()
+    d.trans_b = trans_b
+    rc = t2sp_b200.gemm(Buffer.from_numpy(A), Buffer.from_numpy(np.ascontiguousarray(B.T) if trans_b else B), cb, d)
+    assert rc == 0
+    assert not np.isnan(cb.keepalive).any()
+    truth = O.gemm_f32(A, B, acc64=True)
+    err = normwise(cb.keepalive, truth)
+    print(f"fp32 pair {M}x{N}x{K}: normwise {err:.3e}")
+    assert err <= TOL_FP32
+    assert componentwise(cb.keepalive, truth, O.gemm_f32(np.abs(A), np.abs(B), acc64=True)) <= TOL_FP32
