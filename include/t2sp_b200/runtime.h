@@ -145,7 +145,7 @@ int t2sp_b200_mttkrp(halide_buffer_t *a, halide_buffer_t *b, halide_buffer_t *c,
  * sums use a fixed array of T2SP_B200_NOALLOC_SCRATCH_BYTES inside the loaded module instead
  * of the library's allocator. The call performs no cudaMalloc/cudaFree and no host staging.
  *  - limit: 4*I*R bytes (one partial slab) must fit in the array, else
- *    halide_error_code_buffer_allocation_too_large; R <= 128; `a` 16-byte aligned with
+ *    halide_error_code_buffer_allocation_too_large; R <= 128; `a` and `c` 16-byte aligned with
  *    strides that are multiples of 4 elements.
  *  - every GPU that loads the library holds the array until the process exits; all calls on
  *    a device share it (contents of the previous call remain; nothing has to be cleared

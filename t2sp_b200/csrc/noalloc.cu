@@ -124,9 +124,21 @@ extern "C" int t2sp_b200_mttkrp_noalloc(const float* a, int64_t a_stride_i, int6
         cuuint32_t box[3] = {32, cuuint32_t(kBlockM), 1};
         cuuint32_t estr[3] = {1, 1, 1};
         if (g_encode_fn(&p.mapA[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(a), gdim, gstr, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return fail(halide_error_code_constraint_violated, "the tensor `a` cannot be described to TMA (alignment or size)");
+    }
+    {
+        cuuint64_t gdim[2] = {cuuint64_t(L), cuuint64_t(R)};
+        cuuint64_t gstr[1] = {cuuint64_t(c_stride_r) * 4};
+        cuuint32_t box[2] = {32, cuuint32_t(bn)};
+        cuuint32_t estr[2] = {1, 1};
+        if ((reinterpret_cast<uintptr_t>(c) & 15) || (c_stride_r * 4) % 16 ||
+            g_encode_fn(&p.mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(c), gdim, gstr, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return fail(halide_error_code_constraint_violated,
+                        "the factor `c` cannot be described to TMA (16-byte aligned base, column stride a multiple of 4 elements)");
     }
     const int lblks = (L + 31) / 32;
     p.M = I; p.N = R; p.tile_rows = kBlockM; p.a_tx_bytes = kBlockM * 128;

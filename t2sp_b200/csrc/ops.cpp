@@ -900,9 +900,15 @@ int mttkrp_launch(const char* who, float* pa, int64_t lda1, int64_t lda2, const 
         uint64_t dims[3] = {uint64_t(L), uint64_t(I), uint64_t(Kd)};
         uint64_t str[3] = {4, uint64_t(lda1) * 4, uint64_t(lda2) * 4};
         uint32_t box[3] = {32, uint32_t(kBlockM), 1};
-        // consecutive k-blocks of a CTA step through k, not l, so the neighbouring 128 bytes of a row
-        // are not wanted soon: plain 128-byte L2 fetches
-        if (!rt_encode_tmap(&p.mapA[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, pa, dims, str, box, false, false)) return tma_unsupported("a");
+        if (!rt_encode_tmap(&p.mapA[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, pa, dims, str, box)) return tma_unsupported("a");
+    }
+    {
+        // factor c(l, r): one box = 32 consecutive l of every column r, i.e. one K-major B tile
+        if (!tma_ok(pc, {ldc * 4})) return tma_unsupported("c");
+        uint64_t dims[2] = {uint64_t(L), uint64_t(R)};
+        uint64_t str[2] = {4, uint64_t(ldc) * 4};
+        uint32_t box[2] = {32, uint32_t(bn)};
+        if (!rt_encode_tmap(&p.mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(pc), dims, str, box)) return tma_unsupported("c");
     }
     const int lblks = (L + 31) / 32;
     p.M = I; p.N = R; p.tile_rows = kBlockM; p.a_tx_bytes = kBlockM * 128;

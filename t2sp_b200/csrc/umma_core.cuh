@@ -52,7 +52,10 @@ struct CoreCfg {
     static constexpr int kStageBytes = kABytes + kBBytes;    // one ring stage: [A | B] as TMA delivers them
     // 3xTF32: the raw fp32 tiles double as the hi operands (the tensor core reads only the top 19
     // bits of each word); the lo tiles live in a short ring of their own, [A_lo | B_lo] per slot.
-    static constexpr int kLoSlots = kX3 ? 2 : 0;
+    static constexpr int kLoSlots = kX3 ? (OP == OP_MTTKRP ? (BN <= 64 ? 4 : 3) : 2) : 0;
+    // MTTKRP writes its partial slabs column-major and never stages an output tile: its staging
+    // bytes go to a deeper lo ring instead.
+    static constexpr int kCStage = (OP == OP_MTTKRP) ? 0 : kCStageBytes;
     static constexpr int kBoxBytesMn = AT::kBlockK * 128;           // one MN-major box: kBlockK rows of 128 B
     static constexpr int kBoxesMn = kBBytes / kBoxBytesMn;          // boxes per MN-major B tile
     static constexpr int kBoxElemsMn = 128 / AT::kElem;             // N elements per MN-major box
@@ -63,9 +66,9 @@ struct CoreCfg {
     // small cross terms.
     static constexpr int kTmemCols = kX3 ? (4 * BN <= 256 ? 256 : 512) : 2 * BN;
     static constexpr int kChunkKb = 8;  // 3xTF32: k-blocks summed inside TMEM before an fp32 drain
-    static constexpr int kNumBars = 2 * STAGES + 10;
+    static constexpr int kNumBars = 2 * STAGES + 14;
     static constexpr int kTailBytes = kNumBars * 8 + 16 + 4 * 256 * 8;
-    static constexpr int kSmemBytes = (STAGES + kLoSlots) * kStageBytes + kCStageBytes + kTailBytes + 1024;
+    static constexpr int kSmemBytes = (STAGES + kLoSlots) * kStageBytes + kCStage + kTailBytes + 1024;
     static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "TMEM columns must be a power of two");
     static_assert(!kX3 || 4 * BN <= 512, "3xTF32 needs four accumulators in TMEM");
     static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
@@ -184,12 +187,12 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* lo_ring = smem + STAGES * Cfg::kStageBytes;     // 3xTF32: kLoSlots x [A_lo | B_lo]
     uint8_t* cstage = lo_ring + Cfg::kLoSlots * Cfg::kStageBytes;  // EPI_TMA staging tiles
-    uint8_t* tail = cstage + kCStageBytes;
+    uint8_t* tail = cstage + Cfg::kCStage;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);  // TMA data landed
     uint64_t* empty_bar = full_bar + STAGES;                 // MMAs that read the stage retired
     uint64_t* ready_bar = empty_bar + STAGES;                // 3xTF32: lo slot written (2)
-    uint64_t* lofree_bar = ready_bar + 2;                    // 3xTF32: MMAs that read the lo slot retired (2)
-    uint64_t* tfull_bar = lofree_bar + 2;                    // accumulator complete (2)
+    uint64_t* lofree_bar = ready_bar + 4;                    // 3xTF32: MMAs that read the lo slot retired
+    uint64_t* tfull_bar = lofree_bar + 4;                    // accumulator complete (2)
     uint64_t* tempty_bar = tfull_bar + 2;                    // accumulator drained (2)
     uint64_t* sempty_bar = tempty_bar + 2;                   // 3xTF32: cross-term accumulator drained (2)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sempty_bar + 2);
@@ -206,7 +209,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
             ptx::mbar_init(&full_bar[s], 1);
             ptx::mbar_init(&empty_bar[s], 1);
         }
-        for (int a = 0; a < 2; ++a) {
+        for (int a = 0; a < 4; ++a) {
             ptx::mbar_init(&ready_bar[a], 128);
             ptx::mbar_init(&lofree_bar[a], 1);
         }
@@ -236,7 +239,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
             } else {
                 ptx::prefetch_tensormap(&p.mapA[0]);
             }
-            if constexpr (!Cfg::kBGenerated) ptx::prefetch_tensormap(&p.mapB);
+            ptx::prefetch_tensormap(&p.mapB);
             int it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
@@ -251,7 +254,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                     if (!bounded_wait(&empty_bar[s], ph ^ 1, ab, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
                     uint8_t* sa = smem + s * Cfg::kStageBytes;
                     uint8_t* sb = sa + Cfg::kABytes;
-                    ptx::mbar_expect_tx(&full_bar[s], p.a_tx_bytes + (Cfg::kBGenerated ? 0 : Cfg::kBBytes));
+                    ptx::mbar_expect_tx(&full_bar[s], p.a_tx_bytes + Cfg::kBBytes);
                     if constexpr (OP == OP_GEMM || OP == OP_TTM) {
                         ptx::tma_load_2d(sa, &p.mapA[0], &full_bar[s], kb * AT::kBlockK, m0);
                         if constexpr (OP == OP_TTM) {
@@ -301,9 +304,13 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                         }
                     } else {
                         // MTTKRP: tensor (l, i, k); this CTA's split walks k-blocks [nb*num_kb, (nb+1)*num_kb)
+                        // with the l-block fastest, so consecutive stages fetch neighbouring 128-byte
+                        // pieces of the same 128 rows. The factor slice c(l-block, all r) lands in the B
+                        // region, already in the K-major swizzled layout of the Khatri-Rao tile.
                         const int g = nb * p.num_kb + kb;
-                        const int lb = g / p.Kdim, k = g % p.Kdim;
+                        const int k = g / p.lblks, lb = g % p.lblks;
                         ptx::tma_load_3d(sa, &p.mapA[0], &full_bar[s], lb * AT::kBlockK, m0, k);
+                        ptx::tma_load_2d(sb, &p.mapB, &full_bar[s], lb * AT::kBlockK, 0);
                     }
                 }
             }
@@ -341,10 +348,10 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                         const int kend = min(kb0 + Cfg::kChunkKb, nkb);
                         for (int kb = kb0; kb < kend; ++kb, ++it) {
                             const int s = it % STAGES;
-                            const int ls = it & 1;
+                            const int ls = it % Cfg::kLoSlots;
                             // the splitter arrives on ready[ls] after it has seen full[s], so this
                             // wait covers the raw tiles too
-                            if (!bounded_wait(&ready_bar[ls], (it >> 1) & 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
+                            if (!bounded_wait(&ready_bar[ls], (it / Cfg::kLoSlots) & 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
                             ptx::tc_fence_after_sync();
                             const uint32_t sa = ptx::smem_u32(smem + s * Cfg::kStageBytes);
                             const uint32_t sb = sa + Cfg::kABytes;
@@ -495,43 +502,31 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
             int it = 0;
             bool ok = true;
             constexpr int kGenPos = BN * 8 / 128;  // MTTKRP: 16-byte chunks of the generated tile per thread
-            float gen_c[kGenPos][4], gen_b[kGenPos];
-            int gen_lb = -1, gen_g = -1;
-            (void)gen_c; (void)gen_b; (void)gen_lb; (void)gen_g;
+            float gen_b[kGenPos];
+            int gen_k = -1;
+            (void)gen_b; (void)gen_k;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 const int nb = (OP == OP_MTTKRP) ? t / p.tiles_m : 0;
                 const int nkb = kb_count<OP>(p, nb);
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
-                    const int ls = it & 1;
+                    const int ls = it % Cfg::kLoSlots;
                     uint8_t* hi = smem + s * Cfg::kStageBytes;
                     uint8_t* lo = lo_ring + ls * Cfg::kStageBytes;
                     // the lo slot is free once the MMAs of two k-blocks ago have read it
-                    if (!bounded_wait_warp(&lofree_bar[ls], ((it >> 1) & 1) ^ 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
+                    if (!bounded_wait_warp(&lofree_bar[ls], ((it / Cfg::kLoSlots) & 1) ^ 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
+                    if (!bounded_wait_warp(&full_bar[s], ph, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
                     if constexpr (Cfg::kBGenerated) {
-                        // The B tile is the Khatri-Rao slab KR[(l,k), r] = c(l,r) * b(k,r) for this
-                        // k-block, written K-major with the 128-byte swizzle; it can be built while
-                        // the A tile is still in flight, but only once the stage is free. Each thread
-                        // owns kGenPos 16-byte chunks (row r of the tile, 4 consecutive l values); its
-                        // c values stay in registers while consecutive k-blocks share the same l-block.
-                        if (!bounded_wait_warp(&empty_bar[s], ph ^ 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
+                        // The B region holds c(l-block, r) as TMA delivered it: row r of the tile, 32
+                        // consecutive l values, 128-byte swizzle. Scaling row r by b(k, r) in place turns
+                        // it into the Khatri-Rao tile KR[(l,k), r] (the hi operand); lo goes to the lo
+                        // slot. Each thread owns kGenPos 16-byte chunks; b(k, :) is constant while the
+                        // l-block runs through its lblks values, so it is re-read only when k changes.
                         const int g = nb * p.num_kb + kb;
-                        const int lb = g / p.Kdim, k = g % p.Kdim;
-                        if (lb != gen_lb) {
-                            gen_lb = lb;
-#pragma unroll
-                            for (int i = 0; i < kGenPos; ++i) {
-                                const int idx = st + 128 * i, r = idx >> 3, ch = idx & 7;
-                                const int l = lb * 32 + ch * 4;
-                                const float* cp = p.fc + static_cast<long long>(r) * p.ldfc + l;
-#pragma unroll
-                                for (int e = 0; e < 4; ++e) gen_c[i][e] = (r < p.R && l + e < p.L) ? __ldg(cp + e) : 0.f;
-                            }
-                        }
-                        // b(k, r) for this k-block was fetched one iteration ago; fetch the next one now
-                        float bv[kGenPos];
-                        if (gen_g != g) {
+                        const int k = g / p.lblks;
+                        if (k != gen_k) {
+                            gen_k = k;
 #pragma unroll
                             for (int i = 0; i < kGenPos; ++i) {
                                 const int r = (st + 128 * i) >> 3;
@@ -539,33 +534,20 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                             }
                         }
 #pragma unroll
-                        for (int i = 0; i < kGenPos; ++i) bv[i] = gen_b[i];
-                        {
-                            const int g1 = min(g + 1, p.total_kb - 1);
-                            const int k1 = g1 % p.Kdim;
-                            gen_g = g1;
-#pragma unroll
-                            for (int i = 0; i < kGenPos; ++i) {
-                                const int r = (st + 128 * i) >> 3;
-                                gen_b[i] = r < p.R ? __ldg(p.fb + static_cast<long long>(r) * p.ldfb + k1) : 0.f;
-                            }
-                        }
-#pragma unroll
                         for (int i = 0; i < kGenPos; ++i) {
-                            const int idx = st + 128 * i, r = idx >> 3, ch = idx & 7;
-                            float h[4], l4[4];
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float v = gen_c[i][e] * bv[i];
-                                h[e] = v;
-                                l4[e] = v - __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
-                            }
-                            const int off = Cfg::kABytes + r * 128 + ((ch ^ (r & 7)) << 4);
-                            *reinterpret_cast<float4*>(hi + off) = make_float4(h[0], h[1], h[2], h[3]);
-                            *reinterpret_cast<float4*>(lo + off) = make_float4(l4[0], l4[1], l4[2], l4[3]);
+                            const int off = Cfg::kABytes + (st + 128 * i) * 16;  // chunk position as stored
+                            const float4 c4 = *reinterpret_cast<const float4*>(hi + off);
+                            const float bv = gen_b[i];
+                            float4 h, l;
+                            h.x = c4.x * bv; h.y = c4.y * bv; h.z = c4.z * bv; h.w = c4.w * bv;
+                            l.x = h.x - __uint_as_float(__float_as_uint(h.x) & 0xFFFFE000u);
+                            l.y = h.y - __uint_as_float(__float_as_uint(h.y) & 0xFFFFE000u);
+                            l.z = h.z - __uint_as_float(__float_as_uint(h.z) & 0xFFFFE000u);
+                            l.w = h.w - __uint_as_float(__float_as_uint(h.w) & 0xFFFFE000u);
+                            *reinterpret_cast<float4*>(hi + off) = h;
+                            *reinterpret_cast<float4*>(lo + off) = l;
                         }
                     }
-                    if (!bounded_wait_warp(&full_bar[s], ph, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
                     constexpr int kSplitBytes = Cfg::kBGenerated ? Cfg::kABytes : (Cfg::kABytes + Cfg::kBBytes);
                     // lo = x - trunc_tf32(x): exact in fp32, at most 13 significant bits. The raw
                     // tiles are left as they are: the tensor core ignores their low 13 mantissa bits.
