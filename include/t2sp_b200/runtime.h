@@ -189,6 +189,8 @@ uint64_t t2sp_b200_kernel_launches(void);       /* kernels launched by this libr
  * exec_time.txt in dirname($BITSTREAM) or to $T2SP_B200_EXEC_TIME_FILE when set.      */
 double t2sp_b200_last_kernel_ns(void);
 const char *t2sp_b200_version(void);
+/* SM count and maximum SM clock (kHz) of the calling thread's device; 0 on success. */
+int t2sp_b200_device_info(int *sm_count, int *sm_clock_khz);
 
 #ifdef __cplusplus
 }

@@ -31,5 +31,11 @@ if [ -f "$ROOT/t2sp_b200/libt2sp_b200.so" ]; then
   $CXX $FLAGS -DTINY -I $PERF/conv    $PERF/conv/conv-run-fpga.cpp       $STUBS/conv-interface.cpp    $LINK -o $ROOT/tests/_bin/conv_tiny
   $CXX $FLAGS -DTINY -I $PERF/capsule $PERF/capsule/capsule-run-fpga.cpp $STUBS/capsule-interface.cpp $LINK -o $ROOT/tests/_bin/capsule_tiny
   $CXX $FLAGS $REF/t2s/tests/correctness/aot/gemm-run.cpp $STUBS/host.cpp $LINK -o $ROOT/tests/_bin/aot_gemm
+  # performance mode of the same drivers (no -DTINY: the A10 design constants and problem sizes),
+  # with this repository's implementation of the Roofline.h helpers in place of Roofline.cpp
+  SHIM="$ROOT/t2sp_b200/csrc/roofline_shim.cpp"
+  $CXX $FLAGS -I $PERF/gemm    $PERF/gemm/gemm-run-fpga.cpp       $STUBS/gemm-interface.cpp    $SHIM $LINK -o $ROOT/tests/_bin/gemm_large_a10
+  $CXX $FLAGS -I $PERF/conv    $PERF/conv/conv-run-fpga.cpp       $STUBS/conv-interface.cpp    $SHIM $LINK -o $ROOT/tests/_bin/conv_large_a10
+  $CXX $FLAGS -I $PERF/capsule $PERF/capsule/capsule-run-fpga.cpp $STUBS/capsule-interface.cpp $SHIM $LINK -o $ROOT/tests/_bin/capsule_large_a10
 fi
 echo "reference drivers built"

@@ -81,6 +81,7 @@ def lib():
         L.t2sp_b200_kernel_launches.restype = ctypes.c_uint64
         L.t2sp_b200_last_kernel_ns.restype = ctypes.c_double
         L.t2sp_b200_version.restype = ctypes.c_char_p
+        L.t2sp_b200_device_info.argtypes = [ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
         _lib = L
     return _lib
 

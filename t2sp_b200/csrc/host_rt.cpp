@@ -437,4 +437,15 @@ uint64_t t2sp_b200_kernel_launches(void) { return rt_launch_count(); }
 double t2sp_b200_last_kernel_ns(void) { return tls().last_kernel_ns; }
 const char* t2sp_b200_version(void) { return "t2sp_b200 0.1 (sm_100a)"; }
 
+int t2sp_b200_device_info(int* sm_count, int* sm_clock_khz) {
+    if (int e = rt_ensure_device()) return e;
+    int sms = 0, khz = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, tls().device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, tls().device) != cudaSuccess)
+        return halide_error_code_device_interface_no_device;
+    if (sm_count) *sm_count = sms;
+    if (sm_clock_khz) *sm_clock_khz = khz;
+    return 0;
+}
+
 }  // extern "C"

@@ -100,3 +100,23 @@ def test_unaligned_rows_are_rejected_not_misread(lib):
     A, B = np.ones((64, 30), np.float32), np.ones((30, 64), np.float32)
     rc, _ = call_gemm(A, B, "f32")
     assert rc == -8
+
+
+@pytest.mark.parametrize("name", ["gemm_large_a10", "conv_large_a10", "capsule_large_a10"])
+def test_unmodified_reference_driver_performance_mode(lib, name, tmp_path):
+    """The same drivers without -DTINY: the reference's A10 problem sizes (GEMM 10240 x 8192 x 16384,
+    conv 64 x 256 x 60 x 64, capsule batch 4096) with its roofline report. DSPs/FMax/ExecTime/roofline
+    come from t2sp_b200/csrc/roofline_shim.cpp; the driver must print its GFlops line, draw
+    roofline.png and end with Success."""
+    exe = os.path.join(ROOT, "tests", "_bin", name)
+    if not os.path.exists(exe):
+        pytest.skip("driver binary not built (needs the reference tree at build time)")
+    res = subprocess.run([exe], capture_output=True, text=True, timeout=900, cwd=str(tmp_path))
+    assert res.returncode == 0, (res.stdout[-500:], res.stderr[-500:])
+    lines = res.stdout.strip().splitlines()
+    assert lines[-1].startswith("Success")
+    gflops = [float(l.split(":")[1]) for l in lines if l.startswith("GFlops:")]
+    assert gflops and gflops[0] > 1000.0, lines[-8:]
+    print(name, "GFlops", gflops[0])
+    png = (tmp_path / "roofline.png").read_bytes()
+    assert png[:8] == b"\x89PNG\r\n\x1a\n" and len(png) > 1000
