@@ -73,8 +73,21 @@ typedef struct t2sp_gemm_desc {
     int32_t JJJ, III, JJ, II; /* layout 1: inner tile extents (0 = read them from C) */
     int32_t precision;        /* enum t2sp_precision */
     int32_t trans_b;          /* 1: B is stored transposed, 2-D (K_tot, J_tot) with k innermost */
+    int32_t trans_a;          /* 1: A is stored transposed, 2-D (I_tot, K_tot) with i innermost (fp32 only;
+                                 a transposed copy is made on the device) */
+    int32_t scale;            /* 1: C = alpha * A x B + beta * C (fp32 output, layout 0); C is then read too */
+    float alpha, beta;
 } t2sp_gemm_desc;
 int t2sp_b200_gemm(halide_buffer_t *A, halide_buffer_t *B, halide_buffer_t *C, const t2sp_gemm_desc *desc);
+
+/* BLAS-style front of the same kernel, the counterpart of the reference's PEPPERS wrapper
+ * `sgemm(transa, transb, m, n, k, alpha, a, lda, b, ldb, beta, c, ldc)`
+ * (t2s/peppers/blas/level3/gemm/release/a10/blas-gemm.{h,cpp}, driver sgemm-run-fpga.cpp):
+ * row-major host arrays, op(A) is m x k, op(B) is k x n, C = alpha*op(A)*op(B) + beta*C.
+ * 'N'/'n' = as stored, anything else = transposed. A leading dimension <= 0 means dense, which is
+ * what the reference driver passes (it calls with lda = ldb = ldc = 0). Returns a halide error code. */
+int t2sp_b200_sgemm(char transa, char transb, int m, int n, int k, float alpha, const float *a, int lda,
+                    const float *b, int ldb, float beta, float *c, int ldc);
 
 /* ---- 2-D convolution, stride 1, input already enlarged by KX-1 / KY-1
  *                                                     (t2s/tests/performance/conv/conv.cpp:30-65)

@@ -31,6 +31,12 @@ if [ -f "$ROOT/t2sp_b200/libt2sp_b200.so" ]; then
   $CXX $FLAGS -DTINY -I $PERF/conv    $PERF/conv/conv-run-fpga.cpp       $STUBS/conv-interface.cpp    $LINK -o $ROOT/tests/_bin/conv_tiny
   $CXX $FLAGS -DTINY -I $PERF/capsule $PERF/capsule/capsule-run-fpga.cpp $STUBS/capsule-interface.cpp $LINK -o $ROOT/tests/_bin/capsule_tiny
   $CXX $FLAGS $REF/t2s/tests/correctness/aot/gemm-run.cpp $STUBS/host.cpp $LINK -o $ROOT/tests/_bin/aot_gemm
+  # the oneAPI-flavoured GEMM driver (extra selector argument, returns the kernel time)
+  ONE="$PERF/oneapi/src"
+  $CXX $FLAGS -DTINY -DFPGA_EMULATOR -I $ONE $ONE/oneapi-target-4-run.cpp $LINK -o $ROOT/tests/_bin/oneapi_gemm_tiny
+  # the PEPPERS BLAS driver (sgemm with alpha/beta), A10 release constants with its own 4x4x4 outer loops
+  BLAS="$REF/t2s/peppers/blas/level3/gemm/release/a10"
+  $CXX $FLAGS -I $BLAS $BLAS/sgemm-run-fpga.cpp $STUBS/blas-gemm.cpp $LINK -o $ROOT/tests/_bin/blas_sgemm_a10
   # performance mode of the same drivers (no -DTINY: the A10 design constants and problem sizes),
   # with this repository's implementation of the Roofline.h helpers in place of Roofline.cpp
   SHIM="$ROOT/t2sp_b200/csrc/roofline_shim.cpp"

@@ -17,7 +17,8 @@ _lib = None
 
 
 class GemmDesc(ctypes.Structure):
-    _fields_ = [(n, ctypes.c_int32) for n in ("layout", "JJJ", "III", "JJ", "II", "precision", "trans_b")]
+    _fields_ = [(n, ctypes.c_int32) for n in ("layout", "JJJ", "III", "JJ", "II", "precision", "trans_b", "trans_a",
+                                               "scale")] + [("alpha", ctypes.c_float), ("beta", ctypes.c_float)]
 
 
 class ConvDesc(ctypes.Structure):
@@ -68,6 +69,9 @@ def lib():
                      "t2sp_b200_copy_to_host", "t2sp_b200_detach_device_ptr"):
             getattr(L, name).argtypes = [P]
             getattr(L, name).restype = ctypes.c_int
+        L.t2sp_b200_sgemm.argtypes = [ctypes.c_char, ctypes.c_char, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_float,
+                                      P, ctypes.c_int, P, ctypes.c_int, ctypes.c_float, P, ctypes.c_int]
+        L.t2sp_b200_sgemm.restype = ctypes.c_int
         i64, i32 = ctypes.c_int64, ctypes.c_int32
         L.t2sp_b200_mttkrp_noalloc.argtypes = [P, i64, i64, P, i64, P, i64, P, i64, i32, i32, i32, i32, P, i32]
         L.t2sp_b200_mttkrp_noalloc.restype = ctypes.c_int

@@ -266,12 +266,31 @@ bool all_resident(std::initializer_list<const halide_buffer_t*> bufs) {
 }
 
 struct Views {
-    DeviceView v[4];
+    DeviceView v[8];
     int n = 0;
     ~Views() {
         for (int i = 0; i < n; ++i) rt_drop_view(&v[i]);
     }
 };
+
+// TMA needs a 16-byte aligned base and row pitch. A 2-D operand that does not have them is copied
+// once, on the device, into a scratch block with a padded pitch (cudaMemcpy2DAsync), and the kernel
+// reads the copy. `ptr` / `ld_bytes` are updated in place.
+int repack_if_unaligned(Views& vw, char*& ptr, int64_t& ld_bytes, int64_t row_bytes, int64_t rows) {
+    if (tma_ok(ptr, {ld_bytes}) || rows <= 0 || row_bytes <= 0) return 0;
+    const int64_t pitch = (row_bytes + 15) / 16 * 16;
+    void* q = rt_alloc(size_t(pitch) * rows);
+    if (!q) return halide_error_code_device_malloc_failed;
+    vw.v[vw.n].ptr = q; vw.v[vw.n].borrowed = false; vw.n++;
+    if (pitch != row_bytes) cudaMemsetAsync(q, 0, size_t(pitch) * rows, rt_stream());
+    if (cudaMemcpy2DAsync(q, pitch, ptr, ld_bytes, row_bytes, rows, cudaMemcpyDeviceToDevice, rt_stream()) != cudaSuccess) {
+        cudaGetLastError();
+        return halide_error_code_device_run_failed;
+    }
+    ptr = static_cast<char*>(q);
+    ld_bytes = pitch;
+    return 0;
+}
 
 uint32_t idesc_for(int arith, uint32_t in_type, bool b_mn_major, int bn) {
     if (arith == AR_F16) return make_instr_desc(1, in_type == kBF16 ? 1 : 0, false, b_mn_major, kBlockM, bn);
@@ -345,7 +364,11 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         if (int e = check_extents_nonneg(a)) return e;
 
     const bool trans_b = desc && desc->trans_b;
-    const int K = A->dim[0].extent, M = A->dim[1].extent, N = B->dim[trans_b ? 1 : 0].extent;
+    const bool trans_a = desc && desc->trans_a;
+    const bool scale = desc && desc->scale;
+    if (trans_a && in_t != kF32) return halide_error_bad_type(nullptr, "Input buffer A (transposed)", in_t, kF32);
+    if (scale && (in_t == kI8 || layout != 0)) return constraint("gemm.desc.scale", 1, "fp32 output in the plain layout", 0);
+    const int K = A->dim[trans_a ? 1 : 0].extent, M = A->dim[trans_a ? 0 : 1].extent, N = B->dim[trans_b ? 1 : 0].extent;
     if (B->dim[trans_b ? 0 : 1].extent != K)
         return constraint(trans_b ? "B.extent.0" : "B.extent.1", B->dim[trans_b ? 0 : 1].extent, "A.extent.0", K);
 
@@ -385,12 +408,19 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
     vw.n++;
     if (int e = rt_output_view(C, "C", &vw.v[vw.n])) return e;
     vw.n++;
+    if (scale && desc->beta != 0.f && !vw.v[2].borrowed) {
+        // C is an input too: bring the caller's values to the device copy
+        if (cudaMemcpyAsync(vw.v[2].ptr, C->host, vw.v[2].bytes, cudaMemcpyHostToDevice, rt_stream()) != cudaSuccess)
+            return halide_error_code_copy_to_device_failed;
+    }
     const int es = (A->type.bits + 7) / 8;
     char* pa = static_cast<char*>(vw.v[0].ptr) + origin_offset(A) * es;
     char* pb = static_cast<char*>(vw.v[1].ptr) + origin_offset(B) * es;
     uint32_t* pc = static_cast<uint32_t*>(vw.v[2].ptr) + origin_offset(C);
 
-    if (K == 0) {
+    if (K == 0 && scale) {
+        return constraint("A.extent.0", 0, "positive when alpha/beta scaling is requested", 1);
+    } else if (K == 0) {
         // empty contraction: the result is all zeros
         cudaMemsetAsync(vw.v[2].ptr, 0, vw.v[2].bytes, rt_stream());
     } else {
@@ -402,9 +432,27 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         const int x3un = arith == AR_TF32X3 ? x3_pair_width(M, N, kBlockM) : 0;
         const bool pair = x3un || (arith != AR_TF32X3 && M >= 512 && N >= 512 && !getenv("T2SP_B200_NO_PAIR"));
         const int bn = x3un ? x3un : (pair ? 256 : core_pick_bn(arith, op, N, M));
-        const int64_t lda = int64_t(A->dim[1].stride) * es, ldb = int64_t(B->dim[1].stride) * es;
+        int64_t lda = int64_t(A->dim[1].stride) * es;
+        const int64_t ldb = int64_t(B->dim[1].stride) * es;
+        if (trans_a) {
+            // A arrives as (I_tot, K_tot), i innermost: make the K-major copy the kernel reads, with a
+            // row pitch that TMA accepts whatever K is
+            const int64_t pitch = (int64_t(K) + 3) / 4 * 4;
+            void* at = rt_alloc(size_t(M) * pitch * 4);
+            if (!at) return halide_error_code_device_malloc_failed;
+            vw.v[vw.n].ptr = at; vw.v[vw.n].borrowed = false; vw.n++;
+            if (pitch != K) cudaMemsetAsync(at, 0, size_t(M) * pitch * 4, rt_stream());
+            if (transpose32_launch(pa, A->dim[1].stride, at, pitch, K, M, rt_stream()) != cudaSuccess)
+                return halide_error_code_device_run_failed;
+            rt_count_launch(1);
+            pa = static_cast<char*>(at);
+            lda = pitch * 4;
+        }
+        int64_t ldb2 = ldb;
+        if (int e = repack_if_unaligned(vw, pa, lda, int64_t(K) * es, M)) return e;
+        if (int e = repack_if_unaligned(vw, pb, ldb2, int64_t(trans_b ? K : N) * es, trans_b ? N : K)) return e;
         if (!tma_ok(pa, {lda})) return tma_unsupported("A");
-        if (!tma_ok(pb, {ldb})) return tma_unsupported("B");
+        if (!tma_ok(pb, {ldb2})) return tma_unsupported("B");
         CoreParams p;
         memset(&p, 0, sizeof(p));
         {
@@ -413,11 +461,11 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
             if (!rt_encode_tmap(&p.mapA[0], tmap_type(in_t), 2, pa, dims, str, box)) return tma_unsupported("A");
         }
         if (trans_b) {
-            uint64_t dims[2] = {uint64_t(K), uint64_t(N)}, str[2] = {uint64_t(es), uint64_t(ldb)};
+            uint64_t dims[2] = {uint64_t(K), uint64_t(N)}, str[2] = {uint64_t(es), uint64_t(ldb2)};
             uint32_t box[2] = {uint32_t(bk), uint32_t(pair ? bn / 2 : bn)};
             if (!rt_encode_tmap(&p.mapB, tmap_type(in_t), 2, pb, dims, str, box)) return tma_unsupported("B");
         } else {
-            uint64_t dims[2] = {uint64_t(N), uint64_t(K)}, str[2] = {uint64_t(es), uint64_t(ldb)};
+            uint64_t dims[2] = {uint64_t(N), uint64_t(K)}, str[2] = {uint64_t(es), uint64_t(ldb2)};
             uint32_t box[2] = {uint32_t(128 / es), uint32_t(bk)};
             if (!rt_encode_tmap(&p.mapB, tmap_type(in_t), 2, pb, dims, str, box, arith == AR_TF32X3)) return tma_unsupported("B");
         }
@@ -432,7 +480,11 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
                                       false, !trans_b, 256, bn);
         }
         p.out = pc;
-        if (layout == 0) {
+        if (layout == 0 && scale) {
+            p.epi = EPI_ROWMAJOR;
+            p.ldo = C->dim[1].stride;
+            p.use_ab = 1; p.alpha = desc->alpha; p.beta = desc->beta;
+        } else if (layout == 0) {
             set_rowmajor_epilogue(p, pc, M, N, C->dim[1].stride);
         } else {
             p.epi = EPI_SCATTER;
@@ -447,6 +499,34 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
     }
     if (int e = rt_finish_output(C, "C", &vw.v[2])) return e;
     return finish_call("gemm", "kernel_Out", sync_after);
+}
+
+// ======================================================================================= SGEMM
+extern "C" int t2sp_b200_sgemm(char transa, char transb, int m, int n, int k, float alpha, const float* a, int lda,
+                               const float* b, int ldb, float beta, float* c, int ldc) {
+    if (!a || !b || !c) return halide_error_buffer_argument_is_null(nullptr, !a ? "a" : (!b ? "b" : "c"));
+    if (m < 0 || n < 0 || k < 0) return halide_error_buffer_extents_negative(nullptr, "sgemm", 0, m < 0 ? m : (n < 0 ? n : k));
+    const bool ta = !(transa == 'N' || transa == 'n'), tb = !(transb == 'N' || transb == 'n');
+    // row-major arrays as Halide buffers: the contiguous (last) index is dimension 0
+    const int a0 = ta ? m : k, a1 = ta ? k : m;
+    const int b0 = tb ? k : n, b1 = tb ? n : k;
+    if (lda <= 0) lda = a0;
+    if (ldb <= 0) ldb = b0;
+    if (ldc <= 0) ldc = n;
+    if (lda < a0 || ldb < b0 || ldc < n) return constraint("sgemm.ld", lda < a0 ? lda : (ldb < b0 ? ldb : ldc), "at least the row length", 0);
+    halide_dimension_t da[2] = {{0, a0, 1, 0}, {0, a1, lda, 0}};
+    halide_dimension_t db[2] = {{0, b0, 1, 0}, {0, b1, ldb, 0}};
+    halide_dimension_t dc[2] = {{0, n, 1, 0}, {0, m, ldc, 0}};
+    halide_buffer_t A, B, C;
+    memset(&A, 0, sizeof(A)); memset(&B, 0, sizeof(B)); memset(&C, 0, sizeof(C));
+    const uint32_t f32 = kF32;
+    A.host = reinterpret_cast<uint8_t*>(const_cast<float*>(a)); A.dimensions = 2; A.dim = da; memcpy(&A.type, &f32, 4);
+    B.host = reinterpret_cast<uint8_t*>(const_cast<float*>(b)); B.dimensions = 2; B.dim = db; memcpy(&B.type, &f32, 4);
+    C.host = reinterpret_cast<uint8_t*>(c); C.dimensions = 2; C.dim = dc; memcpy(&C.type, &f32, 4);
+    t2sp_gemm_desc d;
+    memset(&d, 0, sizeof(d));
+    d.trans_a = ta; d.trans_b = tb; d.scale = 1; d.alpha = alpha; d.beta = beta;
+    return t2sp_b200_gemm(&A, &B, &C, &d);
 }
 
 // ======================================================================================= TTM
@@ -522,7 +602,9 @@ extern "C" int t2sp_b200_ttm(halide_buffer_t* a, halide_buffer_t* b, halide_buff
         const int M = static_cast<int>(Mrows), N = Kn;
         const int x3un = x3_pair_width(M, N, kBlockM);
         const int bn = x3un ? x3un : core_pick_bn(AR_TF32X3, OP_TTM, N, M);
-        const int64_t lda = int64_t(a->dim[1].stride) * 4, ldb = int64_t(b->dim[1].stride) * 4;
+        int64_t lda = int64_t(a->dim[1].stride) * 4, ldb = int64_t(b->dim[1].stride) * 4;
+        if (int e = repack_if_unaligned(vw, pa, lda, int64_t(L) * 4, M)) return e;
+        if (int e = repack_if_unaligned(vw, pb, ldb, int64_t(L) * 4, N)) return e;
         if (!tma_ok(pa, {lda})) return tma_unsupported("a");
         if (!tma_ok(pb, {ldb})) return tma_unsupported("b");
         CoreParams p;

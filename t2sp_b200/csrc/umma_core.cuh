@@ -155,7 +155,15 @@ __device__ __forceinline__ void store_chunk_tma(const CoreParams& p, uint8_t* bu
 __device__ __forceinline__ void store_row_chunk(const CoreParams& p, uint32_t* out32, int m, int nc,
                                                 const uint32_t (&r)[32], long long offm, const long long* ntab) {
     if (nc >= p.N) return;
-    if (p.epi == EPI_ROWMAJOR) {
+    if (p.epi == EPI_ROWMAJOR && p.use_ab) {
+        float* dst = reinterpret_cast<float*>(out32) + static_cast<long long>(m) * p.ldo + nc;
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+            if (nc + j < p.N) {
+                const float v = p.alpha * __uint_as_float(r[j]);
+                dst[j] = p.beta != 0.f ? v + p.beta * dst[j] : v;
+            }
+    } else if (p.epi == EPI_ROWMAJOR) {
         uint32_t* dst = out32 + static_cast<long long>(m) * p.ldo + nc;
         if (nc + 32 <= p.N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll

@@ -145,6 +145,30 @@ cudaError_t x3pair_launch(int op, int un, const CoreParams& p, int grid, cudaStr
     return cudaErrorInvalidValue;
 }
 
+__global__ void transpose32_kernel(const uint32_t* __restrict__ src, long long ld_src, uint32_t* __restrict__ dst,
+                                   long long ld_dst, int rows, int cols) {
+    __shared__ uint32_t tile[32][33];
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int r = r0 + j, c = c0 + threadIdx.x;
+        if (r < rows && c < cols) tile[j][threadIdx.x] = src[r * ld_src + c];
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int c = c0 + j, r = r0 + threadIdx.x;  // dst[c][r] = src[r][c]
+        if (r < rows && c < cols) dst[c * ld_dst + r] = tile[threadIdx.x][j];
+    }
+}
+
+cudaError_t transpose32_launch(const void* src, long long ld_src, void* dst, long long ld_dst, int rows, int cols,
+                               cudaStream_t stream) {
+    if (rows <= 0 || cols <= 0) return cudaSuccess;
+    dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
+    transpose32_kernel<<<grid, block, 0, stream>>>(static_cast<const uint32_t*>(src), ld_src, static_cast<uint32_t*>(dst),
+                                                   ld_dst, rows, cols);
+    return cudaGetLastError();
+}
+
 cudaError_t reduce_partials_launch(const float* partials, float* out, long long elems, int splits,
                                    cudaStream_t stream) {
     const int threads = 256;

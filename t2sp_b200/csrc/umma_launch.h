@@ -25,6 +25,10 @@ cudaError_t pair_launch(int arith, int op, const CoreParams& p, int grid, cudaSt
 // p.idesc describes a 256 x un TF32 MMA.
 cudaError_t x3pair_launch(int op, int un, const CoreParams& p, int grid, cudaStream_t stream);
 
+// dst[c][r] = src[r][c] for a rows x cols matrix of 32-bit elements (pitches in elements).
+cudaError_t transpose32_launch(const void* src, long long ld_src, void* dst, long long ld_dst, int rows, int cols,
+                               cudaStream_t stream);
+
 // Number of SMs of the current device (cached).
 int core_sm_count();
 

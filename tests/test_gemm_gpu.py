@@ -191,3 +191,23 @@ def test_fp32_cta_pair_kernel(lib, M, N, K, trans_b):
     print(f"fp32 pair {M}x{N}x{K}: normwise {err:.3e}")
     assert err <= TOL_FP32
     assert componentwise(cb.keepalive, truth, O.gemm_f32(np.abs(A), np.abs(B), acc64=True)) <= TOL_FP32
+
+
+@pytest.mark.parametrize("ta,tb,m,n,k", [("N", "N", 256, 192, 128), ("T", "N", 300, 200, 100), ("N", "T", 128, 260, 64),
+                                         ("T", "T", 520, 516, 90), ("N", "N", 2048, 1024, 256)])
+def test_blas_sgemm(lib, ta, tb, m, n, k):
+    """BLAS-style entry (reference: t2s/peppers/blas/level3/gemm/release/a10/blas-gemm.cpp): row-major arrays,
+    transposes, alpha/beta. transa = 'T' exercises the on-device transpose, including K not a multiple of 4."""
+    import ctypes
+    a = O.uniform(9, 1, (k, m) if ta == "T" else (m, k))
+    b = O.uniform(9, 2, (n, k) if tb == "T" else (k, n))
+    c0 = O.uniform(9, 3, (m, n))
+    c = c0.copy()
+    alpha, beta = 1.75, -0.5
+    rc = lib.t2sp_b200_sgemm(ta.encode(), tb.encode(), m, n, k, alpha, a.ctypes.data, 0, b.ctypes.data, 0, beta,
+                             c.ctypes.data, 0)
+    assert rc == 0
+    opa = a.T if ta == "T" else a
+    opb = b.T if tb == "T" else b
+    truth = alpha * (opa.astype(np.float64) @ opb.astype(np.float64)) + beta * c0.astype(np.float64)
+    assert normwise(c, truth) <= TOL_FP32
