@@ -221,7 +221,8 @@ struct Timing {
 };
 
 // Runs one lowered contraction: launch, optional timing, status check.
-int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool sync_after, bool pair = false) {
+int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool sync_after, bool pair = false,
+             bool pair2 = false) {
     ThreadState& ts = tls();
     cudaStream_t s = rt_stream();
     p.status = rt_status_word();
@@ -235,7 +236,8 @@ int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool syn
     if (pair) grid = 2 * std::max(1, std::min(tiles, core_sm_count() / 2));  // one cluster of 2 CTAs per tile slot
     if (sync_after) cudaEventRecord(rt_event(0), s);
     cudaError_t e = !pair ? core_launch(arith, op, bn, p, grid, s)
-                          : (arith == AR_TF32X3 ? x3pair_launch(op, bn, p, grid, s) : pair_launch(arith, op, p, grid, s));
+                          : (arith == AR_TF32X3 ? x3pair_launch(op, bn, p, grid, s)
+                                                : (pair2 ? pair2_launch(arith, op, p, grid, s) : pair_launch(arith, op, p, grid, s)));
     if (e != cudaSuccess) {
         fprintf(stderr, "t2sp_b200: %s: kernel launch failed: %s\n", who, cudaGetErrorString(e));
         return halide_error_code_device_run_failed;
@@ -474,8 +476,11 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         p.num_kb = (K + bk - 1) / bk; p.total_kb = p.num_kb;
         p.tiles_m = (M + kBlockM - 1) / kBlockM; p.tiles_n = (N + bn - 1) / bn;
         p.idesc = idesc_for(arith, in_t, !trans_b, bn);
+        // 512-row pair tiles when there are enough of them to fill the SM pairs several times over
+        const char* p2env = getenv("T2SP_B200_PAIR2");
+        const bool pair2 = pair && !x3un && (p2env ? atoi(p2env) != 0 : false) && M >= 1024;
         if (pair) {
-            p.tiles_m = (M + 255) / 256;
+            p.tiles_m = pair2 ? (M + 511) / 512 : (M + 255) / 256;
             p.idesc = make_instr_desc(arith == AR_I8 ? 2 : 1, arith == AR_I8 ? 1 : (arith == AR_TF32X3 ? 2 : (in_t == kBF16 ? 1 : 0)),
                                       false, !trans_b, 256, bn);
         }
@@ -495,7 +500,7 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
             add_digit(p.dn, JJJ, JJ, C->dim[2].stride);
             add_digit(p.dn, JJJ * JJ, 1 << 30, C->dim[4].stride);
         }
-        if (int e = run_core("gemm", arith, op, bn, p, sync_after, pair)) return e;
+        if (int e = run_core("gemm", arith, op, bn, p, sync_after, pair, pair2)) return e;
     }
     if (int e = rt_finish_output(C, "C", &vw.v[2])) return e;
     return finish_call("gemm", "kernel_Out", sync_after);

@@ -1,6 +1,7 @@
 // Instantiations of the contraction kernel and their launch table.
 #include "umma_core.cuh"
 #include "umma_pair.cuh"
+#include "umma_pair2.cuh"
 #include "umma_x3pair.cuh"
 #include "umma_launch.h"
 
@@ -28,6 +29,22 @@ template <int ARITH, int OP, int STAGES>
 cudaError_t launch_pair(const CoreParams& p, int grid, cudaStream_t stream) {
     using Cfg = PairCfg<ARITH, OP, STAGES>;
     auto kern = umma_pair_kernel<ARITH, OP, STAGES>;
+    static bool configured[16] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 16 && !configured[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
+template <int ARITH, int OP, int STAGES>
+cudaError_t launch_pair2(const CoreParams& p, int grid, cudaStream_t stream) {
+    using Cfg = Pair2Cfg<ARITH, OP, STAGES>;
+    auto kern = umma_pair2_kernel<ARITH, OP, STAGES>;
     static bool configured[16] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -127,6 +144,14 @@ cudaError_t pair_launch(int arith, int op, const CoreParams& p, int grid, cudaSt
     if (arith == AR_F16 && op == OP_TTM) return launch_pair<AR_F16, OP_TTM, 6>(p, grid, stream);
     if (arith == AR_I8 && op == OP_GEMM) return launch_pair<AR_I8, OP_GEMM, 6>(p, grid, stream);
     if (arith == AR_I8 && op == OP_TTM) return launch_pair<AR_I8, OP_TTM, 6>(p, grid, stream);
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t pair2_launch(int arith, int op, const CoreParams& p, int grid, cudaStream_t stream) {
+    if (arith == AR_F16 && op == OP_GEMM) return launch_pair2<AR_F16, OP_GEMM, 4>(p, grid, stream);
+    if (arith == AR_F16 && op == OP_TTM) return launch_pair2<AR_F16, OP_TTM, 4>(p, grid, stream);
+    if (arith == AR_I8 && op == OP_GEMM) return launch_pair2<AR_I8, OP_GEMM, 4>(p, grid, stream);
+    if (arith == AR_I8 && op == OP_TTM) return launch_pair2<AR_I8, OP_TTM, 4>(p, grid, stream);
     return cudaErrorInvalidValue;
 }
 

@@ -20,6 +20,9 @@ cudaError_t core_launch(int arith, int op, int bn, const CoreParams& p, int grid
 // describes a 256 x 256 MMA. B is MN-major for OP_GEMM and K-major for OP_TTM.
 cudaError_t pair_launch(int arith, int op, const CoreParams& p, int grid, cudaStream_t stream);
 
+// Same with 512 x 256 tiles (each CTA owns two 128-row sub-tiles); p.tiles_m counts 512-row tiles.
+cudaError_t pair2_launch(int arith, int op, const CoreParams& p, int grid, cudaStream_t stream);
+
 // Launches the two-CTA 3xTF32 kernel (fp32 data, 256 x `un` tiles, un = 256 or 128) for
 // OP_GEMM / OP_TTM / OP_CONV / OP_CAPSULE; `grid` must be even, tiles count 256 x un tiles and
 // p.idesc describes a 256 x un TF32 MMA.
