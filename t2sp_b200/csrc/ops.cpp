@@ -478,7 +478,10 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         p.idesc = idesc_for(arith, in_t, !trans_b, bn);
         // 512-row pair tiles when there are enough of them to fill the SM pairs several times over
         const char* p2env = getenv("T2SP_B200_PAIR2");
-        const bool pair2 = pair && !x3un && (p2env ? atoi(p2env) != 0 : false) && M >= 1024;
+        // (measured: 8192^3 bf16 1436 -> 1536 TFLOP/s, 16384^3 1367 -> 1481; with K = 1024 the tile's
+        // drain no longer hides behind the next tile and the 256-row tiles win, 1191 vs 957)
+        const bool long_k = (K + bk - 1) / bk >= 64;
+        const bool pair2 = pair && !x3un && M >= 1024 && (p2env ? atoi(p2env) != 0 : long_k);
         if (pair) {
             p.tiles_m = pair2 ? (M + 511) / 512 : (M + 255) / 256;
             p.idesc = make_instr_desc(arith == AR_I8 ? 2 : 1, arith == AR_I8 ? 1 : (arith == AR_TF32X3 ? 2 : (in_t == kBF16 ? 1 : 0)),

@@ -211,3 +211,18 @@ def test_blas_sgemm(lib, ta, tb, m, n, k):
     opb = b.T if tb == "T" else b
     truth = alpha * (opa.astype(np.float64) @ opb.astype(np.float64)) + beta * c0.astype(np.float64)
     assert normwise(c, truth) <= TOL_FP32
+
+
+@pytest.mark.parametrize("dtype,M,N,K", [("bf16", 1024, 512, 4096), ("bf16", 1500, 700, 4104), ("i8", 1024, 768, 8192)])
+def test_cta_pair_kernel_512_row_tiles(lib, dtype, M, N, K):
+    """Long-K problems (64 or more k-blocks) with M >= 1024 use 512 x 256 pair tiles: two 128-row
+    sub-tiles per CTA, both TMEM accumulators in one tile."""
+    if dtype == "i8":
+        A, B = O.int8(11, 1, (M, K)), O.int8(11, 2, (K, N))
+        rc, C = call_gemm(A, B, "i8", out_dtype=np.int32)
+        assert rc == 0 and np.array_equal(C, O.gemm_i8(A, B))
+    else:
+        A, B = O.to_bf16(O.uniform(11, 1, (M, K))), O.to_bf16(O.uniform(11, 2, (K, N)))
+        rc, C = call_gemm(A, B, "bf16")
+        assert rc == 0 and not np.isnan(C).any()
+        assert normwise(C, O.gemm_h16(A, B, 0, acc64=True)) <= 1e-5
