@@ -25,6 +25,10 @@ struct DeviceState {
     unsigned* status_dev = nullptr;
     unsigned* status_host = nullptr;  // pinned
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    // copy/compute overlap of large host-buffer calls: two side streams and a pool of ordering events
+    cudaStream_t side[2] = {nullptr, nullptr};
+    cudaEvent_t pool[64] = {};
+    bool side_ready = false;
     // caching allocator: free blocks by size, live blocks by address
     std::multimap<size_t, void*> free_blocks;
     std::map<void*, size_t> live_blocks;
@@ -104,6 +108,23 @@ cudaStream_t rt_stream() {
 unsigned* rt_status_word() { return g_dev[tls().device].status_dev; }
 
 cudaEvent_t rt_event(int which) { return which ? g_dev[tls().device].ev1 : g_dev[tls().device].ev0; }
+
+bool rt_side_resources(cudaStream_t* h2d, cudaStream_t* d2h, cudaEvent_t** pool, int* pool_size) {
+    DeviceState& d = g_dev[tls().device];
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!d.side_ready) {
+        for (int i = 0; i < 2; ++i)
+            if (cudaStreamCreateWithFlags(&d.side[i], cudaStreamNonBlocking) != cudaSuccess) return false;
+        for (int i = 0; i < 64; ++i)
+            if (cudaEventCreateWithFlags(&d.pool[i], cudaEventDisableTiming) != cudaSuccess) return false;
+        d.side_ready = true;
+    }
+    *h2d = d.side[0];
+    *d2h = d.side[1];
+    *pool = d.pool;
+    *pool_size = 64;
+    return true;
+}
 
 int rt_check_status(const char* who) {
     DeviceState& d = g_dev[tls().device];

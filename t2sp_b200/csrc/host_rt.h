@@ -78,5 +78,8 @@ int rt_output_view(halide_buffer_t* b, const char* name, DeviceView* v);
 int rt_finish_output(halide_buffer_t* b, const char* name, DeviceView* v);
 void rt_drop_view(DeviceView* v);
 cudaEvent_t rt_event(int which);
+// Two side streams (host->device, device->host) and a pool of untimed events for overlapping the
+// copies of a large host-buffer call with its kernels. Created on first use; false on failure.
+bool rt_side_resources(cudaStream_t* h2d, cudaStream_t* d2h, cudaEvent_t** pool, int* pool_size);
 
 }  // namespace t2sp

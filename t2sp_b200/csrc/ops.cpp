@@ -321,6 +321,121 @@ int block_k_for(int arith) { return arith == AR_F16 ? 64 : (arith == AR_TF32X3 ?
 using namespace t2sp;
 
 // ======================================================================================= GEMM
+namespace t2sp {
+namespace {
+
+// Large GEMM on host buffers: instead of "copy everything in, compute, copy everything out" the
+// operands travel in slabs (rows of A, columns of B) on a host->device stream, every
+// (row slab, column slab) block of C is computed as soon as its two slabs have arrived, and
+// leaves on a device->host stream while later blocks are still being computed. PCIe is full
+// duplex, so the call approaches max(bytes in, bytes out) / link rate instead of their sum.
+// The blocks are ordinary calls of t2sp_b200_gemm on device-resident sub-buffers (same memory,
+// shifted base, full pitch). Returns 1 if it handled the call, 0 if the caller should take the
+// plain path, or a negative halide error.
+int gemm_host_pipelined(halide_buffer_t* A, halide_buffer_t* B, halide_buffer_t* C, const t2sp_gemm_desc* desc,
+                        int M, int N, int K, bool* done) {
+    *done = false;
+    if (getenv("T2SP_B200_NO_PIPELINE")) return 0;
+    if (desc && (desc->layout || desc->trans_a || desc->trans_b || desc->scale)) return 0;
+    if (A->device || B->device || C->device) return 0;
+    if (A->dim[0].min || A->dim[1].min || B->dim[0].min || B->dim[1].min || C->dim[0].min || C->dim[1].min) return 0;
+    const int es = (A->type.bits + 7) / 8;
+    const double bytes = double(M) * K * es + double(K) * N * es + double(M) * N * 4;
+    if (bytes < 96e6 || M < 2048 || N < 2048) return 0;
+    if ((int64_t(A->dim[1].stride) * es) % 16 || (int64_t(B->dim[1].stride) * es) % 16 || (N * es) % 16) return 0;
+    cudaStream_t s_in, s_out, s_main = rt_stream();
+    cudaEvent_t* ev;
+    int nev;
+    if (!rt_side_resources(&s_in, &s_out, &ev, &nev)) return 0;
+    const int GM = 4, GN = 4;
+    const int ms = ((M + GM - 1) / GM + 511) / 512 * 512, ns = ((N + GN - 1) / GN + 255) / 256 * 256;
+    const int nm = (M + ms - 1) / ms, nn = (N + ns - 1) / ns;
+    if (2 + nm + nn + nm * nn > nev) return 0;
+
+    // dense device copies of A (pitch K), B (pitch N), C (pitch N)
+    DeviceView va, vb, vc;
+    va.ptr = rt_alloc(size_t(M) * K * es); vb.ptr = rt_alloc(size_t(K) * N * es); vc.ptr = rt_alloc(size_t(M) * N * 4);
+    struct Guard { DeviceView *a, *b, *c; ~Guard() { rt_drop_view(a); rt_drop_view(b); rt_drop_view(c); } } guard{&va, &vb, &vc};
+    if (!va.ptr || !vb.ptr || !vc.ptr) return halide_error_code_device_malloc_failed;
+    char* dA = static_cast<char*>(va.ptr);
+    char* dB = static_cast<char*>(vb.ptr);
+    char* dC = static_cast<char*>(vc.ptr);
+
+    cudaEvent_t e_start = ev[0], e_done = ev[1];
+    cudaEvent_t* eA = ev + 2;
+    cudaEvent_t* eB = eA + nm;
+    cudaEvent_t* eC = eB + nn;
+    cudaEventRecord(rt_event(0), s_main);
+    cudaEventRecord(e_start, s_main);
+    cudaStreamWaitEvent(s_in, e_start, 0);
+    cudaStreamWaitEvent(s_out, e_start, 0);
+    bool ok = true;
+    auto copy_a = [&](int i) {
+        const int r0 = i * ms, rows = std::min(ms, M - r0);
+        ok &= cudaMemcpy2DAsync(dA + size_t(r0) * K * es, size_t(K) * es, A->host + size_t(r0) * A->dim[1].stride * es,
+                                size_t(A->dim[1].stride) * es, size_t(K) * es, rows, cudaMemcpyHostToDevice, s_in) == cudaSuccess;
+        cudaEventRecord(eA[i], s_in);
+    };
+    auto copy_b = [&](int j) {
+        const int c0 = j * ns, cols = std::min(ns, N - c0);
+        ok &= cudaMemcpy2DAsync(dB + size_t(c0) * es, size_t(N) * es, B->host + size_t(c0) * es, size_t(B->dim[1].stride) * es,
+                                size_t(cols) * es, K, cudaMemcpyHostToDevice, s_in) == cudaSuccess;
+        cudaEventRecord(eB[j], s_in);
+    };
+    // arrival order: what the first block needs first, then the rest of B, then the rest of A
+    copy_a(0);
+    for (int j = 0; j < nn; ++j) copy_b(j);
+    for (int i = 1; i < nm; ++i) copy_a(i);
+
+    ThreadState& ts = tls();
+    const bool was_async = ts.async;
+    ts.async = true;
+    int rc = 0;
+    for (int i = 0; i < nm && rc == 0; ++i) {
+        const int r0 = i * ms, rows = std::min(ms, M - r0);
+        cudaStreamWaitEvent(s_main, eA[i], 0);
+        for (int j = 0; j < nn && rc == 0; ++j) {
+            const int c0 = j * ns, cols = std::min(ns, N - c0);
+            if (i == 0) cudaStreamWaitEvent(s_main, eB[j], 0);
+            halide_dimension_t da[2] = {{0, K, 1, 0}, {0, rows, K, 0}};
+            halide_dimension_t db[2] = {{0, cols, 1, 0}, {0, K, N, 0}};
+            halide_dimension_t dc[2] = {{0, cols, 1, 0}, {0, rows, N, 0}};
+            halide_buffer_t a = *A, b = *B, c = *C;
+            a.host = b.host = c.host = nullptr;
+            a.flags = b.flags = c.flags = 0;
+            a.dim = da; b.dim = db; c.dim = dc;
+            a.device = reinterpret_cast<uint64_t>(dA + size_t(r0) * K * es);
+            b.device = reinterpret_cast<uint64_t>(dB + size_t(c0) * es);
+            c.device = reinterpret_cast<uint64_t>(dC + (size_t(r0) * N + c0) * 4);
+            a.device_interface = b.device_interface = c.device_interface = t2sp_b200_device_interface();
+            rc = t2sp_b200_gemm(&a, &b, &c, desc);
+            cudaEvent_t done_ij = eC[i * nn + j];
+            cudaEventRecord(done_ij, s_main);
+            cudaStreamWaitEvent(s_out, done_ij, 0);
+            ok &= cudaMemcpy2DAsync(C->host + (size_t(r0) * C->dim[1].stride + c0) * 4, size_t(C->dim[1].stride) * 4,
+                                    dC + (size_t(r0) * N + c0) * 4, size_t(N) * 4, size_t(cols) * 4, rows,
+                                    cudaMemcpyDeviceToHost, s_out) == cudaSuccess;
+        }
+    }
+    ts.async = was_async;
+    cudaEventRecord(e_done, s_out);
+    cudaStreamWaitEvent(s_main, e_done, 0);
+    cudaEventRecord(rt_event(1), s_main);
+    // the copies and kernels above reference the device blocks: finish before they go back to the cache
+    const int src = rt_check_status("gemm");
+    float ms_total = 0.f;
+    if (cudaEventElapsedTime(&ms_total, rt_event(0), rt_event(1)) == cudaSuccess) ts.last_kernel_ns = double(ms_total) * 1e6;
+    if (rc) return rc;
+    if (!ok) { cudaGetLastError(); return halide_error_code_copy_to_device_failed; }
+    if (src) return src;
+    C->flags |= 1u;
+    *done = true;
+    return 0;
+}
+
+}  // namespace
+}  // namespace t2sp
+
 extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buffer_t* C,
                               const t2sp_gemm_desc* desc) {
     int layout = desc ? desc->layout : (C && C->dimensions == 6 ? 1 : 0);
@@ -403,6 +518,11 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
     if (int e = rt_ensure_device()) return e;
     const bool resident = all_resident({A, B, C});
     const bool sync_after = !(resident && tls().async);
+    if (!resident && K > 0) {
+        bool done = false;
+        if (int e = gemm_host_pipelined(A, B, C, desc, M, N, K, &done)) return e;
+        if (done) return 0;
+    }
     Views vw;
     if (int e = rt_input_view(A, "A", &vw.v[vw.n])) return e;
     vw.n++;
