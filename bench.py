@@ -437,8 +437,18 @@ def main():
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (None where no capture has been taken).
 KNOWN_TRAFFIC = {
-    # profiles/gemm_bf16_8192_pair_dram_traffic.md: 1247026944 read + 252846336 written per launch
-    "gemm_bf16_8192": 1499873280,
+    # profiles/gemm_bf16_8192_pair_dram_traffic.md: mean of two launches of the 512 x 256 pair kernel
+    # (837695488 + 237744128 and 849618944 + 235083520 bytes read + written)
+    "gemm_bf16_8192": 1080071040,
+    # small-case captures (one launch each): profiles/gemm_bf16_i8_4096_pair_kernels_full.md and
+    # profiles/fp32_3xtf32_kernels_conv_ttm_mttkrp_capsule_sgemm_full.md
+    "gemm_bf16_4096": 95056896 + 32553472,
+    "gemm_i8_4096": 35462400 + 18725376,
+    "conv_cfg2": 19218944,
+    "ttm_cfg3": 268954368 + 217524736,
+    "mttkrp_cfg3": 537528832 + 3500544,
+    "capsule_cfg4": 21988608 + 3584,
+    "sgemm_1024": 8471808,
 }
 
 if __name__ == "__main__":

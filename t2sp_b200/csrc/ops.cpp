@@ -11,6 +11,7 @@
 
 #include <algorithm>
 #include <string>
+#include <vector>
 
 #include "host_rt.h"
 
@@ -229,6 +230,14 @@ int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool syn
     if (p.group_m <= 0) p.group_m = pair ? 8 : 16;
 #ifdef T2SP_DEBUG_KNOBS
     if (const char* d = getenv("T2SP_B200_DEBUG")) p.debug = atoi(d);
+    static long long* trace_dev = nullptr;
+    const char* trace_path = getenv("T2SP_B200_TRACE");
+    p.trace = nullptr;
+    if (trace_path) {
+        if (!trace_dev) cudaMalloc(&trace_dev, 48 * 1024 * sizeof(long long));
+        cudaMemsetAsync(trace_dev, 0, 48 * 1024 * sizeof(long long), s);
+        p.trace = trace_dev;
+    }
 #endif
     if (const char* g = getenv("T2SP_B200_GROUP_M")) p.group_m = std::max(1, atoi(g));
     const int tiles = p.tiles_m * p.tiles_n;
@@ -244,6 +253,14 @@ int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool syn
     }
     rt_count_launch(1);
     if (sync_after) cudaEventRecord(rt_event(1), s);
+#ifdef T2SP_DEBUG_KNOBS
+    if (trace_path) {
+        std::vector<long long> host(48 * 1024);
+        cudaStreamSynchronize(s);
+        cudaMemcpy(host.data(), trace_dev, host.size() * sizeof(long long), cudaMemcpyDeviceToHost);
+        if (FILE* f = fopen(trace_path, "wb")) { fwrite(host.data(), sizeof(long long), host.size(), f); fclose(f); }
+    }
+#endif
     (void)ts;
     return 0;
 }

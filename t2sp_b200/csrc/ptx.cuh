@@ -44,6 +44,20 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint64_t* bar, uint32_t cta_
         "r"(cta_rank)
         : "memory");
 }
+// Remote arrive with the default semantics (release at CTA scope). Enough where the data the
+// arrival publishes stays inside the arriving CTA (its own shared memory or TMEM, read later by that
+// CTA's tensor core) and only the go-ahead crosses to the peer; the cluster-scope release of
+// mbar_arrive_cluster costs the arriving thread several hundred cycles more.
+__device__ __forceinline__ void mbar_arrive_peer(uint64_t* bar, uint32_t cta_rank) {
+    asm volatile(
+        "{\n"
+        " .reg .b32 ra;\n"
+        " mapa.shared::cluster.u32 ra, %0, %1;\n"
+        " mbarrier.arrive.shared::cluster.b64 _, [ra];\n"
+        "}\n" ::"r"(smem_u32(bar)),
+        "r"(cta_rank)
+        : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(

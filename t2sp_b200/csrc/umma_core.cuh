@@ -18,7 +18,7 @@
 // the hi*hi accumulator run for only kChunkKb k-blocks before the epilogue warps add it,
 // round-to-nearest, into fp32 registers.
 //
-// Every wait on an mbarrier is bounded: after kWaitTimeoutNs the waiting thread raises a
+// Every wait on an mbarrier is bounded: after kWaitTimeoutCycles the waiting thread raises a
 // status bit in global memory, tells the rest of the CTA to stop, and the CTA drains and
 // frees its TMEM before returning.
 #pragma once
@@ -81,13 +81,14 @@ struct AbortCtx {
 
 __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ab, unsigned code) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = ptx::globaltimer_ns();
+    // the SM's own cycle counter: cheap to read, and roles that block at every k-block come here often
+    const long long t0 = clock64();
     uint32_t polls = 0;
     while (true) {
         if (ptx::mbar_try_wait(bar, parity)) return true;
         if ((++polls & 0x3Fu) == 0) {
             if (*ab.flag) return false;
-            if (ptx::globaltimer_ns() - t0 > kWaitTimeoutNs) {
+            if (clock64() - t0 > kWaitTimeoutCycles) {
                 *ab.flag = 1u;
                 atomicOr(ab.status, code);
                 return false;

@@ -57,10 +57,10 @@ cudaError_t launch_pair2(const CoreParams& p, int grid, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
-template <int OP, int UN, int STAGES>
+template <int OP, int UN, int STAGES, int LOSLOTS>
 cudaError_t launch_x3pair(const CoreParams& p, int grid, cudaStream_t stream) {
-    using Cfg = X3PairCfg<OP, UN, STAGES>;
-    auto kern = umma_x3pair_kernel<OP, UN, STAGES>;
+    using Cfg = X3PairCfg<OP, UN, STAGES, LOSLOTS>;
+    auto kern = umma_x3pair_kernel<OP, UN, STAGES, LOSLOTS>;
     static bool configured[16] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -156,16 +156,22 @@ cudaError_t pair2_launch(int arith, int op, const CoreParams& p, int grid, cudaS
 }
 
 cudaError_t x3pair_launch(int op, int un, const CoreParams& p, int grid, cudaStream_t stream) {
-#define T2SP_X3(OPC, UNV, ST) \
-    if (op == OPC && un == UNV) return launch_x3pair<OPC, UNV, ST>(p, grid, stream)
-    T2SP_X3(OP_GEMM, 256, 4);
-    T2SP_X3(OP_GEMM, 128, 5);
-    T2SP_X3(OP_TTM, 256, 4);
-    T2SP_X3(OP_TTM, 128, 5);
-    T2SP_X3(OP_CONV, 256, 4);
-    T2SP_X3(OP_CONV, 128, 5);
-    T2SP_X3(OP_CAPSULE, 256, 4);
-    T2SP_X3(OP_CAPSULE, 128, 5);
+#define T2SP_X3(OPC, UNV, ST, LO) \
+    if (op == OPC && un == UNV) return launch_x3pair<OPC, UNV, ST, LO>(p, grid, stream)
+#ifdef T2SP_DEBUG_KNOBS
+    if (p.debug & 64) {  // timing experiment: the earlier ring split (4 raw stages, 2 lo slots)
+        T2SP_X3(OP_TTM, 256, 4, 2);
+        T2SP_X3(OP_CONV, 256, 4, 2);
+    }
+#endif
+    T2SP_X3(OP_GEMM, 256, 3, 3);
+    T2SP_X3(OP_GEMM, 128, 5, 3);
+    T2SP_X3(OP_TTM, 256, 3, 3);
+    T2SP_X3(OP_TTM, 128, 5, 3);
+    T2SP_X3(OP_CONV, 256, 3, 3);
+    T2SP_X3(OP_CONV, 128, 5, 3);
+    T2SP_X3(OP_CAPSULE, 256, 3, 3);
+    T2SP_X3(OP_CAPSULE, 128, 5, 3);
 #undef T2SP_X3
     return cudaErrorInvalidValue;
 }

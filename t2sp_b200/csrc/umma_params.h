@@ -17,7 +17,7 @@ enum : unsigned {
     ST_TIMEOUT_SPLITTER = 8u,
 };
 
-constexpr unsigned long long kWaitTimeoutNs = 2000000000ull;  // 2 s
+constexpr long long kWaitTimeoutCycles = 4000000000ll;  // SM cycles: 2 s at 1965 MHz, 4 s at 1 GHz
 constexpr int kBlockM = 128;
 constexpr int kMaxDigits = 8;
 constexpr int kCStageBytes = 4 * 4096;  // EPI_TMA: one 32 x 32 fp32 staging tile per epilogue warp
@@ -87,6 +87,16 @@ struct CoreParams {
     int single_pass;  // fp32 data: 1 = one TF32 MMA per product (raw tiles, no hi/lo split)
     int debug;        // only read by builds with T2SP_DEBUG_KNOBS (timing experiments)
     unsigned* status;
+#ifdef T2SP_DEBUG_KNOBS
+    long long* trace;  // per-role cycle stamps of CTAs 0 and 1 (timing experiments), or null
+#endif
 };
+
+#ifdef T2SP_DEBUG_KNOBS
+#define T2SP_TRACE(p, role, idx) \
+    do { if ((p).trace && blockIdx.x < 2 && (idx) < 1024) (p).trace[((role) + 24 * blockIdx.x) * 1024 + (idx)] = clock64(); } while (0)
+#else
+#define T2SP_TRACE(p, role, idx) do { } while (0)
+#endif
 
 }  // namespace t2sp
