@@ -173,16 +173,42 @@ void add_digit2(Digits& d, int div, int mod, int div2, int mod2, long long strid
 }
 void add_digit(Digits& d, int div, int mod, long long stride) { add_digit2(d, div, mod, 1, 1 << 30, stride); }
 
-// fp32 contractions move to CTA pairs (256 x 256 or 256 x 128 tiles) when there are enough such tiles
-// to occupy most SM pairs; returns the pair tile width or 0.
-int x3_pair_width(long long M, int N, int tile_rows) {
+// fp32 contractions move to CTA pairs (256 x 256 or 256 x 128 tiles) when such tiles, cut along the
+// contraction where that pays (x3_pick_splits), occupy most SM pairs; returns the pair tile width or 0.
+int x3_pick_splits(int tiles, int total_kb);
+int x3_pair_width(long long M, int N, int tile_rows, int num_kb) {
     // 256 x 128 pair tiles did not beat the single-CTA kernel (capsule, N = 128: 133 us vs 108 us), so
     // pairs are used for wide outputs only unless $T2SP_B200_PAIR128 asks otherwise.
     if (getenv("T2SP_B200_NO_PAIR") || tile_rows != kBlockM || N < 128) return 0;
     if (N <= 128 && !getenv("T2SP_B200_PAIR128")) return 0;
     const int un = N > 128 ? 256 : 128;
     const long long tiles = ((M + 255) / 256) * ((N + un - 1) / un);
-    return tiles >= core_sm_count() / 4 ? un : 0;
+    if (tiles > (1 << 20)) return un;
+    return tiles * x3_pick_splits(static_cast<int>(tiles), num_kb) >= core_sm_count() / 4 ? un : 0;
+}
+
+// How many ranges to cut the contraction of an fp32 pair launch into: the one that minimises
+// (waves of work items) x (k-blocks per item) plus the cost of the summing pass, counted in
+// k-block times; 1 when the tiles already fill the SM pairs or the contraction is short.
+int x3_pick_splits(int tiles, int total_kb) {
+    if (getenv("T2SP_B200_NO_SPLITK") || total_kb <= 1) return 1;
+    if (const char* f = getenv("T2SP_B200_SPLITK")) {  // forced number of ranges (tests)
+        const int s = std::max(1, std::min(atoi(f), total_kb));
+        const int per = (total_kb + s - 1) / s;
+        return (total_kb + per - 1) / per;
+    }
+    const int pairs = std::max(1, core_sm_count() / 2);
+    int best = 1;
+    long long best_cost = static_cast<long long>((tiles + pairs - 1) / pairs) * total_kb;
+    for (int s = 2; s <= 8; ++s) {
+        const int per = (total_kb + s - 1) / s;
+        if (per < 8) break;
+        const int eff = (total_kb + per - 1) / per;
+        const long long waves = (static_cast<long long>(tiles) * eff + pairs - 1) / pairs;
+        const long long cost = waves * per + 8 + eff;
+        if (cost < best_cost) { best_cost = cost; best = eff; }
+    }
+    return best;
 }
 
 int resolve_precision(int p) {
@@ -241,12 +267,51 @@ int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool syn
 #endif
     if (const char* g = getenv("T2SP_B200_GROUP_M")) p.group_m = std::max(1, atoi(g));
     const int tiles = p.tiles_m * p.tiles_n;
+    // fp32 pair kernel with fewer tiles than SM pairs: cut the contraction into ranges that run as
+    // work items of their own, partial tiles go to scratch and a second kernel sums them in order
+    // and applies the call's real epilogue.
+    float* partials = nullptr;
+    CoreParams final_p;
+    int slab_rows = 0, ld_part = 0;
+    if (pair && arith == AR_TF32X3) {
+        const int splits = x3_pick_splits(tiles, p.total_kb);
+        if (splits > 1) {
+            slab_rows = p.tiles_m * 256;
+            ld_part = p.tiles_n * bn;
+            partials = static_cast<float*>(rt_alloc(size_t(splits) * slab_rows * ld_part * sizeof(float)));
+            if (!partials) return halide_error_code_device_malloc_failed;
+            final_p = p;
+            if (final_p.epi == EPI_TMA) final_p.epi = EPI_ROWMAJOR;
+            uint64_t dims[2] = {uint64_t(ld_part), uint64_t(splits) * slab_rows}, str[2] = {4, uint64_t(ld_part) * 4};
+            uint32_t box[2] = {32, 32};
+            if (!rt_encode_tmap(&p.mapC, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, partials, dims, str, box)) {
+                rt_free(partials);
+                return halide_error_code_device_run_failed;
+            }
+            p.epi = EPI_TMA;
+            p.out = partials;
+            p.ldo = ld_part;
+            p.use_ab = 0;
+            p.num_kb = (p.total_kb + splits - 1) / splits;
+            p.splits = (p.total_kb + p.num_kb - 1) / p.num_kb;
+            p.slab_rows = slab_rows;
+            p.M = p.splits * slab_rows;  // the kernel's store guard now covers the partial slabs
+            p.N = ld_part;
+        }
+    }
+    const int items = tiles * std::max(1, (pair && arith == AR_TF32X3) ? p.splits : 1);
     int grid = std::max(1, std::min(tiles, core_sm_count()));
-    if (pair) grid = 2 * std::max(1, std::min(tiles, core_sm_count() / 2));  // one cluster of 2 CTAs per tile slot
+    if (pair) grid = 2 * std::max(1, std::min(items, core_sm_count() / 2));  // one cluster of 2 CTAs per work item slot
     if (sync_after) cudaEventRecord(rt_event(0), s);
     cudaError_t e = !pair ? core_launch(arith, op, bn, p, grid, s)
                           : (arith == AR_TF32X3 ? x3pair_launch(op, bn, p, grid, s)
                                                 : (pair2 ? pair2_launch(arith, op, p, grid, s) : pair_launch(arith, op, p, grid, s)));
+    if (e == cudaSuccess && partials) {
+        e = splitk_finalize_launch(partials, ld_part, slab_rows, p.splits, final_p, s);
+        rt_count_launch(1);
+    }
+    // stream order keeps the scratch block safe for whoever gets it next on this stream
+    if (partials) rt_free(partials);
     if (e != cudaSuccess) {
         fprintf(stderr, "t2sp_b200: %s: kernel launch failed: %s\n", who, cudaGetErrorString(e));
         return halide_error_code_device_run_failed;
@@ -568,7 +633,7 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         const int bk = block_k_for(arith);
         const int op = trans_b ? OP_TTM : OP_GEMM;  // OP_TTM is the "both operands K-major" loader
         // Large 16-bit / 8-bit problems run on CTA pairs with 256 x 256 tiles.
-        const int x3un = arith == AR_TF32X3 ? x3_pair_width(M, N, kBlockM) : 0;
+        const int x3un = arith == AR_TF32X3 ? x3_pair_width(M, N, kBlockM, (K + bk - 1) / bk) : 0;
         const bool pair = x3un || (arith != AR_TF32X3 && M >= 512 && N >= 512 && !getenv("T2SP_B200_NO_PAIR"));
         const int bn = x3un ? x3un : (pair ? 256 : core_pick_bn(arith, op, N, M));
         int64_t lda = int64_t(A->dim[1].stride) * es;
@@ -745,7 +810,7 @@ extern "C" int t2sp_b200_ttm(halide_buffer_t* a, halide_buffer_t* b, halide_buff
     } else {
         const int prec = resolve_precision(desc ? desc->precision : 0);
         const int M = static_cast<int>(Mrows), N = Kn;
-        const int x3un = x3_pair_width(M, N, kBlockM);
+        const int x3un = x3_pair_width(M, N, kBlockM, (L + 31) / 32);
         const int bn = x3un ? x3un : core_pick_bn(AR_TF32X3, OP_TTM, N, M);
         int64_t lda = int64_t(a->dim[1].stride) * 4, ldb = int64_t(b->dim[1].stride) * 4;
         if (int e = repack_if_unaligned(vw, pa, lda, int64_t(L) * 4, M)) return e;
@@ -911,7 +976,7 @@ extern "C" int t2sp_b200_conv(halide_buffer_t* I, halide_buffer_t* K, halide_buf
     p.single_pass = prec == T2SP_PRECISION_TF32;
     p.cblks = (CI + 31) / 32; p.KY = KY; p.KX = KX; p.stride = 1;
     p.num_kb = KY * KX * p.cblks; p.total_kb = p.num_kb;
-    const int x3un = x3_pair_width(p.M, CO, p.tile_rows);
+    const int x3un = x3_pair_width(p.M, CO, p.tile_rows, p.num_kb);
     if (x3un) bn = x3un;
     p.tiles_m = x3un ? (p.M + 255) / 256 : (p.M + p.tile_rows - 1) / p.tile_rows; p.tiles_n = (CO + bn - 1) / bn;
     p.idesc = x3un ? make_instr_desc(1, 2, false, true, 256, bn) : idesc_for(AR_TF32X3, kF32, true, bn);
@@ -1074,7 +1139,7 @@ extern "C" int t2sp_b200_capsule(halide_buffer_t* P, halide_buffer_t* W, halide_
     p.single_pass = prec == T2SP_PRECISION_TF32;
     p.cblks = (CP + 31) / 32; p.KY = KY; p.KX = KX; p.stride = s; p.CI = CI; p.CII = CII;
     p.num_kb = KY * KX * p.cblks; p.total_kb = p.num_kb;
-    const int x3un = x3_pair_width(p.M, NW, p.tile_rows);
+    const int x3un = x3_pair_width(p.M, NW, p.tile_rows, p.num_kb);
     if (x3un) bn = x3un;
     p.tiles_m = x3un ? (p.M + 255) / 256 : (p.M + p.tile_rows - 1) / p.tile_rows; p.tiles_n = (NW + bn - 1) / bn;
     p.idesc = x3un ? make_instr_desc(1, 2, false, true, 256, bn) : idesc_for(AR_TF32X3, kF32, true, bn);

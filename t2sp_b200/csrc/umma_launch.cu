@@ -82,6 +82,42 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partials, float
     out[i] = acc;
 }
 
+// One thread per row and four consecutive columns; the sum over the slabs runs in slab order.
+__global__ void splitk_finalize_kernel(const float* __restrict__ part, long long ld_part, long long slab_elems, int splits,
+                                       const __grid_constant__ CoreParams f) {
+    const int quads = (f.N + 3) >> 2;
+    const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (idx >= static_cast<long long>(f.M) * quads) return;
+    const int m = static_cast<int>(idx / quads), n = static_cast<int>(idx % quads) * 4;
+    const float* src = part + static_cast<long long>(m) * ld_part + n;
+    float4 acc = *reinterpret_cast<const float4*>(src);
+    for (int s = 1; s < splits; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(src + s * slab_elems);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const float v[4] = {acc.x, acc.y, acc.z, acc.w};
+    float* out = static_cast<float*>(f.out);
+    if (f.epi == EPI_SCATTER) {
+        const long long offm = digits_offset(f.dm, m);
+        for (int j = 0; j < 4; ++j)
+            if (n + j < f.N) out[offm + digits_offset(f.dn, n + j)] = v[j];
+    } else if (f.epi == EPI_COLMAJOR) {
+        for (int j = 0; j < 4; ++j)
+            if (n + j < f.N) out[static_cast<long long>(n + j) * f.ldo + m] = v[j];
+    } else {
+        float* dst = out + static_cast<long long>(m) * f.ldo + n;
+        for (int j = 0; j < 4; ++j) {
+            if (n + j >= f.N) break;
+            if (f.use_ab) {
+                const float a = f.alpha * v[j];
+                dst[j] = f.beta != 0.f ? a + f.beta * dst[j] : a;
+            } else {
+                dst[j] = v[j];
+            }
+        }
+    }
+}
+
 }  // namespace
 
 int core_sm_count() {
@@ -197,6 +233,16 @@ cudaError_t transpose32_launch(const void* src, long long ld_src, void* dst, lon
     dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
     transpose32_kernel<<<grid, block, 0, stream>>>(static_cast<const uint32_t*>(src), ld_src, static_cast<uint32_t*>(dst),
                                                    ld_dst, rows, cols);
+    return cudaGetLastError();
+}
+
+cudaError_t splitk_finalize_launch(const float* partials, long long ld_part, int slab_rows, int splits,
+                                   const CoreParams& final_p, cudaStream_t stream) {
+    const long long work = static_cast<long long>(final_p.M) * ((final_p.N + 3) / 4);
+    if (work <= 0) return cudaSuccess;
+    const int threads = 256;
+    splitk_finalize_kernel<<<static_cast<unsigned>((work + threads - 1) / threads), threads, 0, stream>>>(
+        partials, ld_part, static_cast<long long>(slab_rows) * ld_part, splits, final_p);
     return cudaGetLastError();
 }
 

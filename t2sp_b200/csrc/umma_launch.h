@@ -40,4 +40,11 @@ int core_sm_count();
 cudaError_t reduce_partials_launch(const float* partials, float* out, long long elems, int splits,
                                    cudaStream_t stream);
 
+// Split-K epilogue of the fp32 pair kernel: sums the `splits` partial tiles (row-major slabs of
+// `slab_rows` rows with pitch `ld_part`, slab after slab) in slab order and writes the M x N result
+// through the epilogue `final_p` describes (row-major with optional alpha/beta, column-major, or the
+// mixed-radix scatter of the tiled layouts).
+cudaError_t splitk_finalize_launch(const float* partials, long long ld_part, int slab_rows, int splits,
+                                   const CoreParams& final_p, cudaStream_t stream);
+
 }  // namespace t2sp

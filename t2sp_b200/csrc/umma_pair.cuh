@@ -196,7 +196,7 @@ umma_pair_kernel(const __grid_constant__ CoreParams p) {
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_cluster(&tempty_bar[acc], 0);
+            if (lane == 0) ptx::mbar_arrive_peer(&tempty_bar[acc], 0);
         }
     }
 

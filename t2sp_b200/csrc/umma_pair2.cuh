@@ -184,7 +184,7 @@ umma_pair2_kernel(const __grid_constant__ CoreParams p) {
                 }
                 ptx::tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive_cluster(&tempty_bar[u], 0);
+                if (lane == 0) ptx::mbar_arrive_peer(&tempty_bar[u], 0);
             }
         }
     }

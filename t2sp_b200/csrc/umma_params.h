@@ -82,6 +82,7 @@ struct CoreParams {
     const float* fb;  // b(k,r), k fastest, column pitch ldfb
     long long ldfc, ldfb;
     int L, Kdim, R;
+    int slab_rows;    // fp32 pair kernel, splits > 1: rows between the partial tiles of successive k-ranges
     int use_ab;       // EPI_ROWMAJOR, fp32: out = alpha * acc + beta * out
     float alpha, beta;
     int single_pass;  // fp32 data: 1 = one TF32 MMA per product (raw tiles, no hi/lo split)

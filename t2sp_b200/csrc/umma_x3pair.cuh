@@ -80,7 +80,13 @@ umma_x3pair_kernel(const __grid_constant__ CoreParams p) {
     const int lane = threadIdx.x & 31;
     const uint32_t rank = ptx::cluster_ctarank();
     const AbortCtx ab{abort_slot, p.status};
-    const int num_tiles = p.tiles_m * p.tiles_n;  // tiles of 256 x UN
+    // Work items: tiles of 256 x UN, each cut along the contraction into `splits` ranges of num_kb
+    // k-blocks (the last one may be shorter). Item t is range t % splits of tile t / splits; with
+    // splits > 1 range s writes its partial tile to rows [s * slab_rows, ...) of the output map.
+    const int splits = p.splits > 1 ? p.splits : 1;
+    const int num_tiles = p.tiles_m * p.tiles_n * splits;
+    auto item_kb_begin = [&](int t) { return (t % splits) * p.num_kb; };
+    auto item_kb_count = [&](int t) { return min(p.num_kb, p.total_kb - (t % splits) * p.num_kb); };
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
@@ -114,7 +120,8 @@ umma_x3pair_kernel(const __grid_constant__ CoreParams p) {
         int it = 0;
         bool ok = true;
         for (int t = pair; t < num_tiles && ok; t += num_pairs) {
-            for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+            const int nkb = item_kb_count(t);
+            for (int kb = 0; kb < nkb; ++kb, ++it) {
                 const int s = it % STAGES;
                 const uint32_t ph = (it / STAGES) & 1;
                 const int ls = it % Cfg::kLoSlots;
@@ -162,15 +169,16 @@ umma_x3pair_kernel(const __grid_constant__ CoreParams p) {
             bool ok = true;
             for (int t = pair; t < num_tiles && ok; t += num_pairs) {
                 int mb, nb;
-                tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
+                tile_coords(t / splits, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
                 const int m0 = mb * 256 + static_cast<int>(rank) * kBlockM;
                 const int n0 = nb * UN + static_cast<int>(rank) * Cfg::kHalfN;
+                const int kb_begin = item_kb_begin(t), nkb = item_kb_count(t);
                 // Tiles walk their k-blocks from different starting points (a sum over k either way): CTAs
                 // that run in step would otherwise all ask for the same 128-byte column of every operand
                 // row at the same time, which lands on a fraction of the DRAM channels.
-                const int rot = t % p.num_kb;
-                for (int step = 0; step < p.num_kb; ++step, ++it) {
-                    const int kb = (step + rot) % p.num_kb;
+                const int rot = t % nkb;
+                for (int step = 0; step < nkb; ++step, ++it) {
+                    const int kb = kb_begin + (step + rot) % nkb;
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!bounded_wait(&empty_bar[s], ph ^ 1, ab, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
@@ -233,8 +241,9 @@ umma_x3pair_kernel(const __grid_constant__ CoreParams p) {
             constexpr uint32_t kLboB = Cfg::kBMnMajor ? Cfg::kBoxBytesMn : 16;
             const uint32_t d_main = tmem_base, d_small = tmem_base + UN;
             for (int t = pair; t < num_tiles && ok; t += num_pairs, ++lt) {
-                for (int kb0 = 0; kb0 < p.num_kb && ok; kb0 += Cfg::kChunkKb, ++gch) {
-                    const int kend = min(kb0 + Cfg::kChunkKb, p.num_kb);
+                const int nkb = item_kb_count(t);
+                for (int kb0 = 0; kb0 < nkb && ok; kb0 += Cfg::kChunkKb, ++gch) {
+                    const int kend = min(kb0 + Cfg::kChunkKb, nkb);
                     for (int kb = kb0; kb < kend; ++kb, ++it) {
                         const int s = it % STAGES;
                         const int ls = it % Cfg::kLoSlots;
@@ -303,7 +312,9 @@ umma_x3pair_kernel(const __grid_constant__ CoreParams p) {
         bool ok = true;
         for (int t = pair; t < num_tiles && ok; t += num_pairs, ++lt) {
             int mb, nb;
-            tile_coords(t, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
+            tile_coords(t / splits, p.tiles_m, p.tiles_n, p.group_m, mb, nb);
+            const int nkb = item_kb_count(t);
+            const int row_shift = (t % splits) * p.slab_rows;
             const int row = q * 32 + lane;
             const int m_cta0 = mb * 256 + static_cast<int>(rank) * kBlockM;
             const int m = m_cta0 + row;
@@ -317,7 +328,7 @@ umma_x3pair_kernel(const __grid_constant__ CoreParams p) {
                 __syncwarp();
             }
             uint32_t sum[CW];
-            for (int kb0 = 0; kb0 < p.num_kb && ok; kb0 += Cfg::kChunkKb, ++gch) {
+            for (int kb0 = 0; kb0 < nkb && ok; kb0 += Cfg::kChunkKb, ++gch) {
                 if (!bounded_wait_warp(cfull_bar, gch & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
                 ptx::tc_fence_after_sync();
                 if (threadIdx.x == 128) T2SP_TRACE(p, 5, gch);
@@ -362,7 +373,7 @@ umma_x3pair_kernel(const __grid_constant__ CoreParams p) {
 #pragma unroll
             for (int c = 0; c < CW / 32; ++c) {
                 if (p.epi == EPI_TMA)
-                    store_chunk_tma(p, cstage + e * 4096, m_cta0 + q * 32, n0 + c * 32,
+                    store_chunk_tma(p, cstage + e * 4096, row_shift + m_cta0 + q * 32, n0 + c * 32,
                                     *reinterpret_cast<uint32_t(*)[32]>(&sum[c * 32]), lane);
                 else if (m < p.M)
                     store_row_chunk(p, out32, m, n0 + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sum[c * 32]), offm,

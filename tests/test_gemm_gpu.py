@@ -193,6 +193,53 @@ def test_fp32_cta_pair_kernel(lib, M, N, K, trans_b):
     assert componentwise(cb.keepalive, truth, O.gemm_f32(np.abs(A), np.abs(B), acc64=True)) <= TOL_FP32
 
 
+@pytest.mark.parametrize("M,N,K,trans_b,force", [(1024, 1024, 1024, 0, None), (1024, 1000, 2048, 1, "3"), (2048, 300, 520, 0, "5")])
+def test_fp32_split_k(lib, monkeypatch, M, N, K, trans_b, force):
+    """fp32 problems with fewer 256-row tiles than SM pairs cut the contraction into ranges (work items of
+    their own) and sum the partial tiles in range order in a second kernel; uneven ranges included."""
+    import t2sp_b200
+    from t2sp_b200 import Buffer, GemmDesc
+    if force:
+        monkeypatch.setenv("T2SP_B200_SPLITK", force)
+    A, B = O.uniform(12, 1, (M, K)), O.uniform(12, 2, (K, N))
+    d = GemmDesc()
+    d.trans_b = trans_b
+    Bin = np.ascontiguousarray(B.T) if trans_b else B
+    outs = []
+    for no_split in (False, True):
+        if no_split:
+            monkeypatch.setenv("T2SP_B200_NO_SPLITK", "1")
+        C = np.full((M, N), np.nan, np.float32)
+        cb = Buffer.from_numpy(C)
+        before = lib.t2sp_b200_kernel_launches()
+        assert t2sp_b200.gemm(Buffer.from_numpy(A), Buffer.from_numpy(Bin), cb, d) == 0
+        outs.append((cb.keepalive.copy(), lib.t2sp_b200_kernel_launches() - before))
+    (split, n_split), (whole, n_whole) = outs
+    assert n_split == n_whole + 1, "the split path launches the summing kernel as well"
+    truth = O.gemm_f32(A, B, acc64=True)
+    assert not np.isnan(split).any()
+    assert normwise(split, truth) <= TOL_FP32 and normwise(whole, truth) <= TOL_FP32
+    assert componentwise(split, truth, O.gemm_f32(np.abs(A), np.abs(B), acc64=True)) <= TOL_FP32
+
+
+def test_fp32_split_k_tiled_layout_and_blas_epilogue(lib):
+    """The summing kernel applies the call's own epilogue: the 6-D tiled layout and alpha/beta."""
+    JJJ, III, JJ, II = 8, 16, 2, 4
+    M, N, K = III * II * 32, JJJ * JJ * 32, 1024
+    A, B = O.uniform(13, 1, (M, K)), O.uniform(13, 2, (K, N))
+    rc, C6 = call_gemm(A, B, "f32", tiled=(JJJ, III, JJ, II))
+    assert rc == 0
+    ref6 = O.gemm_tile_layout(O.gemm_f32(A, B, acc64=True), JJJ, III, JJ, II)
+    assert not np.isnan(C6).any()
+    assert normwise(C6, ref6) <= TOL_FP32
+    m = n = k = 1024
+    a, b, c0 = O.uniform(13, 3, (m, k)), O.uniform(13, 4, (k, n)), O.uniform(13, 5, (m, n))
+    c = c0.copy()
+    assert lib.t2sp_b200_sgemm(b"N", b"N", m, n, k, 1.75, a.ctypes.data, 0, b.ctypes.data, 0, -0.5, c.ctypes.data, 0) == 0
+    truth = 1.75 * (a.astype(np.float64) @ b.astype(np.float64)) - 0.5 * c0.astype(np.float64)
+    assert normwise(c, truth) <= TOL_FP32
+
+
 @pytest.mark.parametrize("ta,tb,m,n,k", [("N", "N", 256, 192, 128), ("T", "N", 300, 200, 100), ("N", "T", 128, 260, 64),
                                          ("T", "T", 520, 516, 90), ("N", "N", 2048, 1024, 256)])
 def test_blas_sgemm(lib, ta, tb, m, n, k):
