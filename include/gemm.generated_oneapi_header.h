@@ -23,7 +23,8 @@
 #define T2SP_B200_HAVE_SYCL 1
 #endif
 #endif
-#ifndef T2SP_B200_HAVE_SYCL
+#if !defined(T2SP_B200_HAVE_SYCL) && !defined(T2SP_B200_SYCL_STANDINS)
+#define T2SP_B200_SYCL_STANDINS 1
 namespace sycl { namespace ext { namespace intel {
 struct fpga_selector {};
 struct fpga_emulator_selector {};

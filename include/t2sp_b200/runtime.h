@@ -123,6 +123,17 @@ typedef struct t2sp_capsule_desc {
 } t2sp_capsule_desc;
 int t2sp_b200_capsule(halide_buffer_t *P, halide_buffer_t *W, halide_buffer_t *V, const t2sp_capsule_desc *desc);
 
+/* N-D operands of the reference's oneAPI flow (spatial index innermost):
+ *   conv:    I 4-D (IY, IX, CI, N), K 4-D (KY, KX, CI, CO), O 10-D as above
+ *            (t2s/tests/correctness/oneapi-integration/oneapi-target-5-conv.cpp:58-62, -5-run.cpp:92-103)
+ *   capsule: P 6-D (MK, MX, CI, IY, IX, N), W 6-D (MY, MK, CI, CO, KY, KX),
+ *            V 9-D (COOO, YYY_XXX, YY_XX, Y_X, MY, MX, COO, CO, N)
+ *            (oneapi-target-6-capsule.cpp:57-61, -6-run.cpp:92-99)
+ * Every constant comes from the extents (capsule: stride 2 as in the reference, or 1, whichever
+ * fits V's pixel slots); `precision` is a t2sp_precision. Bounds queries are not answered. */
+int t2sp_b200_conv_nd(halide_buffer_t *I, halide_buffer_t *K, halide_buffer_t *O, int precision);
+int t2sp_b200_capsule_nd(halide_buffer_t *P, halide_buffer_t *W, halide_buffer_t *V, int precision);
+
 /* ---- TTM:  c(i,j,k) = sum_l a(l,i,j) * b(l,k)   (t2s/tests/correctness/buffer/tmm_small.cpp:46-64,
  *                                                  golden t2s/tests/correctness/util/util.h:428-441)
  * a: 3-D (L,I,J), b: 2-D (L,K)

@@ -34,6 +34,11 @@ if [ -f "$ROOT/t2sp_b200/libt2sp_b200.so" ]; then
   # the oneAPI-flavoured GEMM driver (extra selector argument, returns the kernel time)
   ONE="$PERF/oneapi/src"
   $CXX $FLAGS -DTINY -DFPGA_EMULATOR -I $ONE $ONE/oneapi-target-4-run.cpp $LINK -o $ROOT/tests/_bin/oneapi_gemm_tiny
+  # the oneAPI conv and capsule drivers: N-D operand layouts, constants read from the extents
+  # (the copies under correctness/oneapi-integration: their relative include of Roofline.h resolves)
+  ONEC="$REF/t2s/tests/correctness/oneapi-integration"
+  $CXX $FLAGS -DTINY -DFPGA_EMULATOR -I $ONEC $ONEC/oneapi-target-5-run.cpp $LINK -o $ROOT/tests/_bin/oneapi_conv_tiny
+  $CXX $FLAGS -DTINY -DFPGA_EMULATOR -I $ONEC $ONEC/oneapi-target-6-run.cpp $LINK -o $ROOT/tests/_bin/oneapi_capsule_tiny
   # the PEPPERS BLAS driver (sgemm with alpha/beta), A10 release constants with its own 4x4x4 outer loops
   BLAS="$REF/t2s/peppers/blas/level3/gemm/release/a10"
   $CXX $FLAGS -I $BLAS $BLAS/sgemm-run-fpga.cpp $STUBS/blas-gemm.cpp $LINK -o $ROOT/tests/_bin/blas_sgemm_a10

@@ -65,6 +65,9 @@ def lib():
             fn = getattr(L, name)
             fn.argtypes = [P] * nargs
             fn.restype = ctypes.c_int
+        for name in ("t2sp_b200_conv_nd", "t2sp_b200_capsule_nd"):
+            getattr(L, name).argtypes = [P, P, P, ctypes.c_int]
+            getattr(L, name).restype = ctypes.c_int
         for name in ("t2sp_b200_device_malloc", "t2sp_b200_device_free", "t2sp_b200_copy_to_device",
                      "t2sp_b200_copy_to_host", "t2sp_b200_detach_device_ptr"):
             getattr(L, name).argtypes = [P]
@@ -108,6 +111,18 @@ def conv(I, K, O, desc):
 def capsule(P, W, V, desc):
     """int capsule(P, W, V) (t2s/tests/performance/capsule/capsule.cpp:104)."""
     return lib().t2sp_b200_capsule(P.ptr, W.ptr, V.ptr, _opt(desc))
+
+
+def conv_nd(I, K, O, precision=0):
+    """conv on the oneAPI flow's N-D operands I(IY,IX,CI,N), K(KY,KX,CI,CO), 10-D O
+    (t2s/tests/correctness/oneapi-integration/oneapi-target-5-conv.cpp:58-62)."""
+    return lib().t2sp_b200_conv_nd(I.ptr, K.ptr, O.ptr, precision)
+
+
+def capsule_nd(P, W, V, precision=0):
+    """capsule on the oneAPI flow's N-D operands P(MK,MX,CI,IY,IX,N), W(MY,MK,CI,CO,KY,KX), 9-D V
+    (t2s/tests/correctness/oneapi-integration/oneapi-target-6-capsule.cpp:57-61)."""
+    return lib().t2sp_b200_capsule_nd(P.ptr, W.ptr, V.ptr, precision)
 
 
 def ttm(a, b, c, desc=None):

@@ -1311,3 +1311,181 @@ extern "C" int t2sp_b200_mttkrp(halide_buffer_t* a, halide_buffer_t* b, halide_b
     if (int e = rt_finish_output(d, "d", &vw.v[3])) return e;
     return finish_call("mttkrp", "kernel_unloader", sync_after);
 }
+
+// ======================================================================================= N-D FRONTS
+// The oneAPI flow of the reference passes convolution and capsule operands as N-D buffers with the
+// spatial index innermost (oneapi-target-5-conv.cpp:58-62, oneapi-target-6-capsule.cpp:57-61) instead
+// of the flattened channel-innermost 2-D buffers of the OpenCL flow. These entries re-lay the inputs
+// out on the device (one gather kernel per operand, into scratch) and run the 2-D entries on the
+// copies; every constant the 2-D entries take from a descriptor is read off the N-D extents.
+namespace {
+
+struct Scratch {
+    void* p = nullptr;
+    ~Scratch() { if (p) t2sp::rt_free(p); }  // stream order protects later users of the block
+};
+
+// A dense 2-D fp32 buffer that lives on this library's device.
+void make_device_2d(halide_buffer_t* b, halide_dimension_t* dims, void* ptr, int e0, int e1) {
+    memset(b, 0, sizeof(*b));
+    b->type.code = 2; b->type.bits = 32; b->type.lanes = 1;
+    b->dimensions = 2;
+    b->dim = dims;
+    dims[0].min = 0; dims[0].extent = e0; dims[0].stride = 1; dims[0].flags = 0;
+    dims[1].min = 0; dims[1].extent = e1; dims[1].stride = e0; dims[1].flags = 0;
+    t2sp_b200_wrap_device_ptr(b, reinterpret_cast<uint64_t>(ptr));
+}
+
+int nd_common_checks(Arg* args, int n) {
+    if (int e = check_null(args, n)) return e;
+    for (int i = 0; i < n; ++i) {
+        if (buf_is_bounds_query(args[i].b))
+            return halide_error_host_is_null(nullptr, args[i].role().c_str());  // shapes cannot be inferred from nothing
+        if (int e = check_type_dims(args[i], kF32)) return e;
+        if (int e = check_extents_nonneg(args[i])) return e;
+        if (int e = check_sizes(args[i])) return e;
+        if (int e = check_host(args[i])) return e;
+    }
+    return 0;
+}
+
+// Gathers input buffer `b` (N-D, any strides) into dense scratch laid out by `d` (d.sstride is
+// filled in here from b's strides through `src_dim`: destination dimension i reads b's src_dim[i]).
+int gather_to_scratch(halide_buffer_t* b, const char* name, t2sp::PermuteDesc d, const int* src_dim, size_t dst_elems,
+                      Scratch* out) {
+    t2sp::DeviceView v;
+    if (int e = t2sp::rt_input_view(b, name, &v)) return e;
+    out->p = t2sp::rt_alloc(dst_elems * 4);
+    if (!out->p) { t2sp::rt_drop_view(&v); return halide_error_code_device_malloc_failed; }
+    cudaMemsetAsync(out->p, 0, dst_elems * 4, t2sp::rt_stream());
+    for (int i = 0; i < d.nd; ++i) d.sstride[i] = b->dim[src_dim[i]].stride;
+    const uint32_t* src = static_cast<const uint32_t*>(v.ptr) + origin_offset(b);
+    const cudaError_t e = t2sp::permute_copy_launch(src, out->p, d, t2sp::rt_stream());
+    t2sp::rt_count_launch(1);
+    t2sp::rt_drop_view(&v);  // an uploaded copy goes back to the cache; stream order keeps it valid for the gather
+    return e == cudaSuccess ? 0 : halide_error_code_device_run_failed;
+}
+
+}  // namespace
+
+extern "C" int t2sp_b200_conv_nd(halide_buffer_t* I, halide_buffer_t* K, halide_buffer_t* O, int precision) {
+    Arg args[3] = {{I, "I", false, 4}, {K, "K", false, 4}, {O, "O", true, 10}};
+    if (int e = nd_common_checks(args, 3)) return e;
+    const int IY = I->dim[0].extent, IX = I->dim[1].extent, CI = I->dim[2].extent, N = I->dim[3].extent;
+    const int KY = K->dim[0].extent, KX = K->dim[1].extent, CO = K->dim[3].extent;
+    if (K->dim[2].extent != CI) return constraint("K.extent.2", K->dim[2].extent, "I.extent.2", CI);
+    t2sp_conv_desc d;
+    memset(&d, 0, sizeof(d));
+    d.layout = 1;
+    d.COOO = O->dim[0].extent; d.YYY = O->dim[1].extent; d.XXX = O->dim[2].extent; d.COO = O->dim[3].extent;
+    d.YY = O->dim[4].extent; d.XX = O->dim[5].extent; d.Y = O->dim[6].extent; d.X = O->dim[7].extent;
+    d.OY = d.YYY * d.YY * d.Y; d.OX = d.XXX * d.XX * d.X;
+    d.KY = KY; d.KX = KX; d.CO = CO; d.precision = precision;
+    if (IY != d.OY + KY - 1) return constraint("I.extent.0", IY, "OY+KY-1", d.OY + KY - 1);
+    if (IX != d.OX + KX - 1) return constraint("I.extent.1", IX, "OX+KX-1", d.OX + KX - 1);
+    if (d.COOO * d.COO * O->dim[8].extent != CO) return constraint("COOO*COO*CO", d.COOO * d.COO * O->dim[8].extent, "K.extent.3", CO);
+    if (O->dim[9].extent != N) return constraint("O.extent.9", O->dim[9].extent, "I.extent.3", N);
+    if (CO % 4) return constraint("K.extent.3", CO, "multiple of 4", (CO + 3) / 4 * 4);
+    if (N == 0 || CO == 0 || d.OY == 0 || d.OX == 0) return 0;
+    if (int e = t2sp::rt_ensure_device()) return e;
+    const int CIp = (CI + 3) / 4 * 4;  // zero channels up to the 16-byte pitch TMA needs
+    d.CI = CIp;
+    Scratch si, sk;
+    {
+        t2sp::PermuteDesc pd;
+        memset(&pd, 0, sizeof(pd));
+        pd.nd = 4;  // destination order (ci, n, iy, ix)
+        const int ext[4] = {CI, N, IY, IX}, src[4] = {2, 3, 0, 1};
+        const long long ds[4] = {1, CIp, (long long)CIp * N, (long long)CIp * N * IY};
+        for (int i = 0; i < 4; ++i) { pd.ext[i] = ext[i]; pd.dstride[i] = ds[i]; }
+        if (int e = gather_to_scratch(I, "I", pd, src, size_t(CIp) * N * IY * IX, &si)) return e;
+    }
+    {
+        t2sp::PermuteDesc pd;
+        memset(&pd, 0, sizeof(pd));
+        pd.nd = 4;  // destination order (co, kx, ci, ky)
+        const int ext[4] = {CO, KX, CI, KY}, src[4] = {3, 1, 2, 0};
+        const long long ds[4] = {1, CO, (long long)CO * KX, (long long)CO * KX * CIp};
+        for (int i = 0; i < 4; ++i) { pd.ext[i] = ext[i]; pd.dstride[i] = ds[i]; }
+        if (int e = gather_to_scratch(K, "K", pd, src, size_t(CO) * KX * CIp * KY, &sk)) return e;
+    }
+    halide_buffer_t i2, k2;
+    halide_dimension_t di[2], dk[2];
+    make_device_2d(&i2, di, si.p, CIp * N, IY * IX);
+    make_device_2d(&k2, dk, sk.p, CO * KX, CIp * KY);
+    return t2sp_b200_conv(&i2, &k2, O, &d);
+}
+
+extern "C" int t2sp_b200_capsule_nd(halide_buffer_t* P, halide_buffer_t* W, halide_buffer_t* V, int precision) {
+    Arg args[3] = {{P, "P", false, 6}, {W, "W", false, 6}, {V, "V", true, 9}};
+    if (int e = nd_common_checks(args, 3)) return e;
+    const int MK = P->dim[0].extent, MX = P->dim[1].extent, CI = P->dim[2].extent, IY = P->dim[3].extent,
+              IX = P->dim[4].extent, N = P->dim[5].extent;
+    const int MY = W->dim[0].extent, CO = W->dim[3].extent, KY = W->dim[4].extent, KX = W->dim[5].extent;
+    if (W->dim[1].extent != MK) return constraint("W.extent.1", W->dim[1].extent, "P.extent.0", MK);
+    if (W->dim[2].extent != CI) return constraint("W.extent.2", W->dim[2].extent, "P.extent.2", CI);
+    t2sp_capsule_desc d;
+    memset(&d, 0, sizeof(d));
+    d.layout = 1;
+    d.COOO = V->dim[0].extent; d.YYY_XXX = V->dim[1].extent; d.YY_XX = V->dim[2].extent; d.Y_X = V->dim[3].extent;
+    d.COO = V->dim[6].extent;
+    d.CI = CI; d.CII = CI; d.CO = CO; d.KY = KY; d.KX = KX; d.MY = MY; d.MX = MX; d.MK = MK; d.NN = 1;
+    d.precision = precision;
+    if (V->dim[4].extent != MY) return constraint("V.extent.4", V->dim[4].extent, "W.extent.0", MY);
+    if (V->dim[5].extent != MX) return constraint("V.extent.5", V->dim[5].extent, "P.extent.1", MX);
+    if (d.COOO * d.COO * V->dim[7].extent != CO) return constraint("COOO*COO*CO", d.COOO * d.COO * V->dim[7].extent, "W.extent.3", CO);
+    if (V->dim[8].extent != N) return constraint("V.extent.8", V->dim[8].extent, "P.extent.5", N);
+    // The reference's capsule layer strides by 2 (capsule.cpp:40-41); a stride-1 shape is accepted as well.
+    // The stride is the one whose output size fits the pixel slots of V.
+    const long long slots = (long long)d.YYY_XXX * d.YY_XX * d.Y_X;
+    d.stride = 0;
+    for (int s = 2; s >= 1 && !d.stride; --s) {
+        const int oy = (IY - KY + s) / s, ox = (IX - KX + s) / s;
+        if (oy > 0 && ox > 0 && (IY - KY) % s == 0 && (IX - KX) % s == 0 && (long long)oy * ox <= slots &&
+            (long long)oy * ox > slots - d.YYY_XXX) {
+            d.stride = s; d.OY = oy; d.OX = ox;
+        }
+    }
+    if (!d.stride) return constraint("YYY_XXX*YY_XX*Y_X", (int)slots, "OY*OX", ((IY - KY + 2) / 2) * ((IX - KX + 2) / 2));
+    if ((CI * MK) % 4) return constraint("P.extent.2*P.extent.0", CI * MK, "multiple of 4", (CI * MK + 3) / 4 * 4);
+    if ((CO * MY) % 4) return constraint("W.extent.3*W.extent.0", CO * MY, "multiple of 4", (CO * MY + 3) / 4 * 4);
+    if (N == 0 || CO == 0) return 0;
+    if (int e = t2sp::rt_ensure_device()) return e;
+    Scratch sp, sw;
+    {
+        t2sp::PermuteDesc pd;
+        memset(&pd, 0, sizeof(pd));
+        pd.nd = 6;  // destination order (ci, mk, mx, iy, ix, n)
+        const int ext[6] = {CI, MK, MX, IY, IX, N}, src[6] = {2, 0, 1, 3, 4, 5};
+        long long s = 1;
+        for (int i = 0; i < 6; ++i) { pd.ext[i] = ext[i]; pd.dstride[i] = s; s *= ext[i]; }
+        if (int e = gather_to_scratch(P, "P", pd, src, size_t(s), &sp)) return e;
+    }
+    {
+        t2sp::PermuteDesc pd;
+        memset(&pd, 0, sizeof(pd));
+        pd.nd = 6;  // destination order (co, my, ci, ky, kx, mk): the 2-D layout with CII = CI
+        const int ext[6] = {CO, MY, CI, KY, KX, MK}, src[6] = {3, 0, 2, 4, 5, 1};
+        long long s = 1;
+        for (int i = 0; i < 6; ++i) { pd.ext[i] = ext[i]; pd.dstride[i] = s; s *= ext[i]; }
+        if (int e = gather_to_scratch(W, "W", pd, src, size_t(s), &sw)) return e;
+    }
+    halide_buffer_t p2, w2;
+    halide_dimension_t dp[2], dw[2];
+    make_device_2d(&p2, dp, sp.p, CI * MK * MX, IY * IX * N);
+    make_device_2d(&w2, dw, sw.p, CO * MY, CI * KY * KX * MK);
+    // V as the 10-D buffer of the OpenCL flow: a unit NN dimension goes in before CO
+    halide_buffer_t v10 = *V;
+    halide_dimension_t dv[10];
+    for (int i = 0; i < 7; ++i) dv[i] = V->dim[i];
+    dv[7].min = 0; dv[7].extent = 1; dv[7].stride = V->dim[7].stride; dv[7].flags = 0;
+    dv[8] = V->dim[7];
+    dv[9] = V->dim[8];
+    v10.dimensions = 10;
+    v10.dim = dv;
+    const int rc = t2sp_b200_capsule(&p2, &w2, &v10, &d);
+    V->flags = v10.flags;
+    V->device = v10.device;
+    V->device_interface = v10.device_interface;
+    return rc;
+}

@@ -118,6 +118,23 @@ __global__ void splitk_finalize_kernel(const float* __restrict__ part, long long
     }
 }
 
+__global__ void permute_copy_kernel(const uint32_t* __restrict__ src, uint32_t* __restrict__ dst,
+                                    const __grid_constant__ PermuteDesc d, long long total) {
+    long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (idx >= total) return;
+    long long so = 0, dof = 0;
+#pragma unroll
+    for (int i = 0; i < 6; ++i) {
+        if (i < d.nd) {
+            const int c = static_cast<int>(idx % d.ext[i]);
+            idx /= d.ext[i];
+            so += c * d.sstride[i];
+            dof += c * d.dstride[i];
+        }
+    }
+    dst[dof] = src[so];
+}
+
 }  // namespace
 
 int core_sm_count() {
@@ -243,6 +260,16 @@ cudaError_t splitk_finalize_launch(const float* partials, long long ld_part, int
     const int threads = 256;
     splitk_finalize_kernel<<<static_cast<unsigned>((work + threads - 1) / threads), threads, 0, stream>>>(
         partials, ld_part, static_cast<long long>(slab_rows) * ld_part, splits, final_p);
+    return cudaGetLastError();
+}
+
+cudaError_t permute_copy_launch(const void* src, void* dst, const PermuteDesc& d, cudaStream_t stream) {
+    long long total = 1;
+    for (int i = 0; i < d.nd; ++i) total *= d.ext[i];
+    if (total <= 0) return cudaSuccess;
+    const int threads = 256;
+    permute_copy_kernel<<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0, stream>>>(
+        static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), d, total);
     return cudaGetLastError();
 }
 

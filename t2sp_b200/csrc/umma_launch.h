@@ -47,4 +47,15 @@ cudaError_t reduce_partials_launch(const float* partials, float* out, long long 
 cudaError_t splitk_finalize_launch(const float* partials, long long ld_part, int slab_rows, int splits,
                                    const CoreParams& final_p, cudaStream_t stream);
 
+// Copies a tensor of up to 6 dimensions of 32-bit elements between two layouts: element
+// (c0..c5) moves from src[sum c_d * sstride[d]] to dst[sum c_d * dstride[d]] (strides in elements).
+// Dimension 0 should be the destination's innermost so that the writes coalesce.
+struct PermuteDesc {
+    int nd;
+    int ext[6];
+    long long sstride[6];
+    long long dstride[6];
+};
+cudaError_t permute_copy_launch(const void* src, void* dst, const PermuteDesc& d, cudaStream_t stream);
+
 }  // namespace t2sp

@@ -31,7 +31,9 @@ def test_headers_compile(lang, tmp_path):
     src = tmp_path / ("t." + ("c" if lang == "c" else "cpp"))
     src.write_text('#include "t2sp_b200/runtime.h"\n#include "gemm-interface.h"\n#include "conv-interface.h"\n'
                    '#include "capsule-interface.h"\n#include "host.h"\n#include "ttm-interface.h"\n'
-                   '#include "mttkrp-interface.h"\nint main(void) { return sizeof(halide_buffer_t) == 56 ? 0 : 1; }\n')
+                   '#include "mttkrp-interface.h"\n' + ('' if lang == "c" else '#include "gemm.generated_oneapi_header.h"\n'
+                   '#include "conv.generated_oneapi_header.h"\n#include "capsule.generated_oneapi_header.h"\n') +
+                   'int main(void) { return sizeof(halide_buffer_t) == 56 ? 0 : 1; }\n')
     exe = tmp_path / "t"
     cc = "gcc" if lang == "c" else "g++"
     subprocess.run([cc, "-I", INC, str(src), "-o", str(exe)], check=True, capture_output=True)

@@ -145,3 +145,83 @@ def test_capsule_tiled_output(lib, tiles, NN, CI, CII, CO):
     COOO, YYY_XXX, YY_XX, Y_X, COO = tiles
     ref10 = O.capsule_tile_layout(truth, N, NN, COOO, COO, CO // (COOO * COO), YYY_XXX, YY_XX, Y_X, 4, 4, OY, OX)
     assert normwise(out, ref10) <= TOL_FP32
+
+
+# ---------------------------------------------------------------- oneAPI-flow N-D operand layouts
+def _tile10(out, COOO, YYY, XXX, COO, YY, XX, Y, X):
+    """out[n, co, ox, oy] -> the 10-D o(COOO,YYY,XXX,COO,YY,XX,Y,X,CO,N) (numpy axes reversed)."""
+    N, CO = out.shape[:2]
+    t = out.reshape(N, CO // (COOO * COO), COO, COOO, X, XX, XXX, Y, YY, YYY)
+    #               n  co_o               coo  cooo  x  xx  xxx  y  yy  yyy
+    return np.ascontiguousarray(t.transpose(0, 1, 4, 7, 5, 8, 2, 6, 9, 3))
+
+
+@pytest.mark.parametrize("N,CI,CO,KY,KX,tiles", [
+    (4, 16, 64, 3, 3, (4, 4, 4, 4, 1, 1, 1, 1)),      # oneapi-target-5-parameters.h, TINY
+    (3, 10, 24, 3, 2, (4, 2, 3, 2, 2, 1, 2, 2)),      # channels not a multiple of 4: zero-padded in the device copy
+    (16, 64, 256, 3, 3, (8, 7, 7, 4, 2, 2, 1, 1)),    # wide enough for the CTA-pair kernel
+])
+def test_conv_nd_layout(lib, N, CI, CO, KY, KX, tiles):
+    """I(IY,IX,CI,N), K(KY,KX,CI,CO) as the oneAPI flow passes them
+    (t2s/tests/correctness/oneapi-integration/oneapi-target-5-run.cpp:92-117)."""
+    COOO, YYY, XXX, COO, YY, XX, Y, X = tiles
+    OY, OX = YYY * YY * Y, XXX * XX * X
+    IY, IX = OY + KY - 1, OX + KX - 1
+    I = O.uniform(21, 1, (N, CI, IX, IY))
+    K = O.normal(21, 2, (CO, CI, KX, KY), (1.0 / (KY * KX * CI)) ** 0.5)
+    out = np.full((N, CO // (COOO * COO), X, Y, XX, YY, COO, XXX, YYY, COOO), np.nan, np.float32)
+    ob = Buffer.from_numpy(out)
+    assert t2sp_b200.conv_nd(Buffer.from_numpy(I), Buffer.from_numpy(K), ob) == 0
+    truth = np.zeros((N, CO, OX, OY))
+    I64, K64 = I.astype(np.float64), K.astype(np.float64)
+    for kx in range(KX):
+        for ky in range(KY):
+            truth += np.einsum("ncxy,oc->noxy", I64[:, :, kx:kx + OX, ky:ky + OY], K64[:, :, kx, ky])
+    want = _tile10(truth, *tiles)
+    got = ob.keepalive
+    assert not np.isnan(got).any()
+    assert normwise(got, want) <= TOL_FP32
+
+
+def test_conv_nd_rejects_inconsistent_extents(lib):
+    I = np.zeros((2, 8, 6, 6), np.float32)
+    K = np.zeros((8, 8, 3, 3), np.float32)
+    out = np.zeros((2, 1, 1, 1, 1, 1, 2, 4, 5, 4), np.float32)  # OY = 5 but IY - KY + 1 = 4
+    assert t2sp_b200.conv_nd(Buffer.from_numpy(I), Buffer.from_numpy(K), Buffer.from_numpy(out)) == -8
+    assert t2sp_b200.lib().t2sp_b200_conv_nd(None, None, None, 0) == -12
+
+
+@pytest.mark.parametrize("N,CI,CO,OY,OX,s,vt", [
+    (4, 16, 16, 7, 7, 2, (4, 7, 1, 7, 4)),    # oneapi-target-6-parameters.h, TINY (COOO, YYY_XXX, YY_XX, Y_X, COO)
+    (2, 8, 32, 6, 5, 1, (8, 6, 5, 1, 2)),     # stride 1, as BASELINE's capsule configuration
+])
+def test_capsule_nd_layout(lib, N, CI, CO, OY, OX, s, vt):
+    """P(MK,MX,CI,IY,IX,N), W(MY,MK,CI,CO,KY,KX), 9-D V as the oneAPI flow passes them
+    (t2s/tests/correctness/oneapi-integration/oneapi-target-6-run.cpp:92-173)."""
+    MY = MX = MK = 4
+    KY = KX = 3
+    COOO, YYY_XXX, YY_XX, Y_X, COO = vt
+    IY, IX = s * OY + KY - s, s * OX + KX - s
+    P = O.normal(22, 1, (N, IX, IY, CI, MX, MK), 0.1)
+    W = O.normal(22, 2, (KX, KY, CO, CI, MK, MY), 0.1)
+    V = np.full((N, CO // (COOO * COO), COO, MX, MY, Y_X, YY_XX, YYY_XXX, COOO), np.nan, np.float32)
+    vb = Buffer.from_numpy(V)
+    assert t2sp_b200.capsule_nd(Buffer.from_numpy(P), Buffer.from_numpy(W), vb) == 0
+    P64, W64 = P.astype(np.float64), W.astype(np.float64)
+    truth = np.zeros((N, CO, OX, OY, MX, MY))  # [n, co, ox, oy, mx, my]
+    for kx in range(KX):
+        for ky in range(KY):
+            Ps = P64[:, kx:kx + s * OX:s, ky:ky + s * OY:s]  # [n, ox, oy, ci, mx, mk]
+            truth += np.einsum("nxycmk,ockj->noxymj", Ps, W64[kx, ky])  # m = mx, k = mk, j = my
+    got = vb.keepalive
+    assert not np.isnan(got).any()
+    # pixel slot p = yyy_xxx + YYY_XXX*yy_xx + YYY_XXX*YY_XX*y_x holds (oy, ox) = (p % OY, p / OY)
+    want = np.zeros_like(got, dtype=np.float64)
+    for p in range(YYY_XXX * YY_XX * Y_X):
+        if p >= OY * OX:
+            continue
+        oy, ox = p % OY, p // OY
+        a, b, c = p % YYY_XXX, (p // YYY_XXX) % YY_XX, p // (YYY_XXX * YY_XX)
+        blk = truth[:, :, ox, oy].reshape(N, CO // (COOO * COO), COO, COOO, MX, MY)  # [n, co_o, coo, cooo, mx, my]
+        want[:, :, :, :, :, c, b, a, :] = blk.transpose(0, 1, 2, 4, 5, 3)
+    assert normwise(got, want) <= TOL_FP32
