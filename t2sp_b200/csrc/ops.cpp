@@ -464,40 +464,51 @@ int gemm_host_pipelined(halide_buffer_t* A, halide_buffer_t* B, halide_buffer_t*
                                 size_t(cols) * es, K, cudaMemcpyHostToDevice, s_in) == cudaSuccess;
         cudaEventRecord(eB[j], s_in);
     };
-    // arrival order: what the first block needs first, then the rest of B, then the rest of A
-    copy_a(0);
-    for (int j = 0; j < nn; ++j) copy_b(j);
-    for (int i = 1; i < nm; ++i) copy_a(i);
-
+    // Arrival order: A and B slabs alternate (A0, B0, B1, A1, B2, A2, ...), so that after every slab
+    // some new C blocks have both of their operands on the device; each of them is launched at once and
+    // its result starts downstream while the next slabs are still coming up.
     ThreadState& ts = tls();
     const bool was_async = ts.async;
     ts.async = true;
     int rc = 0;
-    for (int i = 0; i < nm && rc == 0; ++i) {
-        const int r0 = i * ms, rows = std::min(ms, M - r0);
-        cudaStreamWaitEvent(s_main, eA[i], 0);
-        for (int j = 0; j < nn && rc == 0; ++j) {
-            const int c0 = j * ns, cols = std::min(ns, N - c0);
-            if (i == 0) cudaStreamWaitEvent(s_main, eB[j], 0);
-            halide_dimension_t da[2] = {{0, K, 1, 0}, {0, rows, K, 0}};
-            halide_dimension_t db[2] = {{0, cols, 1, 0}, {0, K, N, 0}};
-            halide_dimension_t dc[2] = {{0, cols, 1, 0}, {0, rows, N, 0}};
-            halide_buffer_t a = *A, b = *B, c = *C;
-            a.host = b.host = c.host = nullptr;
-            a.flags = b.flags = c.flags = 0;
-            a.dim = da; b.dim = db; c.dim = dc;
-            a.device = reinterpret_cast<uint64_t>(dA + size_t(r0) * K * es);
-            b.device = reinterpret_cast<uint64_t>(dB + size_t(c0) * es);
-            c.device = reinterpret_cast<uint64_t>(dC + (size_t(r0) * N + c0) * 4);
-            a.device_interface = b.device_interface = c.device_interface = t2sp_b200_device_interface();
-            rc = t2sp_b200_gemm(&a, &b, &c, desc);
-            cudaEvent_t done_ij = eC[i * nn + j];
-            cudaEventRecord(done_ij, s_main);
-            cudaStreamWaitEvent(s_out, done_ij, 0);
-            ok &= cudaMemcpy2DAsync(C->host + (size_t(r0) * C->dim[1].stride + c0) * 4, size_t(C->dim[1].stride) * 4,
-                                    dC + (size_t(r0) * N + c0) * 4, size_t(N) * 4, size_t(cols) * 4, rows,
-                                    cudaMemcpyDeviceToHost, s_out) == cudaSuccess;
+    std::vector<char> launched(size_t(nm) * nn, 0);
+    int ua = 0, ub = 0;  // slabs of A / B uploaded so far
+    auto launch_ready = [&]() {
+        for (int i = 0; i < ua && rc == 0; ++i) {
+            const int r0 = i * ms, rows = std::min(ms, M - r0);
+            for (int j = 0; j < ub && rc == 0; ++j) {
+                if (launched[size_t(i) * nn + j]) continue;
+                launched[size_t(i) * nn + j] = 1;
+                const int c0 = j * ns, cols = std::min(ns, N - c0);
+                cudaStreamWaitEvent(s_main, eA[i], 0);
+                cudaStreamWaitEvent(s_main, eB[j], 0);
+                halide_dimension_t da[2] = {{0, K, 1, 0}, {0, rows, K, 0}};
+                halide_dimension_t db[2] = {{0, cols, 1, 0}, {0, K, N, 0}};
+                halide_dimension_t dc[2] = {{0, cols, 1, 0}, {0, rows, N, 0}};
+                halide_buffer_t a = *A, b = *B, c = *C;
+                a.host = b.host = c.host = nullptr;
+                a.flags = b.flags = c.flags = 0;
+                a.dim = da; b.dim = db; c.dim = dc;
+                a.device = reinterpret_cast<uint64_t>(dA + size_t(r0) * K * es);
+                b.device = reinterpret_cast<uint64_t>(dB + size_t(c0) * es);
+                c.device = reinterpret_cast<uint64_t>(dC + (size_t(r0) * N + c0) * 4);
+                a.device_interface = b.device_interface = c.device_interface = t2sp_b200_device_interface();
+                rc = t2sp_b200_gemm(&a, &b, &c, desc);
+                cudaEvent_t done_ij = eC[i * nn + j];
+                cudaEventRecord(done_ij, s_main);
+                cudaStreamWaitEvent(s_out, done_ij, 0);
+                ok &= cudaMemcpy2DAsync(C->host + (size_t(r0) * C->dim[1].stride + c0) * 4, size_t(C->dim[1].stride) * 4,
+                                        dC + (size_t(r0) * N + c0) * 4, size_t(N) * 4, size_t(cols) * 4, rows,
+                                        cudaMemcpyDeviceToHost, s_out) == cudaSuccess;
+            }
         }
+    };
+    while ((ua < nm || ub < nn) && rc == 0) {
+        // keep the two counts within one of each other, A first, then two of B, then alternate
+        const bool take_a = ub >= nn || (ua < nm && ua <= ub - (ua ? 1 : 0));
+        if (take_a) copy_a(ua++);
+        else copy_b(ub++);
+        launch_ready();
     }
     ts.async = was_async;
     cudaEventRecord(e_done, s_out);
