@@ -52,14 +52,17 @@ struct CoreCfg {
     static constexpr int kStageBytes = kABytes + kBBytes;    // one ring stage: [A | B] as TMA delivers them
     // 3xTF32: the raw fp32 tiles double as the hi operands (the tensor core reads only the top 19
     // bits of each word); the lo tiles live in a short ring of their own, [A_lo | B_lo] per slot.
-    static constexpr int kLoSlots = kX3 ? (OP == OP_MTTKRP ? (BN <= 64 ? 4 : 3) : 2) : 0;
+    static constexpr int kLoSlots = kX3 ? (OP == OP_MTTKRP ? (BN <= 64 ? 4 : 3) : 3) : 0;
     // MTTKRP writes its partial slabs column-major and never stages an output tile: its staging
     // bytes go to a deeper lo ring instead.
     static constexpr int kCStage = (OP == OP_MTTKRP) ? 0 : kCStageBytes;
     static constexpr int kBoxBytesMn = AT::kBlockK * 128;           // one MN-major box: kBlockK rows of 128 B
     static constexpr int kBoxesMn = kBBytes / kBoxBytesMn;          // boxes per MN-major B tile
     static constexpr int kBoxElemsMn = 128 / AT::kElem;             // N elements per MN-major box
-    static constexpr int kWarps = 2 + 4 + (kX3 ? 4 : 0);
+    // split warps: six halve the time a k-block's lo tiles take (the MTTKRP tile generator is written for four)
+    static constexpr int kSplitWarps = kX3 ? (OP == OP_MTTKRP ? 4 : 6) : 0;
+    static constexpr int kSplitThreads = kSplitWarps * 32;
+    static constexpr int kWarps = 2 + 4 + kSplitWarps;
     static constexpr int kThreads = kWarps * 32;
     // 16-bit / int8: two whole-tile accumulators (tile t+1 accumulates while tile t drains).
     // 3xTF32: two chunk accumulators for the hi*hi products plus two (one per tile in flight) for the
@@ -219,7 +222,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
             ptx::mbar_init(&empty_bar[s], 1);
         }
         for (int a = 0; a < 4; ++a) {
-            ptx::mbar_init(&ready_bar[a], 128);
+            ptx::mbar_init(&ready_bar[a], Cfg::kX3 ? Cfg::kSplitThreads : 1);
             ptx::mbar_init(&lofree_bar[a], 1);
         }
         for (int a = 0; a < 2; ++a) {
@@ -562,7 +565,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                     // tiles are left as they are: the tensor core ignores their low 13 mantissa bits.
                     if (!p.single_pass) {
 #pragma unroll 4
-                        for (int off = st * 16; off < kSplitBytes; off += 128 * 16) {
+                        for (int off = st * 16; off < kSplitBytes; off += Cfg::kSplitThreads * 16) {
                             const float4 v = *reinterpret_cast<const float4*>(hi + off);
                             float4 l;
                             l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);

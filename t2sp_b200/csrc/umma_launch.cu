@@ -178,14 +178,14 @@ cudaError_t core_launch(int arith, int op, int bn, const CoreParams& p, int grid
     T2SP_CASE(AR_I8, OP_GEMM, 128, 6);
     T2SP_CASE(AR_I8, OP_TTM, 256, 4);
     T2SP_CASE(AR_I8, OP_TTM, 128, 6);
-    T2SP_CASE(AR_TF32X3, OP_GEMM, 128, 4);
-    T2SP_CASE(AR_TF32X3, OP_GEMM, 64, 6);
-    T2SP_CASE(AR_TF32X3, OP_TTM, 128, 4);
-    T2SP_CASE(AR_TF32X3, OP_TTM, 64, 6);
-    T2SP_CASE(AR_TF32X3, OP_CONV, 128, 4);
-    T2SP_CASE(AR_TF32X3, OP_CONV, 64, 6);
-    T2SP_CASE(AR_TF32X3, OP_CAPSULE, 128, 4);
-    T2SP_CASE(AR_TF32X3, OP_CAPSULE, 64, 6);
+    T2SP_CASE(AR_TF32X3, OP_GEMM, 128, 3);
+    T2SP_CASE(AR_TF32X3, OP_GEMM, 64, 5);
+    T2SP_CASE(AR_TF32X3, OP_TTM, 128, 3);
+    T2SP_CASE(AR_TF32X3, OP_TTM, 64, 5);
+    T2SP_CASE(AR_TF32X3, OP_CONV, 128, 3);
+    T2SP_CASE(AR_TF32X3, OP_CONV, 64, 5);
+    T2SP_CASE(AR_TF32X3, OP_CAPSULE, 128, 3);
+    T2SP_CASE(AR_TF32X3, OP_CAPSULE, 64, 5);
     T2SP_CASE(AR_TF32X3, OP_MTTKRP, 64, 5);
     T2SP_CASE(AR_TF32X3, OP_MTTKRP, 128, 3);
 #undef T2SP_CASE
