@@ -131,6 +131,14 @@ int t2sp_b200_capsule(halide_buffer_t *P, halide_buffer_t *W, halide_buffer_t *V
  *            (oneapi-target-6-capsule.cpp:57-61, -6-run.cpp:92-99)
  * Every constant comes from the extents (capsule: stride 2 as in the reference, or 1, whichever
  * fits V's pixel slots); `precision` is a t2sp_precision. Bounds queries are not answered. */
+/* SYRK as the PEPPERS BLAS layer's generated interface takes it
+ * (t2s/peppers/blas/level3/syrk/release/s10/syrk-interface.h:12, t2s/tests/performance/syrk/syrk.cpp:52-73):
+ * A 2-D (K, N), symmetric C 2-D (N, N), O 6-D (III, III, II, II, I+1, >= I/2) with N = III*II*I;
+ * O(jjj,iii,jj,ii,j,i) = Alpha * sum_k A(k,r) A(k,c) + Beta * C(c,r), where for i >= j
+ * (r, c) = (N-1-ti, N-1-tj) and otherwise (r, c) = (ti, tj - III*II),
+ * ti = iii + III*ii + III*II*i, tj = jjj + III*jj + III*II*j. OpA is ignored, as in the specification. */
+int t2sp_b200_syrk(int32_t OpA, float Alpha, float Beta, halide_buffer_t *A, halide_buffer_t *C, halide_buffer_t *O);
+
 int t2sp_b200_conv_nd(halide_buffer_t *I, halide_buffer_t *K, halide_buffer_t *O, int precision);
 int t2sp_b200_capsule_nd(halide_buffer_t *P, halide_buffer_t *W, halide_buffer_t *V, int precision);
 

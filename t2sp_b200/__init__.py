@@ -65,6 +65,8 @@ def lib():
             fn = getattr(L, name)
             fn.argtypes = [P] * nargs
             fn.restype = ctypes.c_int
+        L.t2sp_b200_syrk.argtypes = [ctypes.c_int32, ctypes.c_float, ctypes.c_float, P, P, P]
+        L.t2sp_b200_syrk.restype = ctypes.c_int
         for name in ("t2sp_b200_conv_nd", "t2sp_b200_capsule_nd"):
             getattr(L, name).argtypes = [P, P, P, ctypes.c_int]
             getattr(L, name).restype = ctypes.c_int
@@ -123,6 +125,12 @@ def capsule_nd(P, W, V, precision=0):
     """capsule on the oneAPI flow's N-D operands P(MK,MX,CI,IY,IX,N), W(MY,MK,CI,CO,KY,KX), 9-D V
     (t2s/tests/correctness/oneapi-integration/oneapi-target-6-capsule.cpp:57-61)."""
     return lib().t2sp_b200_capsule_nd(P.ptr, W.ptr, V.ptr, precision)
+
+
+def syrk(opa, alpha, beta, A, C, O):
+    """int syrk(OpA, Alpha, Beta, A, C, deserializer): the folded 6-D output of the SYRK design
+    (t2s/peppers/blas/level3/syrk/release/s10/syrk-interface.h:12, t2s/tests/performance/syrk/syrk.cpp:52-73)."""
+    return lib().t2sp_b200_syrk(opa, alpha, beta, A.ptr, C.ptr, O.ptr)
 
 
 def ttm(a, b, c, desc=None):

@@ -1500,3 +1500,75 @@ extern "C" int t2sp_b200_capsule_nd(halide_buffer_t* P, halide_buffer_t* W, hali
     V->device_interface = v10.device_interface;
     return rc;
 }
+
+// ======================================================================================= SYRK
+// The generated SYRK interface of the PEPPERS BLAS layer
+// (t2s/peppers/blas/level3/syrk/release/s10/syrk-interface.h:12, specification
+// t2s/tests/performance/syrk/syrk.cpp:52-73): A(K, N), symmetric C(N, N), and the folded 6-D output
+// O(III, III, II, II, I+1, I) with N = III*II*I. The product R = A A^T runs as an fp32 GEMM whose B
+// operand is A itself (both K-major) into scratch; a second kernel folds alpha R + beta C into O.
+// OpA is accepted and, as in the specification (which never reads it), has no effect.
+extern "C" int t2sp_b200_syrk(int32_t opa, float alpha, float beta, halide_buffer_t* A, halide_buffer_t* C,
+                              halide_buffer_t* O) {
+    (void)opa;
+    Arg args[3] = {{A, "A", false, 2}, {C, "C", false, 2}, {O, "deserializer", true, 6}};
+    if (int e = nd_common_checks(args, 3)) return e;
+    const int K = A->dim[0].extent, N = A->dim[1].extent;
+    const int III = O->dim[0].extent, II = O->dim[2].extent, I = O->dim[4].extent - 1;
+    if (O->dim[1].extent != III) return constraint("deserializer.extent.1", O->dim[1].extent, "deserializer.extent.0", III);
+    if (O->dim[3].extent != II) return constraint("deserializer.extent.3", O->dim[3].extent, "deserializer.extent.2", II);
+    if (I < 0 || I % 2) return constraint("deserializer.extent.4 - 1", I, "even", I + 1);
+    if (O->dim[5].extent < I / 2) return constraint("deserializer.extent.5", O->dim[5].extent, "I/2", I / 2);
+    if (III * II * I != N) return constraint("III*II*I", III * II * I, "A.extent.1", N);
+    if (C->dim[0].extent < N || C->dim[1].extent < N) return constraint("C.extent", std::min(C->dim[0].extent, C->dim[1].extent), "A.extent.1", N);
+    for (int i = 0; i < 2; ++i)
+        if (int e = check_stride0(args[i])) return e;
+    if (N == 0) return 0;
+    if (int e = t2sp::rt_ensure_device()) return e;
+    Views vw;
+    if (int e = t2sp::rt_input_view(A, "A", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = t2sp::rt_input_view(C, "C", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = t2sp::rt_output_view(O, "deserializer", &vw.v[vw.n])) return e;
+    vw.n++;
+    // The design writes rows i < I/2 of the folded buffer only; a host buffer comes back whole, so its
+    // device copy starts from the host's content and the untouched elements keep their values.
+    if (!vw.v[2].borrowed && O->host && vw.v[2].bytes &&
+        cudaMemcpyAsync(vw.v[2].ptr, O->host, vw.v[2].bytes, cudaMemcpyHostToDevice, t2sp::rt_stream()) != cudaSuccess) {
+        cudaGetLastError();
+        return halide_error_code_copy_to_device_failed;
+    }
+    Scratch sr;
+    sr.p = t2sp::rt_alloc(size_t(N) * N * 4);
+    if (!sr.p) return halide_error_code_device_malloc_failed;
+    // R(N, N) = A(K, N) x A(K, N)^T through the GEMM entry, on device-resident views
+    halide_buffer_t a = *A, r;
+    halide_dimension_t da[2] = {A->dim[0], A->dim[1]}, dr[2];
+    a.dim = da;
+    a.host = nullptr; a.flags = 0; a.device = 0; a.device_interface = nullptr;
+    t2sp_b200_wrap_device_ptr(&a, reinterpret_cast<uint64_t>(static_cast<float*>(vw.v[0].ptr)));
+    make_device_2d(&r, dr, sr.p, N, N);
+    t2sp_gemm_desc gd;
+    memset(&gd, 0, sizeof(gd));
+    gd.trans_b = 1;
+    ThreadState& ts = tls();
+    const bool was_async = ts.async;
+    ts.async = true;  // the fold below is ordered behind the GEMM on the stream; no host wait in between
+    const int rc = K > 0 ? t2sp_b200_gemm(&a, &a, &r, &gd) : 0;
+    ts.async = was_async;
+    if (rc) return rc;
+    if (K == 0) cudaMemsetAsync(sr.p, 0, size_t(N) * N * 4, t2sp::rt_stream());
+    t2sp::SyrkFold f;
+    f.III = III; f.II = II; f.I = I;
+    for (int d = 0; d < 6; ++d) f.ostride[d] = O->dim[d].stride;
+    f.ldr = N; f.ldc = C->dim[1].stride;
+    f.alpha = alpha; f.beta = beta;
+    const float* pc = static_cast<const float*>(vw.v[1].ptr) + origin_offset(C);
+    float* po = static_cast<float*>(vw.v[2].ptr) + origin_offset(O);
+    if (t2sp::syrk_fold_launch(static_cast<const float*>(sr.p), pc, po, f, t2sp::rt_stream()) != cudaSuccess)
+        return halide_error_code_device_run_failed;
+    t2sp::rt_count_launch(1);
+    if (int e = t2sp::rt_finish_output(O, "deserializer", &vw.v[2])) return e;
+    return t2sp::rt_check_status("syrk");
+}

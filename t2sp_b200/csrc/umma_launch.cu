@@ -135,6 +135,29 @@ __global__ void permute_copy_kernel(const uint32_t* __restrict__ src, uint32_t* 
     dst[dof] = src[so];
 }
 
+__global__ void syrk_fold_kernel(const float* __restrict__ R, const float* __restrict__ C, float* __restrict__ O,
+                                 const __grid_constant__ SyrkFold f) {
+    const int t = f.III * f.II;  // rows (and columns) of one (i, j) block
+    const long long total = static_cast<long long>(t) * t * (f.I + 1) * (f.I / 2);
+    long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (idx >= total) return;
+    const int jjj = idx % f.III; idx /= f.III;
+    const int iii = idx % f.III; idx /= f.III;
+    const int jj = idx % f.II; idx /= f.II;
+    const int ii = idx % f.II; idx /= f.II;
+    const int j = idx % (f.I + 1);
+    const int i = static_cast<int>(idx / (f.I + 1));
+    const int n = t * f.I;
+    const int ti = iii + f.III * ii + t * i, tj = jjj + f.III * jj + t * j;
+    int r, c;
+    if (i >= j) { r = n - 1 - ti; c = n - 1 - tj; }
+    else { r = ti; c = tj - t; }
+    float v = f.alpha * R[r * f.ldr + c];
+    if (f.beta != 0.f) v += f.beta * C[r * f.ldc + c];
+    O[jjj * f.ostride[0] + iii * f.ostride[1] + jj * f.ostride[2] + ii * f.ostride[3] + j * f.ostride[4] +
+      i * f.ostride[5]] = v;
+}
+
 }  // namespace
 
 int core_sm_count() {
@@ -270,6 +293,15 @@ cudaError_t permute_copy_launch(const void* src, void* dst, const PermuteDesc& d
     const int threads = 256;
     permute_copy_kernel<<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0, stream>>>(
         static_cast<const uint32_t*>(src), static_cast<uint32_t*>(dst), d, total);
+    return cudaGetLastError();
+}
+
+cudaError_t syrk_fold_launch(const float* R, const float* C, float* O, const SyrkFold& f, cudaStream_t stream) {
+    const long long t = static_cast<long long>(f.III) * f.II;
+    const long long total = t * t * (f.I + 1) * (f.I / 2);
+    if (total <= 0) return cudaSuccess;
+    const int threads = 256;
+    syrk_fold_kernel<<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0, stream>>>(R, C, O, f);
     return cudaGetLastError();
 }
 

@@ -58,4 +58,18 @@ struct PermuteDesc {
 };
 cudaError_t permute_copy_launch(const void* src, void* dst, const PermuteDesc& d, cudaStream_t stream);
 
+// Folded output of the reference's SYRK design (t2s/tests/performance/syrk/syrk.cpp:38-73): element
+// (jjj,iii,jj,ii,j,i) of the 6-D buffer, i < I/2, j <= I, holds alpha * R[r][c] + beta * C[r][c] with
+//   (r, c) = (N-1-ti, N-1-tj)        when i >= j   ("bottom" half of the upper triangle, mirrored)
+//   (r, c) = (ti, tj - III*II)       otherwise
+// ti = iii + III*ii + III*II*i, tj = jjj + III*jj + III*II*j, N = III*II*I. R is the N x N product
+// (pitch ldr), C the caller's matrix (pitch ldc); ostride are the element strides of the six dimensions.
+struct SyrkFold {
+    int III, II, I;
+    long long ostride[6];
+    long long ldr, ldc;
+    float alpha, beta;
+};
+cudaError_t syrk_fold_launch(const float* R, const float* C, float* O, const SyrkFold& f, cudaStream_t stream);
+
 }  // namespace t2sp

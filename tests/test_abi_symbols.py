@@ -47,7 +47,8 @@ def test_stubs_define_the_interface_symbols(lib, tmp_path):
     stubs = os.path.join(ROOT, "t2sp_b200", "csrc", "stubs")
     so = tmp_path / "libstubs.so"
     objs = []
-    for f in ("gemm-interface.cpp", "conv-interface.cpp", "capsule-interface.cpp", "host.cpp", "ttm-mttkrp-interface.cpp"):
+    for f in ("gemm-interface.cpp", "conv-interface.cpp", "capsule-interface.cpp", "host.cpp", "ttm-mttkrp-interface.cpp",
+              "syrk-interface.cpp", "blas-syrk.cpp", "blas-gemm.cpp"):
         o = tmp_path / (f + ".o")
         subprocess.run(["g++", "-fPIC", "-c", "-I", INC, "-I", os.path.join(ROOT, "tests", "designs"),
                         os.path.join(stubs, f), "-o", str(o)], check=True, capture_output=True)
@@ -55,8 +56,9 @@ def test_stubs_define_the_interface_symbols(lib, tmp_path):
     subprocess.run(["g++", "-shared", "-o", str(so)] + objs + ["-L", os.path.dirname(LIB_PATH), "-lt2sp_b200",
                     "-Wl,-rpath," + os.path.dirname(LIB_PATH)], check=True, capture_output=True)
     S = ctypes.CDLL(str(so))
-    for n in ("gemm", "conv", "capsule", "GEMM", "ttm", "mttkrp"):
+    for n in ("gemm", "conv", "capsule", "GEMM", "ttm", "mttkrp", "syrk"):
         assert hasattr(S, n)
+    assert S.syrk(0, ctypes.c_float(1), ctypes.c_float(0), None, None, None) == -12
     # null buffers are rejected by the generic entry behind the stub, with the reference's code
     assert S.gemm(None, None, None) == -12
     assert S.capsule(None, None, None) == -12

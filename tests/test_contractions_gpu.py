@@ -93,3 +93,31 @@ def test_mttkrp_random(lib, L, I, K, R, splits):
     # deterministic: the split partial sums are added in a fixed order
     rc2, d2 = run_mttkrp(a, b, c, splits)
     assert rc2 == 0 and np.array_equal(d, d2)
+
+
+@pytest.mark.parametrize("III,II,I,K", [(12, 8, 8, 1024), (4, 2, 4, 40), (8, 4, 2, 100)])
+def test_syrk_folded_output(lib, III, II, I, K):
+    """O(jjj,iii,jj,ii,j,i) = Alpha * (A A^T)(r,c) + Beta * C(r,c) with the fold of
+    t2s/tests/performance/syrk/syrk.cpp:38-73: (r,c) = (N-1-ti, N-1-tj) for i >= j, else (ti, tj - III*II)."""
+    N = III * II * I
+    A = O.uniform(14, 1, (N, K))
+    Cs = O.uniform(14, 2, (N, N))
+    Cs = ((Cs + Cs.T) * 0.5).astype(np.float32)
+    alpha, beta = 1.5, -0.25
+    out = np.full((I, I + 1, II, II, III, III), np.nan, np.float32)
+    ob = Buffer.from_numpy(out)
+    assert t2sp_b200.syrk(0, alpha, beta, Buffer.from_numpy(A), Buffer.from_numpy(Cs), ob) == 0
+    R = alpha * (A.astype(np.float64) @ A.astype(np.float64).T) + beta * Cs.astype(np.float64)
+    got = ob.keepalive
+    t = III * II
+    want = np.full(got.shape, np.nan)
+    i, j, ii, jj, iii, jjj = np.meshgrid(np.arange(I // 2), np.arange(I + 1), np.arange(II), np.arange(II),
+                                         np.arange(III), np.arange(III), indexing="ij")
+    ti, tj = iii + III * ii + t * i, jjj + III * jj + t * j
+    bot = i >= j
+    r = np.where(bot, N - 1 - ti, ti)
+    c = np.where(bot, N - 1 - tj, tj - t)
+    want[:I // 2] = R[r, c]
+    assert not np.isnan(got[:I // 2]).any()
+    assert np.isnan(got[I // 2:]).all(), "rows i >= I/2 of the folded buffer are not part of the design's output"
+    assert normwise(got[:I // 2], want[:I // 2]) <= TOL_FP32
