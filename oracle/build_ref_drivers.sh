@@ -45,6 +45,8 @@ if [ -f "$ROOT/t2sp_b200/libt2sp_b200.so" ]; then
   # the PEPPERS SYRK driver over the folded-output syrk interface (S10 release constants: n = 768, k = 1024)
   SYRK="$REF/t2s/peppers/blas/level3/syrk/release/s10"
   $CXX $FLAGS -iquote $ROOT/include -I $SYRK $SYRK/ssyrk-run-fpga.cpp $STUBS/blas-syrk.cpp $STUBS/syrk-interface.cpp $LINK -o $ROOT/tests/_bin/blas_ssyrk_s10
+  # the SYRK design's own driver: checks the folded 6-D output element by element (C not symmetric here)
+  $CXX $FLAGS -DTINY -I $PERF/syrk $PERF/syrk/syrk-run-fpga.cpp $STUBS/syrk-interface.cpp $LINK -o $ROOT/tests/_bin/syrk_tiny
   # performance mode of the same drivers (no -DTINY: the A10 design constants and problem sizes),
   # with this repository's implementation of the Roofline.h helpers in place of Roofline.cpp
   SHIM="$ROOT/t2sp_b200/csrc/roofline_shim.cpp"

@@ -59,8 +59,8 @@ struct CoreCfg {
     static constexpr int kBoxBytesMn = AT::kBlockK * 128;           // one MN-major box: kBlockK rows of 128 B
     static constexpr int kBoxesMn = kBBytes / kBoxBytesMn;          // boxes per MN-major B tile
     static constexpr int kBoxElemsMn = 128 / AT::kElem;             // N elements per MN-major box
-    // split warps: six halve the time a k-block's lo tiles take (the MTTKRP tile generator is written for four)
-    static constexpr int kSplitWarps = kX3 ? (OP == OP_MTTKRP ? 4 : 6) : 0;
+    // split warps: more of them shorten the time a k-block's lo tiles take (MTTKRP also builds its B tile there)
+    static constexpr int kSplitWarps = kX3 ? (OP == OP_MTTKRP ? (BN <= 64 ? 8 : 4) : 6) : 0;
     static constexpr int kSplitThreads = kSplitWarps * 32;
     static constexpr int kWarps = 2 + 4 + kSplitWarps;
     static constexpr int kThreads = kWarps * 32;
@@ -513,7 +513,8 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
             const int st = (warp - 6) * 32 + lane;
             int it = 0;
             bool ok = true;
-            constexpr int kGenPos = BN * 8 / 128;  // MTTKRP: 16-byte chunks of the generated tile per thread
+            constexpr int kGenPos = BN * 8 / (Cfg::kBGenerated ? Cfg::kSplitThreads : 128);  // MTTKRP: 16-byte chunks of the generated tile per thread
+            static_assert(!Cfg::kBGenerated || (BN * 8) % Cfg::kSplitThreads == 0, "the generated tile must divide among the split threads");
             float gen_b[kGenPos];
             int gen_k = -1;
             (void)gen_b; (void)gen_k;
@@ -541,13 +542,13 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                             gen_k = k;
 #pragma unroll
                             for (int i = 0; i < kGenPos; ++i) {
-                                const int r = (st + 128 * i) >> 3;
+                                const int r = (st + Cfg::kSplitThreads * i) >> 3;
                                 gen_b[i] = r < p.R ? __ldg(p.fb + static_cast<long long>(r) * p.ldfb + k) : 0.f;
                             }
                         }
 #pragma unroll
                         for (int i = 0; i < kGenPos; ++i) {
-                            const int off = Cfg::kABytes + (st + 128 * i) * 16;  // chunk position as stored
+                            const int off = Cfg::kABytes + (st + Cfg::kSplitThreads * i) * 16;  // chunk position as stored
                             const float4 c4 = *reinterpret_cast<const float4*>(hi + off);
                             const float bv = gen_b[i];
                             float4 h, l;
