@@ -444,10 +444,10 @@ KNOWN_TRAFFIC = {
     # profiles/fp32_3xtf32_kernels_conv_ttm_mttkrp_capsule_sgemm_full.md
     "gemm_bf16_4096": 95056896 + 32553472,
     "gemm_i8_4096": 35462400 + 18725376,
-    "conv_cfg2": 19218944,
-    "ttm_cfg3": 268954368 + 217524736,
-    "mttkrp_cfg3": 537528832 + 3500544,
-    "capsule_cfg4": 21988608 + 3584,
+    "conv_cfg2": 19220480 + 142336,
+    "ttm_cfg3": 268876800 + 218153984,
+    "mttkrp_cfg3": 537536000 + 4134656,
+    "capsule_cfg4": 21989632 + 4352,
     "sgemm_1024": 8471808,
 }
 

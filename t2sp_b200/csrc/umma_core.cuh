@@ -52,7 +52,7 @@ struct CoreCfg {
     static constexpr int kStageBytes = kABytes + kBBytes;    // one ring stage: [A | B] as TMA delivers them
     // 3xTF32: the raw fp32 tiles double as the hi operands (the tensor core reads only the top 19
     // bits of each word); the lo tiles live in a short ring of their own, [A_lo | B_lo] per slot.
-    static constexpr int kLoSlots = kX3 ? (OP == OP_MTTKRP ? (BN <= 64 ? 4 : 3) : 3) : 0;
+    static constexpr int kLoSlots = kX3 ? (OP == OP_MTTKRP ? (BN <= 64 ? 3 : 3) : 3) : 0;
     // MTTKRP writes its partial slabs column-major and never stages an output tile: its staging
     // bytes go to a deeper lo ring instead.
     static constexpr int kCStage = (OP == OP_MTTKRP) ? 0 : kCStageBytes;

@@ -209,7 +209,7 @@ cudaError_t core_launch(int arith, int op, int bn, const CoreParams& p, int grid
     T2SP_CASE(AR_TF32X3, OP_CONV, 64, 5);
     T2SP_CASE(AR_TF32X3, OP_CAPSULE, 128, 3);
     T2SP_CASE(AR_TF32X3, OP_CAPSULE, 64, 5);
-    T2SP_CASE(AR_TF32X3, OP_MTTKRP, 64, 5);
+    T2SP_CASE(AR_TF32X3, OP_MTTKRP, 64, 6);
     T2SP_CASE(AR_TF32X3, OP_MTTKRP, 128, 3);
 #undef T2SP_CASE
     return cudaErrorInvalidValue;
