@@ -148,3 +148,32 @@ def test_device_helpers_without_device(lib):
     assert lib.t2sp_b200_detach_device_ptr(A.ptr) == 0 and A.raw.device == 0
     assert lib.t2sp_b200_set_device(99) == -36
     assert lib.t2sp_b200_set_device(0) == 0
+
+
+def test_nd_fronts_and_syrk_validation(lib):
+    """conv_nd / capsule_nd / syrk read every constant from the extents; inconsistent shapes are
+    rejected on the host with the reference's codes before any device work."""
+    z = lambda *shape: Buffer.from_numpy(np.zeros(shape, F))
+    assert lib.t2sp_b200_conv_nd(None, None, None, 0) == -12
+    assert lib.t2sp_b200_capsule_nd(None, None, None, 0) == -12
+    assert lib.t2sp_b200_syrk(0, ctypes.c_float(1), ctypes.c_float(0), None, None, None) == -12
+    # conv: I(IY,IX,CI,N) numpy (N,CI,IX,IY); K (CO,CI,KX,KY); O 10-D
+    I, K = z(2, 8, 6, 6), z(8, 8, 3, 3)
+    assert t2sp_b200.conv_nd(I, K, z(2, 1, 1, 1, 1, 1, 2, 4, 4, 4)) == -36   # consistent: only the missing device stops it
+    assert t2sp_b200.conv_nd(I, K, z(2, 1, 1, 1, 1, 1, 2, 4, 5, 4)) == -8    # OY = 5 but IY - KY + 1 = 4
+    assert t2sp_b200.conv_nd(I, z(8, 4, 3, 3), z(2, 1, 1, 1, 1, 1, 2, 4, 4, 4)) == -8   # channel counts differ
+    assert t2sp_b200.conv_nd(I, K, z(3, 1, 1, 1, 1, 1, 2, 4, 4, 4)) == -8    # batch differs
+    assert t2sp_b200.conv_nd(z(8, 6, 6), K, z(2, 1, 1, 1, 1, 1, 2, 4, 4, 4)) == -43  # 3-D input: bad dimensions
+    assert t2sp_b200.conv_nd(Buffer.from_numpy(np.zeros((2, 8, 6, 6), np.float64)), K, z(2, 1, 1, 1, 1, 1, 2, 4, 4, 4)) == -3
+    # capsule: P (N,IX,IY,CI,MX,MK), W (KX,KY,CO,CI,MK,MY), V (N,CO_o,COO,MX,MY,Y_X,YY_XX,YYY_XXX,COOO)
+    P, W = z(2, 5, 5, 4, 4, 4), z(3, 3, 8, 4, 4, 4)
+    assert t2sp_b200.capsule_nd(P, W, z(2, 1, 2, 4, 4, 1, 1, 4, 4)) == -36   # stride 2: 5 -> 2 x 2 outputs = 4 slots
+    assert t2sp_b200.capsule_nd(P, W, z(2, 1, 2, 4, 4, 1, 1, 9, 4)) == -36   # stride 1: 3 x 3 outputs = 9 slots
+    assert t2sp_b200.capsule_nd(P, W, z(2, 1, 2, 4, 4, 1, 1, 3, 4)) == -8    # 3 pixel slots hold neither 2 x 2 nor 3 x 3 outputs
+    assert t2sp_b200.capsule_nd(P, z(3, 3, 8, 4, 2, 4), z(2, 1, 2, 4, 4, 1, 1, 4, 4)) == -8  # MK differs
+    # syrk: A (N,K), C (N,N), O (I, I+1, II, II, III, III) with N = III*II*I
+    A, C = z(16, 8), z(16, 16)
+    assert t2sp_b200.syrk(0, 1.0, 0.0, A, C, z(4, 5, 2, 2, 2, 2)) == -36
+    assert t2sp_b200.syrk(0, 1.0, 0.0, A, C, z(4, 5, 2, 2, 2, 3)) == -8      # the two innermost extents must agree
+    assert t2sp_b200.syrk(0, 1.0, 0.0, A, C, z(2, 4, 2, 2, 2, 2)) == -8      # I = 3 is odd
+    assert t2sp_b200.syrk(0, 1.0, 0.0, z(12, 8), C, z(4, 5, 2, 2, 2, 2)) == -8   # N != III*II*I
