@@ -192,6 +192,45 @@ __device__ __forceinline__ void tc_fence_after_sync() {
 // ---------------------------------------------------------------- tcgen05: MMA issue + commit
 enum : int { KIND_F16 = 0, KIND_TF32 = 1, KIND_I8 = 2 };
 
+// TF32 MMA whose A operand sits in tensor memory: lane = row of the tile, one 32-bit column per K
+// element (8 columns per instruction); B comes from shared memory through its descriptor.
+__device__ __forceinline__ void umma_tf32_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Warp-uniform forms: the whole (converged) warp executes the call and one elected lane issues the
+// instruction. Keeping the issuing loop free of per-lane control flow lets the compiler hold the
+// descriptors in uniform registers instead of moving them there for every instruction.
+__device__ __forceinline__ void umma_tf32_a_tmem_warp(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                                      uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        " .reg .pred pe, p;\n"
+        " elect.sync _|pe, 0xffffffff;\n"
+        " setp.ne.b32 p, %4, 0;\n"
+        " @pe tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_warp(uint64_t* bar) {
+    asm volatile(
+        "{\n"
+        " .reg .pred pe;\n"
+        " elect.sync _|pe, 0xffffffff;\n"
+        " @pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n"
+        "}\n" ::"r"(smem_u32(bar))
+        : "memory");
+}
+
 template <int KIND, int CTA_GROUP>
 __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                      uint32_t accumulate) {
@@ -257,6 +296,18 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
+}
+// 32 lanes x 16 columns of 32-bit registers -> tensor memory (the warp's own lane quarter).
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

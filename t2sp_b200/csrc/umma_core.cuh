@@ -52,7 +52,20 @@ struct CoreCfg {
     static constexpr int kStageBytes = kABytes + kBBytes;    // one ring stage: [A | B] as TMA delivers them
     // 3xTF32: the raw fp32 tiles double as the hi operands (the tensor core reads only the top 19
     // bits of each word); the lo tiles live in a short ring of their own, [A_lo | B_lo] per slot.
-    static constexpr int kLoSlots = kX3 ? (OP == OP_MTTKRP ? (BN <= 64 ? 3 : 3) : 3) : 0;
+    // fp32 tiles keep the A operand of the MMAs in tensor memory: the split warps read the raw A tile
+    // once and write hi and lo straight into TMEM (tcgen05.st), so the three MMAs of a product read only
+    // B from shared memory. TMEM: 2 * kAccBufs accumulators x BN columns (256 in all) + kLoSlots x (32 hi
+    // + 32 lo) columns of A. The lo ring in shared memory then holds B tiles only.
+#ifndef T2SP_ATMEM_MAX_BN
+#define T2SP_ATMEM_MAX_BN 64
+#endif
+    static constexpr bool kATmem = kX3 && BN <= T2SP_ATMEM_MAX_BN;
+    // accumulators per kind (main chunk / cross terms): two where TMEM has room, else one
+    static constexpr int kAccBufs = (kATmem && BN > 64) ? 1 : 2;
+    static constexpr int kLoSlots = kX3 ? (kATmem ? 4 : 3) : 0;
+    static constexpr int kLoBytes = kATmem ? kBBytes : kStageBytes;  // one lo slot: [A_lo | B_lo], or B_lo alone
+    static constexpr int kLoBOff = kATmem ? 0 : kABytes;             // where B_lo starts inside a lo slot
+    static constexpr int kATmemCol0 = 256;                           // first TMEM column of the A slots
     // MTTKRP writes its partial slabs column-major and never stages an output tile: its staging
     // bytes go to a deeper lo ring instead.
     static constexpr int kCStage = (OP == OP_MTTKRP) ? 0 : kCStageBytes;
@@ -60,20 +73,22 @@ struct CoreCfg {
     static constexpr int kBoxesMn = kBBytes / kBoxBytesMn;          // boxes per MN-major B tile
     static constexpr int kBoxElemsMn = 128 / AT::kElem;             // N elements per MN-major box
     // split warps: more of them shorten the time a k-block's lo tiles take (MTTKRP also builds its B tile there)
-    static constexpr int kSplitWarps = kX3 ? (OP == OP_MTTKRP ? (BN <= 64 ? 8 : 4) : 6) : 0;
+    // split warps: with A in TMEM a multiple of four (each warp reaches one TMEM lane quarter only); the
+    // 128-wide tile keeps four so that its epilogue warps can hold 128 running sums in registers
+    static constexpr int kSplitWarps = kX3 ? (kATmem ? (BN <= 64 ? 8 : 4) : (OP == OP_MTTKRP ? (BN <= 64 ? 8 : 4) : 6)) : 0;
     static constexpr int kSplitThreads = kSplitWarps * 32;
     static constexpr int kWarps = 2 + 4 + kSplitWarps;
     static constexpr int kThreads = kWarps * 32;
     // 16-bit / int8: two whole-tile accumulators (tile t+1 accumulates while tile t drains).
     // 3xTF32: two chunk accumulators for the hi*hi products plus two (one per tile in flight) for the
     // small cross terms.
-    static constexpr int kTmemCols = kX3 ? (4 * BN <= 256 ? 256 : 512) : 2 * BN;
+    static constexpr int kTmemCols = kX3 ? ((4 * BN <= 256 && !kATmem) ? 256 : 512) : 2 * BN;
     static constexpr int kChunkKb = 8;  // 3xTF32: k-blocks summed inside TMEM before an fp32 drain
     static constexpr int kNumBars = 2 * STAGES + 14;
     static constexpr int kTailBytes = kNumBars * 8 + 16 + 4 * 256 * 8;
-    static constexpr int kSmemBytes = (STAGES + kLoSlots) * kStageBytes + kCStage + kTailBytes + 1024;
+    static constexpr int kSmemBytes = STAGES * kStageBytes + kLoSlots * kLoBytes + kCStage + kTailBytes + 1024;
     static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "TMEM columns must be a power of two");
-    static_assert(!kX3 || 4 * BN <= 512, "3xTF32 needs four accumulators in TMEM");
+    static_assert(!kX3 || 2 * kAccBufs * BN + (kATmem ? kLoSlots * 64 : 0) <= 512, "3xTF32 accumulators and A slots must fit TMEM");
     static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
 };
 
@@ -198,7 +213,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* lo_ring = smem + STAGES * Cfg::kStageBytes;     // 3xTF32: kLoSlots x [A_lo | B_lo]
-    uint8_t* cstage = lo_ring + Cfg::kLoSlots * Cfg::kStageBytes;  // EPI_TMA staging tiles
+    uint8_t* cstage = lo_ring + Cfg::kLoSlots * Cfg::kLoBytes;  // EPI_TMA staging tiles
     uint8_t* tail = cstage + Cfg::kCStage;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);  // TMA data landed
     uint64_t* empty_bar = full_bar + STAGES;                 // MMAs that read the stage retired
@@ -264,6 +279,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!bounded_wait(&empty_bar[s], ph ^ 1, ab, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+                    T2SP_TRACE(p, 0, it);
                     uint8_t* sa = smem + s * Cfg::kStageBytes;
                     uint8_t* sb = sa + Cfg::kABytes;
                     ptx::mbar_expect_tx(&full_bar[s], p.a_tx_bytes + Cfg::kBBytes);
@@ -339,7 +355,10 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        // With A in tensor memory the issue loop runs on the whole warp and an elected lane issues each
+        // MMA and commit (measured faster there: MTTKRP 202 -> 187 us; with shared-memory descriptors for A
+        // the same change was slower, capsule 103 -> 144 us); every other path runs it on lane 0.
+        if (Cfg::kATmem || lane == 0) {
             int it = 0, lt = 0;
             bool ok = true;
             constexpr uint32_t kStepK = 32 >> 4;                                           // K-major: 32 B per UMMA
@@ -348,14 +367,16 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
             constexpr uint32_t kLboB = Cfg::kBMnMajor ? Cfg::kBoxBytesMn : 16;
             if constexpr (Cfg::kX3) {
                 int gch = 0;
+                auto wait_bar = [&](uint64_t* bar, uint32_t parity) {
+                    if constexpr (Cfg::kATmem) return bounded_wait_warp(bar, parity, ab, ST_TIMEOUT_MMA, lane);
+                    else return bounded_wait(bar, parity, ab, ST_TIMEOUT_MMA);
+                };
                 for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++lt) {
-                    const uint32_t d_small = tmem_base + (2 + (lt & 1)) * BN;
-                    if (!bounded_wait(&sempty_bar[lt & 1], ((lt >> 1) & 1) ^ 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
+                    const int cs = lt % Cfg::kAccBufs;
+                    const uint32_t d_small = tmem_base + (Cfg::kAccBufs + cs) * BN;
                     const int nkb = kb_count<OP>(p, (OP == OP_MTTKRP) ? t / p.tiles_m : 0);
                     for (int kb0 = 0; kb0 < nkb && ok; kb0 += Cfg::kChunkKb, ++gch) {
-                        const int b = gch & 1;
-                        if (!bounded_wait(&tempty_bar[b], ((gch >> 1) & 1) ^ 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
-                        ptx::tc_fence_after_sync();
+                        const int b = gch % Cfg::kAccBufs;
                         const uint32_t d_main = tmem_base + b * BN;
                         const int kend = min(kb0 + Cfg::kChunkKb, nkb);
                         for (int kb = kb0; kb < kend; ++kb, ++it) {
@@ -363,29 +384,71 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                             const int ls = it % Cfg::kLoSlots;
                             // the splitter arrives on ready[ls] after it has seen full[s], so this
                             // wait covers the raw tiles too
-                            if (!bounded_wait(&ready_bar[ls], (it / Cfg::kLoSlots) & 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
+                            if (!wait_bar(&ready_bar[ls], (it / Cfg::kLoSlots) & 1)) { ok = false; break; }
                             ptx::tc_fence_after_sync();
+                            if (lane == 0) T2SP_TRACE(p, 3, it);
                             const uint32_t sa = ptx::smem_u32(smem + s * Cfg::kStageBytes);
                             const uint32_t sb = sa + Cfg::kABytes;
-                            const uint32_t la = ptx::smem_u32(lo_ring + ls * Cfg::kStageBytes);
-                            const uint64_t da = ptx::make_smem_desc(sa, 16, 1024);
+                            const uint32_t la = ptx::smem_u32(lo_ring + ls * Cfg::kLoBytes);
                             const uint64_t db = ptx::make_smem_desc(sb, kLboB, Cfg::kBSbo, Cfg::kBSwizzle);
+                            const uint64_t dbl = ptx::make_smem_desc(la + Cfg::kLoBOff, kLboB, Cfg::kBSbo, Cfg::kBSwizzle);
+                            const uint32_t a_hi = tmem_base + Cfg::kATmemCol0 + ls * 64, a_lo = a_hi + 32;  // kATmem only
+                            const uint64_t da = ptx::make_smem_desc(sa, 16, 1024);
                             const uint64_t dal = ptx::make_smem_desc(la, 16, 1024);
-                            const uint64_t dbl = ptx::make_smem_desc(la + Cfg::kABytes, kLboB, Cfg::kBSbo, Cfg::kBSwizzle);
+                            auto issue_main = [&]() {
 #pragma unroll
-                            for (int j = 0; j < AT::kBlockK / AT::kUmmaK; ++j) {
-                                if (!p.single_pass) {
-                                    ptx::umma<AT::kKind, 1>(d_small, dal + j * kStepK, db + j * kStepB, p.idesc,
-                                                            (kb | j) ? 1u : 0u);
-                                    ptx::umma<AT::kKind, 1>(d_small, da + j * kStepK, dbl + j * kStepB, p.idesc, 1u);
+                                for (int j = 0; j < 4; ++j) {
+                                    const uint32_t acc = ((kb - kb0) | j) ? 1u : 0u;
+                                    if constexpr (Cfg::kATmem) ptx::umma_tf32_a_tmem_warp(d_main, a_hi + 8 * j, db + j * kStepB, p.idesc, acc);
+                                    else ptx::umma<AT::kKind, 1>(d_main, da + j * kStepK, db + j * kStepB, p.idesc, acc);
                                 }
-                                ptx::umma<AT::kKind, 1>(d_main, da + j * kStepK, db + j * kStepB, p.idesc,
-                                                        ((kb - kb0) | j) ? 1u : 0u);
+                            };
+                            auto issue_cross = [&]() {
+                                if (p.single_pass) return;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const uint32_t acc = (kb | j) ? 1u : 0u;
+                                    if constexpr (Cfg::kATmem) {
+                                        ptx::umma_tf32_a_tmem_warp(d_small, a_lo + 8 * j, db + j * kStepB, p.idesc, acc);
+                                        ptx::umma_tf32_a_tmem_warp(d_small, a_hi + 8 * j, dbl + j * kStepB, p.idesc, 1u);
+                                    } else {
+                                        ptx::umma<AT::kKind, 1>(d_small, dal + j * kStepK, db + j * kStepB, p.idesc, acc);
+                                        ptx::umma<AT::kKind, 1>(d_small, da + j * kStepK, dbl + j * kStepB, p.idesc, 1u);
+                                    }
+                                }
+                            };
+                            // The main accumulator b is free once the epilogue drained the chunk that used
+                            // it last (tempty), the cross-term accumulator once the tile that used it last
+                            // was drained (sempty, which follows that tile's last tempty). Inside a tile the
+                            // cross terms of a chunk's first k-block go out before the wait on tempty.
+                            if (kb == 0) {
+                                if (!wait_bar(&tempty_bar[b], ((gch / Cfg::kAccBufs) & 1) ^ 1)) { ok = false; break; }
+                                ptx::tc_fence_after_sync();
+                                issue_main();
+                                if (!wait_bar(&sempty_bar[cs], ((lt / Cfg::kAccBufs) & 1) ^ 1)) { ok = false; break; }
+                                ptx::tc_fence_after_sync();
+                                issue_cross();
+                            } else {
+                                issue_cross();
+                                if (kb == kb0) {
+                                    if (!wait_bar(&tempty_bar[b], ((gch / Cfg::kAccBufs) & 1) ^ 1)) { ok = false; break; }
+                                    ptx::tc_fence_after_sync();
+                                }
+                                issue_main();
                             }
-                            ptx::umma_commit(&empty_bar[s]);
-                            ptx::umma_commit(&lofree_bar[ls]);
+                            if constexpr (Cfg::kATmem) {
+                                ptx::umma_commit_warp(&empty_bar[s]);
+                                ptx::umma_commit_warp(&lofree_bar[ls]);
+                            } else {
+                                ptx::umma_commit(&empty_bar[s]);
+                                ptx::umma_commit(&lofree_bar[ls]);
+                            }
+                            if (lane == 0) T2SP_TRACE(p, 4, it);
                         }
-                        if (ok) ptx::umma_commit(&tfull_bar[b]);
+                        if (ok) {
+                            if constexpr (Cfg::kATmem) ptx::umma_commit_warp(&tfull_bar[b]);
+                            else ptx::umma_commit(&tfull_bar[b]);
+                        }
                     }
                 }
             } else {
@@ -442,8 +505,8 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                 uint32_t sum[BN];  // fp32 running sums of this thread's output row, kept as raw bits
                 const int nkb = kb_count<OP>(p, nb);
                 for (int kb0 = 0; kb0 < nkb && ok; kb0 += Cfg::kChunkKb, ++gch) {
-                    const int b = gch & 1;
-                    if (!bounded_wait_warp(&tfull_bar[b], (gch >> 1) & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
+                    const int b = gch % Cfg::kAccBufs;
+                    if (!bounded_wait_warp(&tfull_bar[b], (gch / Cfg::kAccBufs) & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
                     ptx::tc_fence_after_sync();
                     if (kb0 == 0) {
                         // first chunk of the tile: load straight into the sums, all loads in flight at once
@@ -472,7 +535,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
 #pragma unroll
                     for (int c = 0; c < BN / 32; ++c) {
                         uint32_t r[32];
-                        ptx::tmem_ld_32x32(lane_base + (2 + (lt & 1)) * BN + c * 32, r);
+                        ptx::tmem_ld_32x32(lane_base + (Cfg::kAccBufs + lt % Cfg::kAccBufs) * BN + c * 32, r);
                         ptx::tmem_ld_wait();
 #pragma unroll
                         for (int j = 0; j < 32; ++j)
@@ -481,7 +544,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                 }
                 ptx::tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(&sempty_bar[lt & 1]);
+                if (lane == 0) ptx::mbar_arrive(&sempty_bar[lt % Cfg::kAccBufs]);
 #pragma unroll
                 for (int c = 0; c < BN / 32; ++c) {
                     if (p.epi == EPI_TMA)
@@ -526,10 +589,13 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                     const uint32_t ph = (it / STAGES) & 1;
                     const int ls = it % Cfg::kLoSlots;
                     uint8_t* hi = smem + s * Cfg::kStageBytes;
-                    uint8_t* lo = lo_ring + ls * Cfg::kStageBytes;
-                    // the lo slot is free once the MMAs of two k-blocks ago have read it
+                    uint8_t* lo = lo_ring + ls * Cfg::kLoBytes;
+                    uint8_t* lo_b = lo + Cfg::kLoBOff - Cfg::kABytes;  // lo_b + (offset inside the raw stage) = B_lo position
+                    // the lo slot is free once the MMAs that read it last have retired
                     if (!bounded_wait_warp(&lofree_bar[ls], ((it / Cfg::kLoSlots) & 1) ^ 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
+                    if (st == 0) T2SP_TRACE(p, 8, it);
                     if (!bounded_wait_warp(&full_bar[s], ph, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
+                    if (st == 0) T2SP_TRACE(p, 1, it);
                     if constexpr (Cfg::kBGenerated) {
                         // The B region holds c(l-block, r) as TMA delivered it: row r of the tile, 32
                         // consecutive l values, 128-byte swizzle. Scaling row r by b(k, r) in place turns
@@ -558,25 +624,57 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                             l.z = h.z - __uint_as_float(__float_as_uint(h.z) & 0xFFFFE000u);
                             l.w = h.w - __uint_as_float(__float_as_uint(h.w) & 0xFFFFE000u);
                             *reinterpret_cast<float4*>(hi + off) = h;
-                            *reinterpret_cast<float4*>(lo + off) = l;
+                            *reinterpret_cast<float4*>(lo_b + off) = l;
                         }
                     }
-                    constexpr int kSplitBytes = Cfg::kBGenerated ? Cfg::kABytes : (Cfg::kABytes + Cfg::kBBytes);
                     // lo = x - trunc_tf32(x): exact in fp32, at most 13 significant bits. The raw
                     // tiles are left as they are: the tensor core ignores their low 13 mantissa bits.
+                    constexpr int kSplitFrom = Cfg::kATmem ? Cfg::kABytes : 0;
+                    constexpr int kSplitTo = Cfg::kBGenerated ? Cfg::kABytes : (Cfg::kABytes + Cfg::kBBytes);
+                    if constexpr (Cfg::kATmem) {
+                        // A goes to tensor memory: this thread owns one tile row (or half of it). The row's
+                        // 16-byte chunks sit at
+                        // chunk ^ (row & 7) in the swizzled tile, which also spreads a warp's reads over
+                        // all banks.
+                        const int q = warp & 3;
+                        const int row = q * 32 + lane;
+                        const uint8_t* rp = hi + row * 128;
+                        // with eight split warps two of them share a lane quarter, 16 K values each
+#pragma unroll
+                        for (int h = (warp - 6) >> 2; h < 2; h += Cfg::kSplitWarps / 4) {
+                            uint32_t vh[16], vl[16];
+#pragma unroll
+                            for (int cc = 0; cc < 4; ++cc) {
+                                const float4 v = *reinterpret_cast<const float4*>(rp + (((4 * h + cc) ^ (row & 7)) << 4));
+                                vh[4 * cc + 0] = __float_as_uint(v.x); vh[4 * cc + 1] = __float_as_uint(v.y);
+                                vh[4 * cc + 2] = __float_as_uint(v.z); vh[4 * cc + 3] = __float_as_uint(v.w);
+                            }
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                vl[j] = __float_as_uint(__uint_as_float(vh[j]) - __uint_as_float(vh[j] & 0xFFFFE000u));
+                            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::kATmemCol0 + ls * 64 + 16 * h;
+                            ptx::tmem_st_32x16(taddr, vh);
+                            if (!p.single_pass) ptx::tmem_st_32x16(taddr + 32, vl);
+                        }
+                    }
                     if (!p.single_pass) {
 #pragma unroll 4
-                        for (int off = st * 16; off < kSplitBytes; off += Cfg::kSplitThreads * 16) {
+                        for (int off = kSplitFrom + st * 16; off < kSplitTo; off += Cfg::kSplitThreads * 16) {
                             const float4 v = *reinterpret_cast<const float4*>(hi + off);
                             float4 l;
                             l.x = v.x - __uint_as_float(__float_as_uint(v.x) & 0xFFFFE000u);
                             l.y = v.y - __uint_as_float(__float_as_uint(v.y) & 0xFFFFE000u);
                             l.z = v.z - __uint_as_float(__float_as_uint(v.z) & 0xFFFFE000u);
                             l.w = v.w - __uint_as_float(__float_as_uint(v.w) & 0xFFFFE000u);
-                            *reinterpret_cast<float4*>(lo + off) = l;
+                            *reinterpret_cast<float4*>((off < Cfg::kABytes ? lo : lo_b) + off) = l;
                         }
                     }
+                    if constexpr (Cfg::kATmem) {
+                        ptx::tmem_st_wait();
+                        ptx::tc_fence_before_sync();
+                    }
                     ptx::fence_proxy_async_smem();
+                    if (st == 0) T2SP_TRACE(p, 2, it);
                     ptx::mbar_arrive(&ready_bar[ls]);
                 }
             }
