@@ -194,21 +194,8 @@ enum : int { KIND_F16 = 0, KIND_TF32 = 1, KIND_I8 = 2 };
 
 // TF32 MMA whose A operand sits in tensor memory: lane = row of the tile, one 32-bit column per K
 // element (8 columns per instruction); B comes from shared memory through its descriptor.
-__device__ __forceinline__ void umma_tf32_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
-                                                 uint32_t accumulate) {
-    asm volatile(
-        "{\n"
-        " .reg .pred p;\n"
-        " setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n"
-        "}\n" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
 // Warp-uniform forms: the whole (converged) warp executes the call and one elected lane issues the
-// instruction. Keeping the issuing loop free of per-lane control flow lets the compiler hold the
-// descriptors in uniform registers instead of moving them there for every instruction.
+// instruction, so the issuing loop has no per-lane control flow.
 __device__ __forceinline__ void umma_tf32_a_tmem_warp(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
                                                       uint32_t accumulate) {
     asm volatile(

@@ -90,6 +90,7 @@ struct CoreCfg {
     static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "TMEM columns must be a power of two");
     static_assert(!kX3 || 2 * kAccBufs * BN + (kATmem ? kLoSlots * 64 : 0) <= 512, "3xTF32 accumulators and A slots must fit TMEM");
     static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
+    static_assert(!kX3 || STAGES >= kLoSlots, "the stage barriers double as lo-slot barriers: the raw ring must be at least as deep");
 };
 
 struct AbortCtx {
@@ -218,8 +219,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);  // TMA data landed
     uint64_t* empty_bar = full_bar + STAGES;                 // MMAs that read the stage retired
     uint64_t* ready_bar = empty_bar + STAGES;                // 3xTF32: lo slot written (2)
-    uint64_t* lofree_bar = ready_bar + 4;                    // 3xTF32: MMAs that read the lo slot retired
-    uint64_t* tfull_bar = lofree_bar + 4;                    // accumulator complete (2)
+    uint64_t* tfull_bar = ready_bar + 4;                     // accumulator complete (2)
     uint64_t* tempty_bar = tfull_bar + 2;                    // accumulator drained (2)
     uint64_t* sempty_bar = tempty_bar + 2;                   // 3xTF32: cross-term accumulator drained (2)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sempty_bar + 2);
@@ -238,7 +238,6 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
         }
         for (int a = 0; a < 4; ++a) {
             ptx::mbar_init(&ready_bar[a], Cfg::kX3 ? Cfg::kSplitThreads : 1);
-            ptx::mbar_init(&lofree_bar[a], 1);
         }
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(&tfull_bar[a], 1);
@@ -436,13 +435,8 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                                 }
                                 issue_main();
                             }
-                            if constexpr (Cfg::kATmem) {
-                                ptx::umma_commit_warp(&empty_bar[s]);
-                                ptx::umma_commit_warp(&lofree_bar[ls]);
-                            } else {
-                                ptx::umma_commit(&empty_bar[s]);
-                                ptx::umma_commit(&lofree_bar[ls]);
-                            }
+                            if constexpr (Cfg::kATmem) ptx::umma_commit_warp(&empty_bar[s]);
+                            else ptx::umma_commit(&empty_bar[s]);
                             if (lane == 0) T2SP_TRACE(p, 4, it);
                         }
                         if (ok) {
@@ -592,7 +586,13 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                     uint8_t* lo = lo_ring + ls * Cfg::kLoBytes;
                     uint8_t* lo_b = lo + Cfg::kLoBOff - Cfg::kABytes;  // lo_b + (offset inside the raw stage) = B_lo position
                     // the lo slot is free once the MMAs that read it last have retired
-                    if (!bounded_wait_warp(&lofree_bar[ls], ((it / Cfg::kLoSlots) & 1) ^ 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
+                    // the lo slot (and the TMEM A slot) is free once the MMAs of k-block it - kLoSlots retired:
+                    // that is a completion of that k-block's stage barrier, so one commit per k-block serves
+                    // the producer and the split warps alike
+                    if (it >= Cfg::kLoSlots) {
+                        const int jt = it - Cfg::kLoSlots;
+                        if (!bounded_wait_warp(&empty_bar[jt % STAGES], (jt / STAGES) & 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
+                    }
                     if (st == 0) T2SP_TRACE(p, 8, it);
                     if (!bounded_wait_warp(&full_bar[s], ph, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
                     if (st == 0) T2SP_TRACE(p, 1, it);
