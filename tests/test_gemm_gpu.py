@@ -293,3 +293,35 @@ def test_large_host_gemm_is_pipelined_and_identical(lib):
     assert np.array_equal(C1, C2)
     rows = slice(1000, 1064)
     assert normwise(C1[rows], O.gemm_h16(np.ascontiguousarray(A[rows]), B, 0, acc64=True)) <= 1e-5
+
+
+def test_concurrent_host_threads(lib):
+    """The library is re-entrant (per-thread stream and status word, reference: single-shot globals in
+    t2s/src/AOT-OpenCL-Runtime.cpp:25-34): two host threads issue different contractions at once."""
+    import threading
+    import t2sp_b200
+    from t2sp_b200 import Buffer
+    jobs = [("f32", 384, 320, 520, 41), ("bf16", 512, 768, 1024, 42)]
+    errors = []
+
+    def work(dtype, M, N, K, seed):
+        try:
+            A, B = O.uniform(seed, 1, (M, K)), O.uniform(seed, 2, (K, N))
+            if dtype == "bf16":
+                A, B = O.to_bf16(A), O.to_bf16(B)
+                truth = O.bf16_to_f32(A).astype(np.float64) @ O.bf16_to_f32(B).astype(np.float64)
+            else:
+                truth = A.astype(np.float64) @ B.astype(np.float64)
+            for _ in range(8):
+                rc, C = call_gemm(A, B, dtype)
+                if rc != 0 or normwise(C, truth) > (TOL_BF16 if dtype == "bf16" else TOL_FP32):
+                    errors.append((dtype, rc, normwise(C, truth)))
+        except Exception as e:  # surfaced by the assertion below
+            errors.append((dtype, repr(e)))
+
+    threads = [threading.Thread(target=work, args=j) for j in jobs]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
