@@ -22,6 +22,10 @@ $CXX $FLAGS $OFLAGS -DTINY -DREF_GEMM    -I $PERF/gemm    $PERF/gemm/gemm-run-fp
 $CXX $FLAGS $OFLAGS -DTINY -DREF_CONV    -I $PERF/conv    $PERF/conv/conv-run-fpga.cpp       $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_conv_tiny
 $CXX $FLAGS $OFLAGS -DTINY -DREF_CAPSULE -I $PERF/capsule $PERF/capsule/capsule-run-fpga.cpp $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_capsule_tiny
 $CXX $FLAGS $OFLAGS -DREF_AOT_GEMM $REF/t2s/tests/correctness/aot/gemm-run.cpp $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_aot_gemm
+$CXX $FLAGS $OFLAGS -DTINY -DREF_SYRK -I $PERF/syrk $PERF/syrk/syrk-run-fpga.cpp $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_syrk_tiny
+ONEC="$REF/t2s/tests/correctness/oneapi-integration"
+$CXX -I $HERE/pin_include $FLAGS $OFLAGS -DTINY -DFPGA_EMULATOR -DREF_ONEAPI_CONV    -I $ONEC $ONEC/oneapi-target-5-run.cpp $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_oneapi_conv_tiny
+$CXX -I $HERE/pin_include $FLAGS $OFLAGS -DTINY -DFPGA_EMULATOR -DREF_ONEAPI_CAPSULE -I $ONEC $ONEC/oneapi-target-6-run.cpp $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_oneapi_capsule_tiny
 
 # (2) the same drivers against the product
 LINK="-L $ROOT/t2sp_b200 -lt2sp_b200 -Wl,-rpath,\$ORIGIN/../../t2sp_b200"

@@ -387,4 +387,85 @@ double oracle_max_abs(const float* x, size_t n) {
     return m;
 }
 
+// ------------------------------------------------------------------------------ SYRK (folded output)
+// Out(jjj,iii,jj,ii,j,i) = Alpha * sum_{k ascending} A(k,r) * A(k,c) + Beta * C(c,r)
+//                                                   t2s/tests/performance/syrk/syrk.cpp:38-73
+// with ti = iii + III*ii + III*II*i, tj = jjj + III*jj + III*II*j, N = III*II*I and
+//   (r, c) = (N-1-ti, N-1-tj) where i >= j ("is_bot"), (ti, tj - III*II) otherwise;
+// loop bounds j in [0, I], i in [0, I/2) (syrk.cpp:80-86). A: (K,N) k innermost; C: (N,N), element
+// C(x, y) at y*ldc + x; O dense (III,III,II,II,I+1,Irows), only rows i < I/2 are written.
+// Golden loop: syrk-run-fpga.cpp:70-106.
+void oracle_syrk_f32(const float* A, const float* C, float* O, int K, int III, int II, int I, int Irows, int ldc,
+                     float alpha, float beta, int acc64) {
+    const int t = III * II, N = t * I;
+    par_for((I / 2) * (I + 1), [&](int ij) {
+        const int i = ij / (I + 1), j = ij % (I + 1);
+        for (int ii = 0; ii < II; ++ii)
+            for (int jj = 0; jj < II; ++jj)
+                for (int iii = 0; iii < III; ++iii)
+                    for (int jjj = 0; jjj < III; ++jjj) {
+                        const int ti = iii + III * ii + t * i, tj = jjj + III * jj + t * j;
+                        const int r = i >= j ? N - 1 - ti : ti, c = i >= j ? N - 1 - tj : tj - t;
+                        const float* ar = A + size_t(r) * K;
+                        const float* ac = A + size_t(c) * K;
+                        float v;
+                        if (acc64) {
+                            double z = 0.0;
+                            for (int k = 0; k < K; ++k) z += double(ar[k]) * double(ac[k]);
+                            v = float(double(alpha) * z + double(beta) * double(C[size_t(r) * ldc + c]));
+                        } else {
+                            float z = 0.f;
+                            for (int k = 0; k < K; ++k) z = z + ar[k] * ac[k];
+                            v = alpha * z + beta * C[size_t(r) * ldc + c];
+                        }
+                        const size_t off = jjj + size_t(III) * (iii + size_t(III) * (jj + size_t(II) * (ii + size_t(II) * (j + size_t(I + 1) * i))));
+                        (void)Irows;
+                        O[off] = v;
+                    }
+    });
+}
+
+// ------------------------------------------------------------------------------ N-D operand layouts (oneAPI flow)
+// conv:    I(iy, ix, ci, n), K(ky, kx, ci, co)      t2s/tests/correctness/oneapi-integration/oneapi-target-5-conv.cpp:58-62
+// capsule: P(mk, mx, ci, iy, ix, n), W(my, mk, ci, co, ky, kx)                        oneapi-target-6-capsule.cpp:57-61
+// Same sums and summation order as the 2-D specifications; these re-lay the operands out into the
+// 2-D buffers of oracle_conv_f32 / oracle_capsule_f32 (CII = CI) on the CPU.
+void oracle_conv_nd_to_2d(const float* I4, const float* K4, float* I2, float* K2, int N, int CI, int CO, int KY, int KX,
+                          int IY, int IX) {
+    for (int n = 0; n < N; ++n)
+        for (int ci = 0; ci < CI; ++ci)
+            for (int ix = 0; ix < IX; ++ix)
+                for (int iy = 0; iy < IY; ++iy)
+                    I2[(size_t(ci) + size_t(CI) * n) + size_t(CI) * N * (iy + size_t(IY) * ix)] =
+                        I4[iy + size_t(IY) * (ix + size_t(IX) * (ci + size_t(CI) * n))];
+    for (int co = 0; co < CO; ++co)
+        for (int ci = 0; ci < CI; ++ci)
+            for (int kx = 0; kx < KX; ++kx)
+                for (int ky = 0; ky < KY; ++ky)
+                    K2[(size_t(co) + size_t(CO) * kx) + size_t(CO) * KX * (ci + size_t(CI) * ky)] =
+                        K4[ky + size_t(KY) * (kx + size_t(KX) * (ci + size_t(CI) * co))];
+}
+
+void oracle_capsule_nd_to_2d(const float* P6, const float* W6, float* P2, float* W2, int N, int CI, int CO, int KY, int KX,
+                             int IY, int IX, int MY, int MX, int MK) {
+    const size_t p0 = size_t(CI) * MK * MX;  // extent of dimension 0 of P2 (NN = 1)
+    for (int n = 0; n < N; ++n)
+        for (int ix = 0; ix < IX; ++ix)
+            for (int iy = 0; iy < IY; ++iy)
+                for (int ci = 0; ci < CI; ++ci)
+                    for (int mx = 0; mx < MX; ++mx)
+                        for (int mk = 0; mk < MK; ++mk)
+                            P2[(ci + size_t(CI) * (mk + size_t(MK) * mx)) + p0 * (iy + size_t(IY) * (ix + size_t(IX) * n))] =
+                                P6[mk + size_t(MK) * (mx + size_t(MX) * (ci + size_t(CI) * (iy + size_t(IY) * (ix + size_t(IX) * n))))];
+    const size_t w0 = size_t(CO) * MY;
+    for (int kx = 0; kx < KX; ++kx)
+        for (int ky = 0; ky < KY; ++ky)
+            for (int co = 0; co < CO; ++co)
+                for (int ci = 0; ci < CI; ++ci)
+                    for (int mk = 0; mk < MK; ++mk)
+                        for (int my = 0; my < MY; ++my)
+                            W2[(co + size_t(CO) * my) + w0 * (ci + size_t(CI) * (ky + size_t(KY) * (kx + size_t(KX) * mk)))] =
+                                W6[my + size_t(MY) * (mk + size_t(MK) * (ci + size_t(CI) * (co + size_t(CO) * (ky + size_t(KY) * kx))))];
+}
+
 }  // extern "C"

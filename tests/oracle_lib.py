@@ -121,6 +121,44 @@ def capsule_tile_layout(V2, N, NN, COOO, COO, COout, YYY_XXX, YY_XX, Y_X, MY, MX
     return out
 
 
+def syrk_f32(A, C, III, II, I, alpha, beta, acc64=False):
+    """A: (N,K), C: (N,N) -> folded O: (I, I+1, II, II, III, III) (rows i >= I/2 stay NaN: the design
+    does not write them)."""
+    N, K = A.shape
+    Ofold = np.full((I, I + 1, II, II, III, III), np.nan, np.float32)
+    L = load()
+    L.oracle_syrk_f32.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 6 + [ctypes.c_float] * 2 + [ctypes.c_int]
+    L.oracle_syrk_f32(_p(A), _p(C), _p(Ofold), K, III, II, I, I, C.shape[1], alpha, beta, int(acc64))
+    return Ofold
+
+
+def conv_nd_f32(I4, K4, tiles, acc64=False):
+    """I4: (N,CI,IX,IY), K4: (CO,CI,KX,KY) -> the 10-D tiled output of the oneAPI flow."""
+    N, CI, IX, IY = I4.shape
+    CO, _, KX, KY = K4.shape
+    COOO, YYY, XXX, COO, YY, XX, Y, X = tiles
+    OY, OX = IY - KY + 1, IX - KX + 1
+    I2 = np.empty((IY * IX, CI * N), np.float32)
+    K2 = np.empty((CI * KY, CO * KX), np.float32)
+    load().oracle_conv_nd_to_2d(_p(I4), _p(K4), _p(I2), _p(K2), N, CI, CO, KY, KX, IY, IX)
+    return conv_tile_layout(conv_f32(I2, K2, N, CI, CO, KY, KX, OY, OX, acc64=acc64), N, COOO, YYY, XXX, COO, YY, XX, Y, X,
+                            CO // (COOO * COO))
+
+
+def capsule_nd_f32(P6, W6, vt, s, acc64=False):
+    """P6: (N,IX,IY,CI,MX,MK), W6: (KX,KY,CO,CI,MK,MY) -> the 9-D tiled output of the oneAPI flow."""
+    N, IX, IY, CI, MX, MK = P6.shape
+    KX, KY, CO, _, _, MY = W6.shape
+    COOO, YYY_XXX, YY_XX, Y_X, COO = vt
+    OY, OX = (IY - KY + s) // s, (IX - KX + s) // s
+    P2 = np.empty((IY * IX * N, CI * MK * MX), np.float32)
+    W2 = np.empty((CI * KY * KX * MK, CO * MY), np.float32)
+    load().oracle_capsule_nd_to_2d(_p(P6), _p(W6), _p(P2), _p(W2), N, CI, CO, KY, KX, IY, IX, MY, MX, MK)
+    V2 = capsule_f32(P2, W2, N, 1, CI, CI, CO, KY, KX, OY, OX, MY, MX, MK, s, acc64=acc64)
+    V10 = capsule_tile_layout(V2, N, 1, COOO, COO, CO // (COOO * COO), YYY_XXX, YY_XX, Y_X, MY, MX, OY, OX)
+    return V10.reshape(N, CO // (COOO * COO), COO, MX, MY, Y_X, YY_XX, YYY_XXX, COOO)  # the unit NN axis dropped
+
+
 def ttm_f32(a, b, acc64=False):
     """a: (J,I,L), b: (K,L) -> c: (K,J,I)."""
     J, I, L = a.shape

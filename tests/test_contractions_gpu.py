@@ -121,3 +121,4 @@ def test_syrk_folded_output(lib, III, II, I, K):
     assert not np.isnan(got[:I // 2]).any()
     assert np.isnan(got[I // 2:]).all(), "rows i >= I/2 of the folded buffer are not part of the design's output"
     assert normwise(got[:I // 2], want[:I // 2]) <= TOL_FP32
+    assert normwise(got[:I // 2], O.syrk_f32(A, Cs, III, II, I, alpha, beta, acc64=True)[:I // 2]) <= TOL_FP32

@@ -181,6 +181,7 @@ def test_conv_nd_layout(lib, N, CI, CO, KY, KX, tiles):
     got = ob.keepalive
     assert not np.isnan(got).any()
     assert normwise(got, want) <= TOL_FP32
+    assert normwise(got, O.conv_nd_f32(I, K, tiles, acc64=True)) <= TOL_FP32   # the pinned oracle agrees
 
 
 def test_conv_nd_rejects_inconsistent_extents(lib):
@@ -225,3 +226,4 @@ def test_capsule_nd_layout(lib, N, CI, CO, OY, OX, s, vt):
         blk = truth[:, :, ox, oy].reshape(N, CO // (COOO * COO), COO, COOO, MX, MY)  # [n, co_o, coo, cooo, mx, my]
         want[:, :, :, :, :, c, b, a, :] = blk.transpose(0, 1, 2, 4, 5, 3)
     assert normwise(got, want) <= TOL_FP32
+    assert normwise(got, O.capsule_nd_f32(P, W, vt, s, acc64=True)) <= TOL_FP32   # the pinned oracle agrees
