@@ -175,7 +175,7 @@ void add_digit(Digits& d, int div, int mod, long long stride) { add_digit2(d, di
 
 // fp32 contractions move to CTA pairs (256 x 256 or 256 x 128 tiles) when such tiles, cut along the
 // contraction where that pays (x3_pick_splits), occupy most SM pairs; returns the pair tile width or 0.
-int x3_pick_splits(int tiles, int total_kb);
+int x3_pick_splits(int tiles, int total_kb, bool scatter = false);
 int x3_pair_width(long long M, int N, int tile_rows, int num_kb) {
     // 256 x 128 pair tiles did not beat the single-CTA kernel (capsule, N = 128: 133 us vs 108 us), so
     // pairs are used for wide outputs only unless $T2SP_B200_PAIR128 asks otherwise.
@@ -190,7 +190,7 @@ int x3_pair_width(long long M, int N, int tile_rows, int num_kb) {
 // How many ranges to cut the contraction of an fp32 pair launch into: the one that minimises
 // (waves of work items) x (k-blocks per item) plus the cost of the summing pass, counted in
 // k-block times; 1 when the tiles already fill the SM pairs or the contraction is short.
-int x3_pick_splits(int tiles, int total_kb) {
+int x3_pick_splits(int tiles, int total_kb, bool scatter) {
     if (getenv("T2SP_B200_NO_SPLITK") || total_kb <= 1) return 1;
     if (const char* f = getenv("T2SP_B200_SPLITK")) {  // forced number of ranges (tests)
         const int s = std::max(1, std::min(atoi(f), total_kb));
@@ -205,7 +205,9 @@ int x3_pick_splits(int tiles, int total_kb) {
         if (per < 8) break;
         const int eff = (total_kb + per - 1) / per;
         const long long waves = (static_cast<long long>(tiles) * eff + pairs - 1) / pairs;
-        const long long cost = waves * per + 8 + eff;
+        // the summing pass decodes a mixed-radix address per element for the tiled layouts: measured
+        // about 30 k-block times dearer than the row-major one at the published conv size
+        const long long cost = waves * per + 8 + eff + (scatter ? 32 : 0);
         if (cost < best_cost) { best_cost = cost; best = eff; }
     }
     return best;
@@ -274,7 +276,7 @@ int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool syn
     CoreParams final_p;
     int slab_rows = 0, ld_part = 0;
     if (pair && arith == AR_TF32X3) {
-        const int splits = x3_pick_splits(tiles, p.total_kb);
+        const int splits = x3_pick_splits(tiles, p.total_kb, p.epi == EPI_SCATTER);
         if (splits > 1) {
             slab_rows = p.tiles_m * 256;
             ld_part = p.tiles_n * bn;
@@ -1363,12 +1365,12 @@ int nd_common_checks(Arg* args, int n) {
 // Gathers input buffer `b` (N-D, any strides) into dense scratch laid out by `d` (d.sstride is
 // filled in here from b's strides through `src_dim`: destination dimension i reads b's src_dim[i]).
 int gather_to_scratch(halide_buffer_t* b, const char* name, t2sp::PermuteDesc d, const int* src_dim, size_t dst_elems,
-                      Scratch* out) {
+                      Scratch* out, bool zero_fill = false) {
     t2sp::DeviceView v;
     if (int e = t2sp::rt_input_view(b, name, &v)) return e;
     out->p = t2sp::rt_alloc(dst_elems * 4);
     if (!out->p) { t2sp::rt_drop_view(&v); return halide_error_code_device_malloc_failed; }
-    cudaMemsetAsync(out->p, 0, dst_elems * 4, t2sp::rt_stream());
+    if (zero_fill) cudaMemsetAsync(out->p, 0, dst_elems * 4, t2sp::rt_stream());  // the copy leaves padding untouched
     for (int i = 0; i < d.nd; ++i) d.sstride[i] = b->dim[src_dim[i]].stride;
     const uint32_t* src = static_cast<const uint32_t*>(v.ptr) + origin_offset(b);
     const cudaError_t e = t2sp::permute_copy_launch(src, out->p, d, t2sp::rt_stream());
@@ -1403,13 +1405,29 @@ extern "C" int t2sp_b200_conv_nd(halide_buffer_t* I, halide_buffer_t* K, halide_
     d.CI = CIp;
     Scratch si, sk;
     {
-        t2sp::PermuteDesc pd;
-        memset(&pd, 0, sizeof(pd));
-        pd.nd = 4;  // destination order (ci, n, iy, ix)
-        const int ext[4] = {CI, N, IY, IX}, src[4] = {2, 3, 0, 1};
-        const long long ds[4] = {1, CIp, (long long)CIp * N, (long long)CIp * N * IY};
-        for (int i = 0; i < 4; ++i) { pd.ext[i] = ext[i]; pd.dstride[i] = ds[i]; }
-        if (int e = gather_to_scratch(I, "I", pd, src, size_t(CIp) * N * IY * IX, &si)) return e;
+        // destination (ci, n, iy, ix). A dense input is one batched matrix transpose per image n:
+        // rows = ci (pitch IY*IX), columns = pixels iy + IY*ix  ->  rows = pixels (pitch CIp*N), columns = ci
+        const bool dense = I->dim[1].stride == IY && I->dim[2].stride == IY * IX && N <= 65535;
+        if (dense && CIp == CI) {
+            t2sp::DeviceView v;
+            if (int e = t2sp::rt_input_view(I, "I", &v)) return e;
+            si.p = t2sp::rt_alloc(size_t(CIp) * N * IY * IX * 4);
+            if (!si.p) { t2sp::rt_drop_view(&v); return halide_error_code_device_malloc_failed; }
+            const uint32_t* src = static_cast<const uint32_t*>(v.ptr) + origin_offset(I);
+            const cudaError_t e = t2sp::transpose32_launch(src, (long long)IY * IX, si.p, (long long)CIp * N, CI, IY * IX,
+                                                           t2sp::rt_stream(), N, I->dim[3].stride, CIp);
+            t2sp::rt_count_launch(1);
+            t2sp::rt_drop_view(&v);
+            if (e != cudaSuccess) return halide_error_code_device_run_failed;
+        } else {
+            t2sp::PermuteDesc pd;
+            memset(&pd, 0, sizeof(pd));
+            pd.nd = 4;
+            const int ext[4] = {CI, N, IY, IX}, src[4] = {2, 3, 0, 1};
+            const long long ds[4] = {1, CIp, (long long)CIp * N, (long long)CIp * N * IY};
+            for (int i = 0; i < 4; ++i) { pd.ext[i] = ext[i]; pd.dstride[i] = ds[i]; }
+            if (int e = gather_to_scratch(I, "I", pd, src, size_t(CIp) * N * IY * IX, &si, CIp != CI)) return e;
+        }
     }
     {
         t2sp::PermuteDesc pd;
@@ -1418,7 +1436,7 @@ extern "C" int t2sp_b200_conv_nd(halide_buffer_t* I, halide_buffer_t* K, halide_
         const int ext[4] = {CO, KX, CI, KY}, src[4] = {3, 1, 2, 0};
         const long long ds[4] = {1, CO, (long long)CO * KX, (long long)CO * KX * CIp};
         for (int i = 0; i < 4; ++i) { pd.ext[i] = ext[i]; pd.dstride[i] = ds[i]; }
-        if (int e = gather_to_scratch(K, "K", pd, src, size_t(CO) * KX * CIp * KY, &sk)) return e;
+        if (int e = gather_to_scratch(K, "K", pd, src, size_t(CO) * KX * CIp * KY, &sk, CIp != CI)) return e;
     }
     halide_buffer_t i2, k2;
     halide_dimension_t di[2], dk[2];

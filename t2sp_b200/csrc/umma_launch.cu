@@ -260,9 +260,13 @@ cudaError_t x3pair_launch(int op, int un, const CoreParams& p, int grid, cudaStr
     return cudaErrorInvalidValue;
 }
 
-__global__ void transpose32_kernel(const uint32_t* __restrict__ src, long long ld_src, uint32_t* __restrict__ dst,
-                                   long long ld_dst, int rows, int cols) {
+// dst[z][c][r] = src[z][r][c] for `batch` matrices of rows x cols 32-bit elements (pitches and batch
+// strides in elements), through a 32 x 32 shared-memory tile so that reads and writes both coalesce.
+__global__ void transpose32_kernel(const uint32_t* __restrict__ src, long long ld_src, long long bs_src,
+                                   uint32_t* __restrict__ dst, long long ld_dst, long long bs_dst, int rows, int cols) {
     __shared__ uint32_t tile[32][33];
+    src += blockIdx.z * bs_src;
+    dst += blockIdx.z * bs_dst;
     const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
     for (int j = threadIdx.y; j < 32; j += 8) {
         const int r = r0 + j, c = c0 + threadIdx.x;
@@ -276,11 +280,11 @@ __global__ void transpose32_kernel(const uint32_t* __restrict__ src, long long l
 }
 
 cudaError_t transpose32_launch(const void* src, long long ld_src, void* dst, long long ld_dst, int rows, int cols,
-                               cudaStream_t stream) {
-    if (rows <= 0 || cols <= 0) return cudaSuccess;
-    dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
-    transpose32_kernel<<<grid, block, 0, stream>>>(static_cast<const uint32_t*>(src), ld_src, static_cast<uint32_t*>(dst),
-                                                   ld_dst, rows, cols);
+                               cudaStream_t stream, int batch, long long bs_src, long long bs_dst) {
+    if (rows <= 0 || cols <= 0 || batch <= 0) return cudaSuccess;
+    dim3 grid((cols + 31) / 32, (rows + 31) / 32, batch), block(32, 8);
+    transpose32_kernel<<<grid, block, 0, stream>>>(static_cast<const uint32_t*>(src), ld_src, bs_src,
+                                                   static_cast<uint32_t*>(dst), ld_dst, bs_dst, rows, cols);
     return cudaGetLastError();
 }
 

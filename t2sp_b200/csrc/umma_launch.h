@@ -28,9 +28,10 @@ cudaError_t pair2_launch(int arith, int op, const CoreParams& p, int grid, cudaS
 // p.idesc describes a 256 x un TF32 MMA.
 cudaError_t x3pair_launch(int op, int un, const CoreParams& p, int grid, cudaStream_t stream);
 
-// dst[c][r] = src[r][c] for a rows x cols matrix of 32-bit elements (pitches in elements).
+// dst[z][c][r] = src[z][r][c] for `batch` rows x cols matrices of 32-bit elements (pitches and batch
+// strides in elements; batch <= 65535).
 cudaError_t transpose32_launch(const void* src, long long ld_src, void* dst, long long ld_dst, int rows, int cols,
-                               cudaStream_t stream);
+                               cudaStream_t stream, int batch = 1, long long bs_src = 0, long long bs_dst = 0);
 
 // Number of SMs of the current device (cached).
 int core_sm_count();

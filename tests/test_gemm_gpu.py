@@ -222,8 +222,10 @@ def test_fp32_split_k(lib, monkeypatch, M, N, K, trans_b, force):
     assert componentwise(split, truth, O.gemm_f32(np.abs(A), np.abs(B), acc64=True)) <= TOL_FP32
 
 
-def test_fp32_split_k_tiled_layout_and_blas_epilogue(lib):
-    """The summing kernel applies the call's own epilogue: the 6-D tiled layout and alpha/beta."""
+def test_fp32_split_k_tiled_layout_and_blas_epilogue(lib, monkeypatch):
+    """The summing kernel applies the call's own epilogue: the 6-D tiled layout and alpha/beta.
+    (Split-K is forced: by itself the library avoids it for tiled layouts, whose summing pass is dear.)"""
+    monkeypatch.setenv("T2SP_B200_SPLITK", "4")
     JJJ, III, JJ, II = 8, 16, 2, 4
     M, N, K = III * II * 32, JJJ * JJ * 32, 1024
     A, B = O.uniform(13, 1, (M, K)), O.uniform(13, 2, (K, N))
