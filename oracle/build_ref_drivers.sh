@@ -51,6 +51,13 @@ if [ -f "$ROOT/t2sp_b200/libt2sp_b200.so" ]; then
   $CXX $FLAGS -iquote $ROOT/include -I $SYRK $SYRK/ssyrk-run-fpga.cpp $STUBS/blas-syrk.cpp $STUBS/syrk-interface.cpp $LINK -o $ROOT/tests/_bin/blas_ssyrk_s10
   # the SYRK design's own driver: checks the folded 6-D output element by element (C not symmetric here)
   $CXX $FLAGS -DTINY -I $PERF/syrk $PERF/syrk/syrk-run-fpga.cpp $STUBS/syrk-interface.cpp $LINK -o $ROOT/tests/_bin/syrk_tiny
+  # the GPU-flow drivers, written against the Level Zero helper layer (util/l0_rt_helpers.h): this
+  # repository's header of the same name and API stands in for it; -DITER=1 is the reference's
+  # correctness mode (tests.sh:40), sizes are the GPU design's (2048^3 GEMM, 4 x 256 x 64 x 64 conv, ...)
+  L0="-O3 -I $ROOT/include/l0 -DITER=1"
+  $CXX $FLAGS $L0 -I $PERF/gemm    $PERF/gemm/gemm-run-gpu.cpp       $STUBS/l0_shim.cpp $LINK -o $ROOT/tests/_bin/gemm_gpu_flow
+  $CXX $FLAGS $L0 -I $PERF/conv    $PERF/conv/conv-run-gpu.cpp       $STUBS/l0_shim.cpp $LINK -o $ROOT/tests/_bin/conv_gpu_flow
+  $CXX $FLAGS $L0 -I $PERF/capsule $PERF/capsule/capsule-run-gpu.cpp $STUBS/l0_shim.cpp $LINK -o $ROOT/tests/_bin/capsule_gpu_flow
   # performance mode of the same drivers (no -DTINY: the A10 design constants and problem sizes),
   # with this repository's implementation of the Roofline.h helpers in place of Roofline.cpp
   SHIM="$ROOT/t2sp_b200/csrc/roofline_shim.cpp"

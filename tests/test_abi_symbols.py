@@ -40,6 +40,17 @@ def test_headers_compile(lang, tmp_path):
     assert subprocess.run([str(exe)]).returncode == 0
 
 
+def test_l0_helper_header_compiles_beside_a_design_header(tmp_path):
+    """include/l0/l0_rt_helpers.h is included after a design's const-parameters.h, whose macros are
+    single letters (I, K, N, X ...): it must not use such identifiers itself."""
+    src = tmp_path / "t.cpp"
+    src.write_text('#define GPU 1\n#include "const-parameters.h"\n#define K 64\n#define J 128\n#define I 32\n#define N 4\n'
+                   '#include <math.h>\n#include "l0_rt_helpers.h"\n#include <iostream>\n'
+                   'int main() { auto [d, v, c] = findDriverAndDevice(); (void)d; (void)v; (void)c; return 0; }\n')
+    subprocess.run(["g++", "-std=c++17", "-c", "-I", os.path.join(INC, "l0"), "-I", os.path.join(ROOT, "tests", "designs"),
+                    str(src), "-o", str(tmp_path / "t.o")], check=True, capture_output=True)
+
+
 def test_stubs_define_the_interface_symbols(lib, tmp_path):
     """gemm / conv / capsule / GEMM / ttm / mttkrp are defined by the per-design stubs; build them
     against the test design's constants and look the symbols up."""
@@ -48,7 +59,7 @@ def test_stubs_define_the_interface_symbols(lib, tmp_path):
     so = tmp_path / "libstubs.so"
     objs = []
     for f in ("gemm-interface.cpp", "conv-interface.cpp", "capsule-interface.cpp", "host.cpp", "ttm-mttkrp-interface.cpp",
-              "syrk-interface.cpp", "blas-syrk.cpp", "blas-gemm.cpp"):
+              "syrk-interface.cpp", "blas-syrk.cpp", "blas-gemm.cpp", "l0_shim.cpp"):
         o = tmp_path / (f + ".o")
         subprocess.run(["g++", "-fPIC", "-c", "-I", INC, "-I", os.path.join(ROOT, "tests", "designs"),
                         os.path.join(stubs, f), "-o", str(o)], check=True, capture_output=True)
@@ -56,7 +67,7 @@ def test_stubs_define_the_interface_symbols(lib, tmp_path):
     subprocess.run(["g++", "-shared", "-o", str(so)] + objs + ["-L", os.path.dirname(LIB_PATH), "-lt2sp_b200",
                     "-Wl,-rpath," + os.path.dirname(LIB_PATH)], check=True, capture_output=True)
     S = ctypes.CDLL(str(so))
-    for n in ("gemm", "conv", "capsule", "GEMM", "ttm", "mttkrp", "syrk"):
+    for n in ("gemm", "conv", "capsule", "GEMM", "ttm", "mttkrp", "syrk", "t2sp_l0_image_create", "t2sp_l0_run"):
         assert hasattr(S, n)
     assert S.syrk(0, ctypes.c_float(1), ctypes.c_float(0), None, None, None) == -12
     # null buffers are rejected by the generic entry behind the stub, with the reference's code

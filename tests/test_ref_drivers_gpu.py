@@ -33,6 +33,19 @@ def test_unmodified_reference_driver(lib, name, tmp_path):
     assert "ERROR" not in res.stdout
 
 
+@pytest.mark.parametrize("name", ["gemm_gpu_flow", "conv_gpu_flow", "capsule_gpu_flow"])
+def test_unmodified_gpu_flow_driver(lib, name, tmp_path):
+    """The reference's GPU-flow drivers (t2s/tests/performance/{gemm,conv,capsule}/*-run-gpu.cpp, -DITER=1),
+    written against util/l0_rt_helpers.h: built with include/l0/l0_rt_helpers.h in its place. Each checks the
+    plain 2-D result of the GPU design's size with its own golden loop and prints `Pass!`."""
+    exe = os.path.join(ROOT, "tests", "_bin", name)
+    if not os.path.exists(exe):
+        pytest.skip("driver binary not built (needs the reference tree at build time)")
+    res = subprocess.run([exe], capture_output=True, text=True, timeout=600, cwd=str(tmp_path))
+    assert res.returncode == 0, (res.stdout[-300:], res.stderr[-500:])
+    assert res.stdout.strip().splitlines()[-1].startswith("Pass")
+
+
 def test_golden_aot_gemm_fixture(lib):
     a, b, exact = KAT["aot_gemm_a"], KAT["aot_gemm_b"], KAT["aot_gemm_c_exact"].astype(np.float64)
     rc, C6 = call_gemm(a, b, "f32", tiled=(4, 2, 4, 4))
