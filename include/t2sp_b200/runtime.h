@@ -26,27 +26,46 @@ extern "C" {
 #endif
 
 #ifdef T2SP_B200_OWN_HALIDE_ABI
-/* Subset of halide_error_code_t (HalideRuntime.h:957-1143) that this library returns. */
+/* halide_error_code_t (HalideRuntime.h:957-1143): the codes this library and its error reporters return. */
 enum halide_error_code_t {
     halide_error_code_success = 0,
     halide_error_code_generic_error = -1,
+    halide_error_code_explicit_bounds_too_small = -2,
     halide_error_code_bad_type = -3,
     halide_error_code_access_out_of_bounds = -4,
     halide_error_code_buffer_allocation_too_large = -5,
     halide_error_code_buffer_extents_too_large = -6,
+    halide_error_code_constraints_make_required_region_smaller = -7,
     halide_error_code_constraint_violated = -8,
+    halide_error_code_param_too_small = -9,
+    halide_error_code_param_too_large = -10,
     halide_error_code_out_of_memory = -11,
     halide_error_code_buffer_argument_is_null = -12,
+    halide_error_code_debug_to_file_failed = -13,
     halide_error_code_copy_to_host_failed = -14,
     halide_error_code_copy_to_device_failed = -15,
     halide_error_code_device_malloc_failed = -16,
     halide_error_code_device_sync_failed = -17,
     halide_error_code_device_free_failed = -18,
+    halide_error_code_no_device_interface = -19,
     halide_error_code_device_run_failed = -23,
+    halide_error_code_unaligned_host_ptr = -24,
+    halide_error_code_bad_fold = -25,
+    halide_error_code_fold_factor_too_small = -26,
+    halide_error_code_requirement_failed = -27,
     halide_error_code_buffer_extents_negative = -28,
+    halide_error_code_failed_to_upgrade_buffer_t = -29,
+    halide_error_code_failed_to_downgrade_buffer_t = -30,
+    halide_error_code_specialize_fail = -31,
+    halide_error_code_device_wrap_native_failed = -32,
     halide_error_code_host_is_null = -34,
+    halide_error_code_bad_extern_fold = -35,
     halide_error_code_device_interface_no_device = -36,
-    halide_error_code_bad_dimensions = -43
+    halide_error_code_host_and_device_dirty = -37,
+    halide_error_code_buffer_is_null = -38,
+    halide_error_code_device_buffer_copy_failed = -39,
+    halide_error_code_bad_dimensions = -43,
+    halide_error_code_integer_division_by_zero = -44
 };
 #endif
 

@@ -13,7 +13,7 @@ ROOT = os.path.dirname(HERE)
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libt2sp_b200.so")
 
-SOURCES = ["umma_launch.cu", "host_rt.cpp", "errors.cpp", "ops.cpp", "noalloc.cu"]
+SOURCES = ["umma_launch.cu", "host_rt.cpp", "errors.cpp", "halide_rt.cpp", "ops.cpp", "noalloc.cu"]
 
 
 def _nvcc():

@@ -73,3 +73,24 @@ def test_stubs_define_the_interface_symbols(lib, tmp_path):
     # null buffers are rejected by the generic entry behind the stub, with the reference's code
     assert S.gemm(None, None, None) == -12
     assert S.capsule(None, None, None) == -12
+
+
+def test_aot_runtime_names_are_exported(lib):
+    """The names the reference's AOT runtime exports (t2s/src/AOT-OpenCL-Runtime.cpp:56-727) exist here
+    too, weak, and the reporters return their halide_error_code_t."""
+    for n in ("halide_opencl_device_interface", "halide_device_malloc", "halide_device_and_host_malloc",
+              "halide_device_and_host_free", "halide_device_and_host_free_as_destructor", "halide_device_host_nop_free",
+              "halide_opencl_wait_for_kernels_finish", "halide_opencl_buffer_copy", "halide_copy_to_device",
+              "halide_copy_to_host", "halide_error_explicit_bounds_too_small", "halide_error_param_too_large_f64",
+              "halide_error_requirement_failed", "halide_error_integer_division_by_zero"):
+        assert hasattr(lib, n), n
+    lib.halide_error_param_too_small_i64.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int64, ctypes.c_int64]
+    assert lib.halide_error_param_too_small_i64(None, b"p", 1, 5) == -9
+    lib.halide_error_param_too_large_f64.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_double, ctypes.c_double]
+    assert lib.halide_error_param_too_large_f64(None, b"p", 2.0, 1.0) == -10
+    lib.halide_error_requirement_failed.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_char_p]
+    assert lib.halide_error_requirement_failed(None, b"x > 0", b"positive") == -27
+    assert lib.halide_error_integer_division_by_zero(None) == -44
+    lib.halide_opencl_device_interface.restype = ctypes.c_void_p
+    lib.t2sp_b200_device_interface.restype = ctypes.c_void_p
+    assert lib.halide_opencl_device_interface() == lib.t2sp_b200_device_interface()

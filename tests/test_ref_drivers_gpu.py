@@ -118,3 +118,27 @@ def test_unaligned_rows_are_repacked(lib):
     rc, C = call_gemm(A, B, "f32")
     assert rc == 0
     assert np.array_equal(C, (A.astype(np.float64) @ B.astype(np.float64)).astype(np.float32))
+
+
+def test_aot_runtime_entry_points_round_trip(lib):
+    """halide_device_and_host_malloc / halide_copy_to_device / halide_copy_to_host / halide_device_and_host_free
+    under the reference runtime's names (t2s/src/AOT-OpenCL-Runtime.cpp:119-441)."""
+    P = ctypes.c_void_p
+    b = Buffer((64, 16), "f32")          # no host, no device yet
+    lib.halide_device_and_host_malloc.argtypes = [P, P, P]
+    lib.halide_copy_to_device.argtypes = [P, P, P]
+    lib.halide_copy_to_host.argtypes = [P, P]
+    lib.halide_device_and_host_free.argtypes = [P, P]
+    assert lib.halide_device_and_host_malloc(None, b.ptr, None) == 0
+    assert b.raw.host and b.raw.device
+    host = np.ctypeslib.as_array(ctypes.cast(b.raw.host, ctypes.POINTER(ctypes.c_float)), shape=(16, 64))
+    host[:] = np.arange(16 * 64, dtype=np.float32).reshape(16, 64)
+    b.raw.flags |= 1                      # host_dirty
+    assert lib.halide_copy_to_device(None, b.ptr, None) == 0
+    host[:] = -1.0
+    b.raw.flags |= 2                      # device_dirty: the device copy is the current one
+    assert lib.halide_copy_to_host(None, b.ptr) == 0
+    assert np.array_equal(host, np.arange(16 * 64, dtype=np.float32).reshape(16, 64))
+    assert lib.halide_opencl_wait_for_kernels_finish(None) == 0
+    assert lib.halide_device_and_host_free(None, b.ptr) == 0
+    assert not b.raw.host and not b.raw.device
