@@ -58,6 +58,11 @@ if [ -f "$ROOT/t2sp_b200/libt2sp_b200.so" ]; then
   $CXX $FLAGS $L0 -I $PERF/gemm    $PERF/gemm/gemm-run-gpu.cpp       $STUBS/l0_shim.cpp $LINK -o $ROOT/tests/_bin/gemm_gpu_flow
   $CXX $FLAGS $L0 -I $PERF/conv    $PERF/conv/conv-run-gpu.cpp       $STUBS/l0_shim.cpp $LINK -o $ROOT/tests/_bin/conv_gpu_flow
   $CXX $FLAGS $L0 -I $PERF/capsule $PERF/capsule/capsule-run-gpu.cpp $STUBS/l0_shim.cpp $LINK -o $ROOT/tests/_bin/capsule_gpu_flow
+  # the CM-flow drivers (CmDevice / CmSurface2D / CmQueue ...): include/cm stands in for the CM runtime headers
+  CM="-O3 -I $ROOT/include/cm -DITER=1"
+  $CXX $FLAGS $CM -I $PERF/gemm    $PERF/gemm/gemm-run-gpu-cm.cpp       $STUBS/l0_shim.cpp $LINK -o $ROOT/tests/_bin/gemm_cm_flow
+  $CXX $FLAGS $CM -I $PERF/conv    $PERF/conv/conv-run-gpu-cm.cpp       $STUBS/l0_shim.cpp $LINK -o $ROOT/tests/_bin/conv_cm_flow
+  $CXX $FLAGS $CM -I $PERF/capsule $PERF/capsule/capsule-run-gpu-cm.cpp $STUBS/l0_shim.cpp $LINK -o $ROOT/tests/_bin/capsule_cm_flow
   # performance mode of the same drivers (no -DTINY: the A10 design constants and problem sizes),
   # with this repository's implementation of the Roofline.h helpers in place of Roofline.cpp
   SHIM="$ROOT/t2sp_b200/csrc/roofline_shim.cpp"

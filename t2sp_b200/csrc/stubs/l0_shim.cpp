@@ -1,4 +1,4 @@
-// What sits behind include/l0/l0_rt_helpers.h: images as device buffers of this library and the launch
+// What sits behind include/l0/l0_rt_helpers.h and include/cm/cm_rt.h: images / surfaces as device buffers of this library and the launch
 // of the operator a "kernel" names (the reference side: t2s/tests/performance/util/l0_rt_helpers.h:137-153,
 // 326-346 over Level Zero).
 #include <stdio.h>
@@ -32,6 +32,17 @@ extern "C" void* t2sp_l0_image_create(unsigned width, unsigned height, const voi
     }
     return im;
 }
+
+extern "C" int t2sp_l0_image_write(void* image, const void* src) {
+    Image* im = static_cast<Image*>(image);
+    im->buf.host = const_cast<uint8_t*>(static_cast<const uint8_t*>(src));
+    im->buf.flags |= 1;
+    const int rc = t2sp_b200_copy_to_device(&im->buf);
+    im->buf.host = nullptr;
+    return rc;
+}
+
+extern "C" double t2sp_l0_last_kernel_ns(void) { return t2sp_b200_last_kernel_ns(); }
 
 extern "C" int t2sp_l0_image_read(void* image, void* dst) {
     Image* im = static_cast<Image*>(image);

@@ -51,6 +51,16 @@ def test_l0_helper_header_compiles_beside_a_design_header(tmp_path):
                     str(src), "-o", str(tmp_path / "t.o")], check=True, capture_output=True)
 
 
+def test_cm_runtime_headers_compile_beside_a_design_header(tmp_path):
+    src = tmp_path / "t.cpp"
+    src.write_text('#define GPU 1\n#include "const-parameters.h"\n#define K 64\n#define J 128\n#define I 32\n'
+                   '#include <assert.h>\n#include "cm_rt.h"\n#include "common/cm_rt_helpers.h"\n#include "common/isa_helpers.h"\n'
+                   'int main() { CmDevice *d = nullptr; unsigned v = 0; cm_result_check(::CreateCmDevice(d, v)); '
+                   'return cm::util::isa::loadFile("gemm_genx.isa").size() ? 0 : 1; }\n')
+    subprocess.run(["g++", "-std=c++17", "-c", "-I", os.path.join(INC, "cm"), "-I", os.path.join(ROOT, "tests", "designs"),
+                    str(src), "-o", str(tmp_path / "t.o")], check=True, capture_output=True)
+
+
 def test_stubs_define_the_interface_symbols(lib, tmp_path):
     """gemm / conv / capsule / GEMM / ttm / mttkrp are defined by the per-design stubs; build them
     against the test design's constants and look the symbols up."""

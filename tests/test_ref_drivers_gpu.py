@@ -33,10 +33,12 @@ def test_unmodified_reference_driver(lib, name, tmp_path):
     assert "ERROR" not in res.stdout
 
 
-@pytest.mark.parametrize("name", ["gemm_gpu_flow", "conv_gpu_flow", "capsule_gpu_flow"])
+@pytest.mark.parametrize("name", ["gemm_gpu_flow", "conv_gpu_flow", "capsule_gpu_flow", "gemm_cm_flow", "conv_cm_flow",
+                                  "capsule_cm_flow"])
 def test_unmodified_gpu_flow_driver(lib, name, tmp_path):
     """The reference's GPU-flow drivers (t2s/tests/performance/{gemm,conv,capsule}/*-run-gpu.cpp, -DITER=1),
-    written against util/l0_rt_helpers.h: built with include/l0/l0_rt_helpers.h in its place. Each checks the
+    written against util/l0_rt_helpers.h: built with include/l0/l0_rt_helpers.h in its place; and their CM-runtime
+    twins (*-run-gpu-cm.cpp), built with include/cm/ in place of the CM runtime headers. Each checks the
     plain 2-D result of the GPU design's size with its own golden loop and prints `Pass!`."""
     exe = os.path.join(ROOT, "tests", "_bin", name)
     if not os.path.exists(exe):
