@@ -153,6 +153,8 @@ __device__ __forceinline__ void tma_store_2d(const void* map, const void* src, i
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Wait until the shared-memory sources of all committed bulk groups have been read.
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Same, but the newest committed group may still be reading.
+__device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 // Wait until all committed bulk groups have completed (their global writes are done).
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 

@@ -24,8 +24,12 @@ struct Pair2Cfg {
     static constexpr int kThreads = 6 * 32;
     static constexpr int kTmemCols = 512;
     static constexpr int kNumBars = 2 * STAGES + 4;
-    static constexpr int kTailBytes = kNumBars * 8 + 16 + 4 * 256 * 8;
-    static constexpr int kSmemBytes = STAGES * kStageBytes + kCStageBytes + kTailBytes + 1024;
+    // two 32 x 32 fp32 staging tiles per epilogue warp for the TMA-store epilogue; the scatter epilogue,
+    // which does not stage, keeps its per-warp column tables (4 x 256 offsets) in the same bytes
+    static constexpr int kCStageBytes2 = 4 * 2 * 4096;
+    static_assert(kCStageBytes2 >= 4 * 256 * 8, "column tables must fit the staging bytes");
+    static constexpr int kTailBytes = kNumBars * 8 + 16;
+    static constexpr int kSmemBytes = STAGES * kStageBytes + kCStageBytes2 + kTailBytes + 1024;
     static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
 };
 
@@ -37,14 +41,14 @@ umma_pair2_kernel(const __grid_constant__ CoreParams p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* cstage = smem + STAGES * Cfg::kStageBytes;
-    uint8_t* tail = cstage + kCStageBytes;
+    uint8_t* tail = cstage + Cfg::kCStageBytes2;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);  // leader's: both CTAs' TMA data landed
     uint64_t* empty_bar = full_bar + STAGES;                 // per CTA: MMAs that read the stage retired
     uint64_t* tfull_bar = empty_bar + STAGES;                // per CTA: the tile's accumulators are complete ([0] used)
     uint64_t* tempty_bar = tfull_bar + 2;                    // leader's: accumulator of sub-tile 0 / 1 drained by both CTAs
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
     uint32_t* abort_slot = tmem_slot + 1;
-    long long* ntable = reinterpret_cast<long long*>(tmem_slot + 4);
+    long long* ntable = reinterpret_cast<long long*>(cstage);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -93,6 +97,7 @@ umma_pair2_kernel(const __grid_constant__ CoreParams p) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!bounded_wait(&empty_bar[s], ph ^ 1, ab, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+                    T2SP_TRACE(p, 0, it);
                     uint8_t* sa = smem + s * Cfg::kStageBytes;
                     uint8_t* sb = sa + Cfg::kABytes;
                     const uint32_t leader_full = ptx::map_to_cta(&full_bar[s], 0);
@@ -123,8 +128,10 @@ umma_pair2_kernel(const __grid_constant__ CoreParams p) {
                 for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
+                    T2SP_TRACE(p, 8, it);
                     if (!bounded_wait(&full_bar[s], ph, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
                     ptx::tc_fence_after_sync();
+                    T2SP_TRACE(p, 3, it);
                     const uint32_t sa = ptx::smem_u32(smem + s * Cfg::kStageBytes);
                     const uint64_t db = ptx::make_smem_desc(sa + Cfg::kABytes, kLboB, 1024);
 #pragma unroll
@@ -133,6 +140,7 @@ umma_pair2_kernel(const __grid_constant__ CoreParams p) {
                             // the previous tile's accumulator u must have been drained by both CTAs
                             if (!bounded_wait(&tempty_bar[u], (lt & 1) ^ 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
                             ptx::tc_fence_after_sync();
+                            T2SP_TRACE(p, 10, lt * 2 + u);
                         }
                         const uint64_t da = ptx::make_smem_desc(sa + u * Cfg::kSubBytes, 16, 1024);
 #pragma unroll
@@ -143,6 +151,7 @@ umma_pair2_kernel(const __grid_constant__ CoreParams p) {
                     if (!ok) break;
                     ptx::umma_commit_pair(ptx::map_to_cta(&empty_bar[s], 0));
                     ptx::umma_commit_pair(ptx::map_to_cta(&empty_bar[s], 1));
+                    T2SP_TRACE(p, 4, it);
                 }
                 if (ok) {
                     ptx::umma_commit_pair(ptx::map_to_cta(&tfull_bar[0], 0));
@@ -168,23 +177,72 @@ umma_pair2_kernel(const __grid_constant__ CoreParams p) {
             }
             if (!bounded_wait_warp(&tfull_bar[0], lt & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
             ptx::tc_fence_after_sync();
+            if (warp == 2 && lane == 0) T2SP_TRACE(p, 5, lt);
             uint32_t* out32 = reinterpret_cast<uint32_t*>(p.out);
-#pragma unroll 1
-            for (int u = 0; u < 2; ++u) {
-                const int m_warp0 = mb * 512 + u * 256 + static_cast<int>(rank) * kBlockM + q * 32;
-                const int m = m_warp0 + lane;
-                const long long offm = (p.epi == EPI_SCATTER) ? digits_offset(p.dm, m) : 0;
-#pragma unroll 1
-                for (int c = 0; c < Cfg::kUmmaN / 32; ++c) {
-                    uint32_t r[32];
-                    ptx::tmem_ld_32x32(lane_base + u * Cfg::kUmmaN + c * 32, r);
+            if (p.epi == EPI_TMA) {
+                // The 16 chunks of 32 columns (sub-tile 0's eight, then sub-tile 1's) go through two
+                // staging tiles in turn: the load of chunk c+1 from tensor memory is in flight while chunk
+                // c is written to shared memory and handed to the TMA, and a staging tile is rewritten once
+                // the store issued two chunks earlier has read it. An accumulator is released as soon as
+                // its last chunk is in registers. The drain runs at the rate one SM can write towards L2
+                // (measured: a CTA's 256 KB take 8100-8500 cycles, 31-32 bytes per cycle, the same with
+                // coalesced st.global.v4 instead of TMA stores and with the CTAs' drains staggered in time).
+                uint8_t* stage0 = cstage + (warp - 2) * 8192;
+                const int m_q = mb * 512 + static_cast<int>(rank) * kBlockM + q * 32;
+                auto put = [&](const uint32_t (&r)[32], int c) {
+                    uint8_t* buf = stage0 + (c & 1) * 4096;
+                    if (lane == 0) ptx::bulk_wait_read_1();
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                            make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    const int m_warp0 = m_q + (c >> 3) * 256, nc = n0 + (c & 7) * 32;
+                    if (lane == 0) {
+                        if (m_warp0 < p.M && nc < p.N) ptx::tma_store_2d(&p.mapC, buf, nc, m_warp0);
+                        ptx::bulk_commit_group();  // also when nothing was stored: the wait above counts groups
+                    }
+                };
+                auto loaded = [&](int c) {  // chunk c has left tensor memory
                     ptx::tmem_ld_wait();
-                    if (p.epi == EPI_TMA) store_chunk_tma(p, cstage + (warp - 2) * 4096, m_warp0, n0 + c * 32, r, lane);
-                    else if (m < p.M) store_row_chunk(p, out32, m, n0 + c * 32, r, offm, ntab + c * 32);
+                    if ((c & 7) == 7) {
+                        ptx::tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive_peer(&tempty_bar[c >> 3], 0);
+                    }
+                    if (warp == 2 && lane == 0) T2SP_TRACE(p, 6, lt * 16 + c);
+                };
+                uint32_t ra[32], rb[32];
+                ptx::tmem_ld_32x32(lane_base, ra);
+                loaded(0);
+#pragma unroll 1
+                for (int c = 0; c < 16; c += 2) {
+                    ptx::tmem_ld_32x32(lane_base + (c + 1) * 32, rb);
+                    put(ra, c);
+                    loaded(c + 1);
+                    if (c + 2 < 16) ptx::tmem_ld_32x32(lane_base + (c + 2) * 32, ra);
+                    put(rb, c + 1);
+                    if (c + 2 < 16) loaded(c + 2);
+                    if (warp == 2 && lane == 0) T2SP_TRACE(p, 7, lt * 16 + c + 1);
                 }
-                ptx::tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive_peer(&tempty_bar[u], 0);
+            } else {
+#pragma unroll 1
+                for (int u = 0; u < 2; ++u) {
+                    const int m = mb * 512 + u * 256 + static_cast<int>(rank) * kBlockM + q * 32 + lane;
+                    const long long offm = (p.epi == EPI_SCATTER) ? digits_offset(p.dm, m) : 0;
+#pragma unroll 1
+                    for (int c = 0; c < Cfg::kUmmaN / 32; ++c) {
+                        uint32_t r[32];
+                        ptx::tmem_ld_32x32(lane_base + u * Cfg::kUmmaN + c * 32, r);
+                        ptx::tmem_ld_wait();
+                        if (m < p.M) store_row_chunk(p, out32, m, n0 + c * 32, r, offm, ntab + c * 32);
+                    }
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive_peer(&tempty_bar[u], 0);
+                }
             }
         }
     }
