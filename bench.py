@@ -38,6 +38,8 @@ WORKLOADS = {
     "ttm_cfg3": ("ttm", dict(L=256, I=512, J=512, K=256)),
     "mttkrp_cfg3": ("mttkrp", dict(L=512, I=512, K=512, R=64)),
     "capsule_cfg4": ("capsule", dict(N=1, NN=32, CI=32, CII=32, CO=32, KY=3, KX=3, OY=16, OX=16, s=1)),
+    # the GER design's A10 constants with its 32 x 32 outer loops: 10240 x 16384 elements
+    "ger_a10": ("ger", dict(KKK=16, III=10, II=32, KK=32, K=32, I=32)),
 }
 
 
@@ -66,6 +68,9 @@ def flops_bytes(kind, w):
     if kind == "mttkrp":
         f = 2.0 * w["I"] * w["L"] * w["K"] * w["R"] + 2.0 * w["I"] * w["K"] * w["R"]
         return f, 4 * (w["L"] * w["I"] * w["K"] + w["L"] * w["R"] + w["K"] * w["R"] + w["I"] * w["R"])
+    if kind == "ger":
+        ti, tk = w["III"] * w["II"] * w["I"], w["KKK"] * w["KK"] * w["K"]
+        return 2.0 * ti * tk, 4 * (2 * ti * tk + ti + tk)
     if kind == "capsule":
         s = w["s"]
         IY, IX = s * w["OY"] + w["KY"] - s, s * w["OX"] + w["KX"] - s
@@ -101,6 +106,10 @@ def make_inputs(kind, w, seed, rank):
     if kind == "mttkrp":
         return ([O.uniform(seed, 1 + rank, (w["K"], w["I"], w["L"])), O.uniform(seed, 2, (w["R"], w["K"])),
                  O.uniform(seed, 3, (w["R"], w["L"]))], (w["R"], w["I"]), np.float32, ["f32"] * 3)
+    if kind == "ger":
+        ti, tk = w["III"] * w["II"] * w["I"], w["KKK"] * w["KK"] * w["K"]
+        return ([O.uniform(seed, 1 + rank, (ti, tk)), O.uniform(seed, 2, (ti,)), O.uniform(seed, 3, (tk,))],
+                (w["I"], w["K"], w["KK"], w["II"], w["III"], w["KKK"]), np.float32, ["f32"] * 3)
     if kind == "capsule":
         s = w["s"]
         IY, IX = s * w["OY"] + w["KY"] - s, s * w["OX"] + w["KX"] - s
@@ -135,6 +144,8 @@ def call_op(kind, bufs, out, desc):
         return t2sp_b200.capsule(bufs[0], bufs[1], out, desc)
     if kind == "ttm":
         return t2sp_b200.ttm(bufs[0], bufs[1], out, desc)
+    if kind == "ger":
+        return t2sp_b200.ger(bufs[0], bufs[1], bufs[2], out)
     return t2sp_b200.mttkrp(bufs[0], bufs[1], bufs[2], out, desc)
 
 
@@ -228,6 +239,8 @@ def cpu_sample(kind, w, budget_s=12.0):
         O.ttm_f32(arrs[0], arrs[1])
     elif kind == "mttkrp":
         O.mttkrp_f32(arrs[0], arrs[1], arrs[2])
+    elif kind == "ger":
+        O.ger_f32(arrs[0], arrs[1], arrs[2], w["KKK"], w["III"], w["II"], w["KK"], w["K"], w["I"])
     else:
         O.capsule_f32(arrs[0], arrs[1], w["N"], w["NN"], w["CI"], w["CII"], w["CO"], w["KY"], w["KX"], w["OY"], w["OX"],
                       4, 4, 4, w["s"])

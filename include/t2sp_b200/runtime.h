@@ -158,6 +158,12 @@ int t2sp_b200_capsule(halide_buffer_t *P, halide_buffer_t *W, halide_buffer_t *V
  * ti = iii + III*ii + III*II*i, tj = jjj + III*jj + III*II*j. OpA is ignored, as in the specification. */
 int t2sp_b200_syrk(int32_t OpA, float Alpha, float Beta, halide_buffer_t *A, halide_buffer_t *C, halide_buffer_t *O);
 
+/* GER as the design's generated interface takes it (t2s/tests/performance/ger/ger.cpp:34-62,112;
+ * driver ger-run-fpga.cpp:50-82): A 2-D (TK, TI), X 1-D (TI), Y 1-D (TK), O 6-D (KKK, III, II, KK, K, I)
+ * with TK = KKK*KK*K and TI = III*II*I; O(kkk,iii,ii,kk,k,i) = A(tk, ti) + X(ti) * Y(tk),
+ * ti = iii + III*ii + III*II*i, tk = kkk + KKK*kk + KKK*KK*k (one fp32 multiply and one add, unfused). */
+int t2sp_b200_ger(halide_buffer_t *A, halide_buffer_t *X, halide_buffer_t *Y, halide_buffer_t *O);
+
 int t2sp_b200_conv_nd(halide_buffer_t *I, halide_buffer_t *K, halide_buffer_t *O, int precision);
 int t2sp_b200_capsule_nd(halide_buffer_t *P, halide_buffer_t *W, halide_buffer_t *V, int precision);
 

@@ -23,6 +23,7 @@ $CXX $FLAGS $OFLAGS -DTINY -DREF_CONV    -I $PERF/conv    $PERF/conv/conv-run-fp
 $CXX $FLAGS $OFLAGS -DTINY -DREF_CAPSULE -I $PERF/capsule $PERF/capsule/capsule-run-fpga.cpp $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_capsule_tiny
 $CXX $FLAGS $OFLAGS -DREF_AOT_GEMM $REF/t2s/tests/correctness/aot/gemm-run.cpp $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_aot_gemm
 $CXX $FLAGS $OFLAGS -DTINY -DREF_SYRK -I $PERF/syrk $PERF/syrk/syrk-run-fpga.cpp $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_syrk_tiny
+$CXX $FLAGS $OFLAGS -DTINY -DREF_GER -I $PERF/ger $PERF/ger/ger-run-fpga.cpp $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_ger_tiny
 ONEC="$REF/t2s/tests/correctness/oneapi-integration"
 $CXX -I $HERE/pin_include $FLAGS $OFLAGS -DTINY -DFPGA_EMULATOR -DREF_ONEAPI_CONV    -I $ONEC $ONEC/oneapi-target-5-run.cpp $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_oneapi_conv_tiny
 $CXX -I $HERE/pin_include $FLAGS $OFLAGS -DTINY -DFPGA_EMULATOR -DREF_ONEAPI_CAPSULE -I $ONEC $ONEC/oneapi-target-6-run.cpp $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_oneapi_capsule_tiny
@@ -51,6 +52,8 @@ if [ -f "$ROOT/t2sp_b200/libt2sp_b200.so" ]; then
   $CXX $FLAGS -iquote $ROOT/include -I $SYRK $SYRK/ssyrk-run-fpga.cpp $STUBS/blas-syrk.cpp $STUBS/syrk-interface.cpp $LINK -o $ROOT/tests/_bin/blas_ssyrk_s10
   # the SYRK design's own driver: checks the folded 6-D output element by element (C not symmetric here)
   $CXX $FLAGS -DTINY -I $PERF/syrk $PERF/syrk/syrk-run-fpga.cpp $STUBS/syrk-interface.cpp $LINK -o $ROOT/tests/_bin/syrk_tiny
+  # the GER design's driver (tiled 6-D output checked element by element)
+  $CXX $FLAGS -DTINY -I $PERF/ger $PERF/ger/ger-run-fpga.cpp $STUBS/ger-interface.cpp $LINK -o $ROOT/tests/_bin/ger_tiny
   # the GPU-flow drivers, written against the Level Zero helper layer (util/l0_rt_helpers.h): this
   # repository's header of the same name and API stands in for it; -DITER=1 is the reference's
   # correctness mode (tests.sh:40), sizes are the GPU design's (2048^3 GEMM, 4 x 256 x 64 x 64 conv, ...)

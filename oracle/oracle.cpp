@@ -425,6 +425,26 @@ void oracle_syrk_f32(const float* A, const float* C, float* O, int K, int III, i
     });
 }
 
+// GER of t2s/tests/performance/ger/ger.cpp:34-62: Out(kkk,iii,ii,kk,k,i) = A(tk, ti) + X(ti) * Y(tk), one
+// fp32 multiply and one fp32 add (this file is built with -ffp-contract=off). A: (TK, TI), k innermost
+// with row pitch lda; O dense (KKK,III,II,KK,K,I). Golden loop: ger-run-fpga.cpp:70-82.
+void oracle_ger_f32(const float* A, const float* X, const float* Y, float* O, int KKK, int III, int II, int KK, int K,
+                    int I, int lda) {
+    par_for(I * K, [&](int ik) {
+        const int i = ik / K, k = ik % K;
+        for (int kk = 0; kk < KK; ++kk)
+            for (int ii = 0; ii < II; ++ii)
+                for (int iii = 0; iii < III; ++iii)
+                    for (int kkk = 0; kkk < KKK; ++kkk) {
+                        const size_t ti = iii + size_t(III) * (ii + size_t(II) * i);
+                        const size_t tk = kkk + size_t(KKK) * (kk + size_t(KK) * k);
+                        const float prod = X[ti] * Y[tk];
+                        const size_t off = kkk + size_t(KKK) * (iii + size_t(III) * (ii + size_t(II) * (kk + size_t(KK) * (k + size_t(K) * i))));
+                        O[off] = A[ti * lda + tk] + prod;
+                    }
+    });
+}
+
 // ------------------------------------------------------------------------------ N-D operand layouts (oneAPI flow)
 // conv:    I(iy, ix, ci, n), K(ky, kx, ci, co)      t2s/tests/correctness/oneapi-integration/oneapi-target-5-conv.cpp:58-62
 // capsule: P(mk, mx, ci, iy, ix, n), W(my, mk, ci, co, ky, kx)                        oneapi-target-6-capsule.cpp:57-61

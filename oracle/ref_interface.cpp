@@ -3,7 +3,7 @@
 // unmodified host drivers (t2s/tests/performance/*/*-run-fpga.cpp with -DTINY,
 // t2s/tests/correctness/aot/gemm-run.cpp) can be linked against it and their in-driver golden
 // loops validate the oracle and its tiled output layouts. Built per kernel with
-// -DREF_GEMM / -DREF_AOT_GEMM / -DREF_CONV / -DREF_CAPSULE / -DREF_SYRK / -DREF_ONEAPI_CONV /
+// -DREF_GEMM / -DREF_AOT_GEMM / -DREF_CONV / -DREF_CAPSULE / -DREF_SYRK / -DREF_GER / -DREF_ONEAPI_CONV /
 // -DREF_ONEAPI_CAPSULE and the design's include path.
 // Never part of libt2sp_b200.so.
 #include <stdint.h>
@@ -22,6 +22,7 @@ void oracle_capsule_f32(const float*, const float*, float*, int, int, int, int, 
                         int, int);
 void oracle_capsule_tile_layout(const float*, float*, int, int, int, int, int, int, int, int, int, int, int, int);
 void oracle_syrk_f32(const float*, const float*, float*, int, int, int, int, int, int, float, float, int);
+void oracle_ger_f32(const float*, const float*, const float*, float*, int, int, int, int, int, int, int);
 void oracle_conv_nd_to_2d(const float*, const float*, float*, float*, int, int, int, int, int, int, int);
 void oracle_capsule_nd_to_2d(const float*, const float*, float*, float*, int, int, int, int, int, int, int, int, int, int);
 }
@@ -79,6 +80,17 @@ extern "C" int syrk(int32_t, float alpha, float beta, halide_buffer_t* A, halide
     oracle_syrk_f32(reinterpret_cast<const float*>(A->host), reinterpret_cast<const float*>(C->host),
                     reinterpret_cast<float*>(O->host), A->dim[0].extent, O->dim[0].extent, O->dim[2].extent,
                     O->dim[4].extent - 1, O->dim[5].extent, C->dim[1].stride, alpha, beta, 0);
+    return 0;
+}
+#endif
+
+#ifdef REF_GER
+// the generated ger(A, X, Y, deserializer) of t2s/tests/performance/ger/ger.cpp
+extern "C" int ger(halide_buffer_t* A, halide_buffer_t* X, halide_buffer_t* Y, halide_buffer_t* O) {
+    oracle_ger_f32(reinterpret_cast<const float*>(A->host), reinterpret_cast<const float*>(X->host),
+                   reinterpret_cast<const float*>(Y->host), reinterpret_cast<float*>(O->host), O->dim[0].extent,
+                   O->dim[1].extent, O->dim[2].extent, O->dim[3].extent, O->dim[4].extent, O->dim[5].extent,
+                   A->dim[1].stride);
     return 0;
 }
 #endif

@@ -67,6 +67,8 @@ def lib():
             fn.restype = ctypes.c_int
         L.t2sp_b200_syrk.argtypes = [ctypes.c_int32, ctypes.c_float, ctypes.c_float, P, P, P]
         L.t2sp_b200_syrk.restype = ctypes.c_int
+        L.t2sp_b200_ger.argtypes = [P, P, P, P]
+        L.t2sp_b200_ger.restype = ctypes.c_int
         for name in ("t2sp_b200_conv_nd", "t2sp_b200_capsule_nd"):
             getattr(L, name).argtypes = [P, P, P, ctypes.c_int]
             getattr(L, name).restype = ctypes.c_int
@@ -125,6 +127,12 @@ def capsule_nd(P, W, V, precision=0):
     """capsule on the oneAPI flow's N-D operands P(MK,MX,CI,IY,IX,N), W(MY,MK,CI,CO,KY,KX), 9-D V
     (t2s/tests/correctness/oneapi-integration/oneapi-target-6-capsule.cpp:57-61)."""
     return lib().t2sp_b200_capsule_nd(P.ptr, W.ptr, V.ptr, precision)
+
+
+def ger(A, X, Y, O):
+    """int ger(A, X, Y, deserializer): the tiled 6-D output of the GER design
+    (t2s/tests/performance/ger/ger.cpp:34-62, ger-run-fpga.cpp:66)."""
+    return lib().t2sp_b200_ger(A.ptr, X.ptr, Y.ptr, O.ptr)
 
 
 def syrk(opa, alpha, beta, A, C, O):

@@ -1590,3 +1590,38 @@ extern "C" int t2sp_b200_syrk(int32_t opa, float alpha, float beta, halide_buffe
     if (int e = t2sp::rt_finish_output(O, "deserializer", &vw.v[2])) return e;
     return t2sp::rt_check_status("syrk");
 }
+
+extern "C" int t2sp_b200_ger(halide_buffer_t* A, halide_buffer_t* X, halide_buffer_t* Y, halide_buffer_t* O) {
+    Arg args[4] = {{A, "A", false, 2}, {X, "X", false, 1}, {Y, "Y", false, 1}, {O, "deserializer", true, 6}};
+    if (int e = nd_common_checks(args, 4)) return e;
+    const int TK = A->dim[0].extent, TI = A->dim[1].extent;
+    const long long ok = 1ll * O->dim[0].extent * O->dim[3].extent * O->dim[4].extent;
+    const long long oi = 1ll * O->dim[1].extent * O->dim[2].extent * O->dim[5].extent;
+    if (ok != TK) return constraint("KKK*KK*K", static_cast<int>(ok), "A.extent.0", TK);
+    if (oi != TI) return constraint("III*II*I", static_cast<int>(oi), "A.extent.1", TI);
+    if (int e = check_covers(args[1], 0, TI)) return e;
+    if (int e = check_covers(args[2], 0, TK)) return e;
+    if (TK == 0 || TI == 0) return 0;
+    if (int e = t2sp::rt_ensure_device()) return e;
+    Views vw;
+    if (int e = t2sp::rt_input_view(A, "A", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = t2sp::rt_input_view(X, "X", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = t2sp::rt_input_view(Y, "Y", &vw.v[vw.n])) return e;
+    vw.n++;
+    if (int e = t2sp::rt_output_view(O, "deserializer", &vw.v[vw.n])) return e;
+    vw.n++;
+    t2sp::GerDesc d;
+    for (int i = 0; i < 6; ++i) { d.ext[i] = O->dim[i].extent; d.ostride[i] = O->dim[i].stride; }
+    d.lda = A->dim[1].stride; d.sa0 = A->dim[0].stride; d.sx = X->dim[0].stride; d.sy = Y->dim[0].stride;
+    // element 0 of the vectors is index 0 whatever the buffer's min (check_covers made sure it is covered)
+    const float* pa = static_cast<const float*>(vw.v[0].ptr) + origin_offset(A);
+    const float* px = static_cast<const float*>(vw.v[1].ptr) - 1ll * X->dim[0].min * X->dim[0].stride;
+    const float* py = static_cast<const float*>(vw.v[2].ptr) - 1ll * Y->dim[0].min * Y->dim[0].stride;
+    float* po = static_cast<float*>(vw.v[3].ptr) + origin_offset(O);
+    if (t2sp::ger_launch(pa, px, py, po, d, t2sp::rt_stream()) != cudaSuccess) return halide_error_code_device_run_failed;
+    t2sp::rt_count_launch(1);
+    if (int e = t2sp::rt_finish_output(O, "deserializer", &vw.v[3])) return e;
+    return t2sp::rt_check_status("ger");
+}

@@ -158,6 +158,85 @@ __global__ void syrk_fold_kernel(const float* __restrict__ R, const float* __res
       i * f.ostride[5]] = v;
 }
 
+// One thread per VEC consecutive kkk of the tiled GER output, in output order, so that a dense output
+// is written in whole lines; the matching run of a is read once (VEC = 4: 16-byte loads and stores
+// with streaming hints, as neither a nor the output is touched again).
+template <int VEC>
+__global__ void ger_tiled_kernel(const float* __restrict__ a, const float* __restrict__ x, const float* __restrict__ y,
+                                 float* __restrict__ o, const __grid_constant__ GerDesc d, long long total) {
+    long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (idx >= total) return;
+    const int kv = d.ext[0] / VEC;
+    const int kkk = static_cast<int>(idx % kv) * VEC; idx /= kv;
+    const int iii = idx % d.ext[1]; idx /= d.ext[1];
+    const int ii = idx % d.ext[2]; idx /= d.ext[2];
+    const int kk = idx % d.ext[3]; idx /= d.ext[3];
+    const int k = idx % d.ext[4];
+    const int i = static_cast<int>(idx / d.ext[4]);
+    const long long ti = iii + d.ext[1] * (ii + static_cast<long long>(d.ext[2]) * i);
+    const long long tk = kkk + d.ext[0] * (kk + static_cast<long long>(d.ext[3]) * k);
+    const long long off = kkk * d.ostride[0] + iii * d.ostride[1] + ii * d.ostride[2] + kk * d.ostride[3] +
+                          k * d.ostride[4] + i * d.ostride[5];
+    const float xv = __ldg(x + ti * d.sx);
+    if constexpr (VEC == 4) {
+        const float4 av = __ldcs(reinterpret_cast<const float4*>(a + ti * d.lda + tk));
+        const float4 yv = __ldg(reinterpret_cast<const float4*>(y + tk));
+        // a separately rounded product and sum, as the specification's two operations (no fused multiply-add)
+        __stcs(reinterpret_cast<float4*>(o + off),
+               make_float4(__fadd_rn(av.x, __fmul_rn(xv, yv.x)), __fadd_rn(av.y, __fmul_rn(xv, yv.y)),
+                           __fadd_rn(av.z, __fmul_rn(xv, yv.z)), __fadd_rn(av.w, __fmul_rn(xv, yv.w))));
+    } else {
+        o[off] = __fadd_rn(a[ti * d.lda + tk * d.sa0], __fmul_rn(xv, __ldg(y + tk * d.sy)));
+    }
+}
+
+// The dense, 16-byte-aligned case of the tiled GER: one CTA per (kk group, k, i). Q consecutive kk are
+// taken together so that the threads of a row read Q * KKK consecutive floats of a (whole 128-byte
+// lines for Q * KKK >= 32) and, with neighbouring rows adjacent in the output, write runs of whole
+// lines too. A thread keeps its column position for all its rows, so the only index arithmetic in the
+// loop is a row increment; U rows are loaded before any is stored.
+template <int U>
+__global__ void __launch_bounds__(256)
+ger_rows_kernel(const float* __restrict__ a, const float* __restrict__ x, const float* __restrict__ y,
+                float* __restrict__ o, const __grid_constant__ GerDesc d, int q, int kv) {
+    unsigned b = blockIdx.x;
+    const unsigned nkh = d.ext[3] / q;
+    const int kkh = b % nkh; b /= nkh;
+    const int k = b % static_cast<unsigned>(d.ext[4]);
+    const int i = b / static_cast<unsigned>(d.ext[4]);
+    const int lanes = kv * q;  // threads per row
+    const int c = threadIdx.x % lanes;
+    const int kk = kkh * q + c / kv, kkk = (c % kv) * 4;
+    const long long tk = kkk + d.ext[0] * (kk + static_cast<long long>(d.ext[3]) * k);
+    const int rows = d.ext[1] * d.ext[2];
+    const long long ti0 = static_cast<long long>(rows) * i;
+    const float4 yv = __ldg(reinterpret_cast<const float4*>(y + tk));
+    const float* ap = a + ti0 * d.lda + tk;
+    const float* xp = x + ti0 * d.sx;
+    float* op = o + kkk + kk * d.ostride[3] + k * d.ostride[4] + i * d.ostride[5];
+    const int rstep = 256 / lanes;
+    for (int r0 = threadIdx.x / lanes; r0 < rows; r0 += rstep * U) {
+        float4 av[U];
+        float xv[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int r = r0 + u * rstep;
+            if (r < rows) {
+                av[u] = __ldcs(reinterpret_cast<const float4*>(ap + r * d.lda));
+                xv[u] = __ldg(xp + r * d.sx);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int r = r0 + u * rstep;
+            if (r < rows)
+                __stcs(reinterpret_cast<float4*>(op + r * d.ostride[1]),
+                       make_float4(__fadd_rn(av[u].x, __fmul_rn(xv[u], yv.x)), __fadd_rn(av[u].y, __fmul_rn(xv[u], yv.y)),
+                                   __fadd_rn(av[u].z, __fmul_rn(xv[u], yv.z)), __fadd_rn(av[u].w, __fmul_rn(xv[u], yv.w))));
+        }
+    }
+}
+
 }  // namespace
 
 int core_sm_count() {
@@ -314,6 +393,35 @@ cudaError_t syrk_fold_launch(const float* R, const float* C, float* O, const Syr
     if (total <= 0) return cudaSuccess;
     const int threads = 256;
     syrk_fold_kernel<<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0, stream>>>(R, C, O, f);
+    return cudaGetLastError();
+}
+
+cudaError_t ger_launch(const float* a, const float* x, const float* y, float* o, const GerDesc& d, cudaStream_t stream) {
+    long long total = 1;
+    for (int i = 0; i < 6; ++i) total *= d.ext[i];
+    if (total <= 0) return cudaSuccess;
+    auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    bool vec = d.ext[0] % 4 == 0 && d.ostride[0] == 1 && d.sa0 == 1 && d.sy == 1 && d.lda % 4 == 0 && aligned16(a) &&
+               aligned16(y) && aligned16(o);
+    for (int i = 1; i < 6; ++i) vec = vec && d.ostride[i] % 4 == 0;
+    const int threads = 256;
+    if (vec && d.ostride[2] == d.ext[1] * d.ostride[1]) {
+        // rows (iii, ii) of one (kk, k, i) are evenly spaced in the output: the row-tiled kernel applies
+        const int kv = d.ext[0] / 4;
+        int q = d.ext[3] % 4 == 0 ? 4 : (d.ext[3] % 2 == 0 ? 2 : 1);
+        while (q > 1 && kv * q > 64) q /= 2;
+        const long long blocks = static_cast<long long>(d.ext[3] / q) * d.ext[4] * d.ext[5];
+        if (kv * q <= 256 && 256 % (kv * q) == 0 && blocks < (1ll << 31)) {
+            ger_rows_kernel<4><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(a, x, y, o, d, q, kv);
+            return cudaGetLastError();
+        }
+    }
+    if (vec) {
+        total /= 4;
+        ger_tiled_kernel<4><<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0, stream>>>(a, x, y, o, d, total);
+    } else {
+        ger_tiled_kernel<1><<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0, stream>>>(a, x, y, o, d, total);
+    }
     return cudaGetLastError();
 }
 

@@ -73,4 +73,14 @@ struct SyrkFold {
 };
 cudaError_t syrk_fold_launch(const float* R, const float* C, float* O, const SyrkFold& f, cudaStream_t stream);
 
+// Tiled output of the reference's GER design (t2s/tests/performance/ger/ger.cpp:34-62): element
+// (kkk,iii,ii,kk,k,i) of the 6-D buffer holds a(tk, ti) + x(ti) * y(tk) with ti = iii + III*ii + III*II*i,
+// tk = kkk + KKK*kk + KKK*KK*k. a is addressed as a[ti * lda + tk * sa0]; x, y with their own strides.
+struct GerDesc {
+    int ext[6];            // KKK, III, II, KK, K, I
+    long long ostride[6];  // element strides of the six output dimensions
+    long long lda, sa0, sx, sy;
+};
+cudaError_t ger_launch(const float* a, const float* x, const float* y, float* o, const GerDesc& d, cudaStream_t stream);
+
 }  // namespace t2sp

@@ -132,6 +132,15 @@ def syrk_f32(A, C, III, II, I, alpha, beta, acc64=False):
     return Ofold
 
 
+def ger_f32(A, X, Y, KKK, III, II, KK, K, I):
+    """A: (TI, TK), X: (TI,), Y: (TK,) -> tiled O: (I, K, KK, II, III, KKK)."""
+    out = np.empty((I, K, KK, II, III, KKK), np.float32)
+    L = load()
+    L.oracle_ger_f32.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_int] * 7
+    L.oracle_ger_f32(_p(A), _p(X), _p(Y), _p(out), KKK, III, II, KK, K, I, A.shape[1])
+    return out
+
+
 def conv_nd_f32(I4, K4, tiles, acc64=False):
     """I4: (N,CI,IX,IY), K4: (CO,CI,KX,KY) -> the 10-D tiled output of the oneAPI flow."""
     N, CI, IX, IY = I4.shape

@@ -69,7 +69,7 @@ def test_stubs_define_the_interface_symbols(lib, tmp_path):
     so = tmp_path / "libstubs.so"
     objs = []
     for f in ("gemm-interface.cpp", "conv-interface.cpp", "capsule-interface.cpp", "host.cpp", "ttm-mttkrp-interface.cpp",
-              "syrk-interface.cpp", "blas-syrk.cpp", "blas-gemm.cpp", "l0_shim.cpp"):
+              "syrk-interface.cpp", "ger-interface.cpp", "blas-syrk.cpp", "blas-gemm.cpp", "l0_shim.cpp"):
         o = tmp_path / (f + ".o")
         subprocess.run(["g++", "-fPIC", "-c", "-I", INC, "-I", os.path.join(ROOT, "tests", "designs"),
                         os.path.join(stubs, f), "-o", str(o)], check=True, capture_output=True)
@@ -77,7 +77,7 @@ def test_stubs_define_the_interface_symbols(lib, tmp_path):
     subprocess.run(["g++", "-shared", "-o", str(so)] + objs + ["-L", os.path.dirname(LIB_PATH), "-lt2sp_b200",
                     "-Wl,-rpath," + os.path.dirname(LIB_PATH)], check=True, capture_output=True)
     S = ctypes.CDLL(str(so))
-    for n in ("gemm", "conv", "capsule", "GEMM", "ttm", "mttkrp", "syrk", "t2sp_l0_image_create", "t2sp_l0_run"):
+    for n in ("gemm", "conv", "capsule", "GEMM", "ttm", "mttkrp", "syrk", "ger", "t2sp_l0_image_create", "t2sp_l0_run"):
         assert hasattr(S, n)
     assert S.syrk(0, ctypes.c_float(1), ctypes.c_float(0), None, None, None) == -12
     # null buffers are rejected by the generic entry behind the stub, with the reference's code

@@ -122,3 +122,34 @@ def test_syrk_folded_output(lib, III, II, I, K):
     assert np.isnan(got[I // 2:]).all(), "rows i >= I/2 of the folded buffer are not part of the design's output"
     assert normwise(got[:I // 2], want[:I // 2]) <= TOL_FP32
     assert normwise(got[:I // 2], O.syrk_f32(A, Cs, III, II, I, alpha, beta, acc64=True)[:I // 2]) <= TOL_FP32
+
+
+@pytest.mark.parametrize("KKK,III,II,KK,K,I", [(16, 10, 4, 4, 3, 2), (2, 2, 2, 2, 2, 2), (6, 3, 2, 5, 2, 3), (8, 7, 5, 6, 2, 2),
+                                               (4, 3, 3, 3, 2, 2), (12, 5, 2, 2, 2, 2)])
+def test_ger_tiled_output_bit_exact(lib, KKK, III, II, KK, K, I):
+    """O(kkk,iii,ii,kk,k,i) = A(tk,ti) + X(ti) * Y(tk) (t2s/tests/performance/ger/ger.cpp:34-62): one
+    rounded product and one rounded sum per element, so the result equals the oracle's bit for bit
+    (KKK = 16, 8, 4: the row-tiled 16-byte kernel with 4, 2 and 1 kk per row group; KKK = 12: the generic
+    16-byte kernel, as 3 x 2 threads per row do not divide a CTA; KKK = 2 and 6: the scalar kernel)."""
+    TI, TK = III * II * I, KKK * KK * K
+    A, X, Y = O.uniform(15, 1, (TI, TK)), O.uniform(15, 2, (TI,)), O.uniform(15, 3, (TK,))
+    out = np.full((I, K, KK, II, III, KKK), np.nan, np.float32)
+    ob = Buffer.from_numpy(out)
+    assert t2sp_b200.ger(Buffer.from_numpy(A), Buffer.from_numpy(X), Buffer.from_numpy(Y), ob) == 0
+    want = O.ger_f32(A, X, Y, KKK, III, II, KK, K, I)
+    assert np.array_equal(ob.keepalive.view(np.uint32), want.view(np.uint32))
+    # and the oracle's layout against plain numpy
+    plain = A + (X[:, None] * Y[None, :]).astype(np.float32)
+    assert np.array_equal(want, plain.reshape(I, II, III, K, KK, KKK).transpose(0, 3, 4, 1, 2, 5))
+
+
+def test_ger_published_size_a10(lib):
+    """The A10 design constants with its 32 x 32 outer loops (const-parameters.h:45-50, ger-run-fpga.cpp:29-30):
+    10240 x 16384 elements, checked in full against numpy (same two roundings)."""
+    KKK, III, II, KK, K, I = 16, 10, 32, 32, 32, 32
+    TI, TK = III * II * I, KKK * KK * K
+    A, X, Y = O.uniform(16, 1, (TI, TK)), O.uniform(16, 2, (TI,)), O.uniform(16, 3, (TK,))
+    ob = Buffer.from_numpy(np.empty((I, K, KK, II, III, KKK), np.float32))
+    assert t2sp_b200.ger(Buffer.from_numpy(A), Buffer.from_numpy(X), Buffer.from_numpy(Y), ob) == 0
+    plain = A + (X[:, None] * Y[None, :]).astype(np.float32)
+    assert np.array_equal(ob.keepalive, plain.reshape(I, II, III, K, KK, KKK).transpose(0, 3, 4, 1, 2, 5))

@@ -177,3 +177,11 @@ def test_nd_fronts_and_syrk_validation(lib):
     assert t2sp_b200.syrk(0, 1.0, 0.0, A, C, z(4, 5, 2, 2, 2, 3)) == -8      # the two innermost extents must agree
     assert t2sp_b200.syrk(0, 1.0, 0.0, A, C, z(2, 4, 2, 2, 2, 2)) == -8      # I = 3 is odd
     assert t2sp_b200.syrk(0, 1.0, 0.0, z(12, 8), C, z(4, 5, 2, 2, 2, 2)) == -8   # N != III*II*I
+    # ger: A (TI,TK), X (TI,), Y (TK,), O (I, K, KK, II, III, KKK)
+    assert lib.t2sp_b200_ger(None, None, None, None) == -12
+    A, X, Y = z(8, 16), z(8), z(16)
+    assert t2sp_b200.ger(A, X, Y, z(2, 2, 2, 2, 2, 4)) == -36
+    assert t2sp_b200.ger(A, X, Y, z(2, 2, 2, 2, 2, 2)) == -8     # KKK*KK*K = 8, A has 16 columns
+    assert t2sp_b200.ger(A, X, Y, z(2, 2, 2, 2, 3, 4)) == -8     # III*II*I = 12, A has 8 rows
+    assert t2sp_b200.ger(A, z(4), Y, z(2, 2, 2, 2, 2, 4)) == -4  # X shorter than A's row count
+    assert t2sp_b200.ger(A, X, z(2, 8), z(2, 2, 2, 2, 2, 4)) == -43  # Y must be 1-D

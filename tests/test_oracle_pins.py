@@ -16,7 +16,7 @@ REF = "/root/reference"
 KAT = np.load(os.path.join(ROOT, "tests", "golden", "kat.npz"))
 
 
-@pytest.mark.parametrize("name", ["pin_gemm_tiny", "pin_conv_tiny", "pin_capsule_tiny", "pin_aot_gemm", "pin_syrk_tiny",
+@pytest.mark.parametrize("name", ["pin_gemm_tiny", "pin_conv_tiny", "pin_capsule_tiny", "pin_aot_gemm", "pin_syrk_tiny", "pin_ger_tiny",
                                   "pin_oneapi_conv_tiny", "pin_oneapi_capsule_tiny"])
 def test_reference_driver_accepts_oracle(name):
     exe = os.path.join(ROOT, "oracle", "_ref", name)

@@ -22,7 +22,7 @@ KAT = np.load(os.path.join(ROOT, "tests", "golden", "kat.npz"))
 
 
 @pytest.mark.parametrize("name", ["gemm_tiny", "conv_tiny", "capsule_tiny", "aot_gemm", "oneapi_gemm_tiny", "oneapi_conv_tiny",
-                                  "oneapi_capsule_tiny", "blas_sgemm_a10", "blas_ssyrk_s10", "syrk_tiny"])
+                                  "oneapi_capsule_tiny", "blas_sgemm_a10", "blas_ssyrk_s10", "syrk_tiny", "ger_tiny"])
 def test_unmodified_reference_driver(lib, name, tmp_path):
     exe = os.path.join(ROOT, "tests", "_bin", name)
     if not os.path.exists(exe):
