@@ -455,13 +455,15 @@ KNOWN_TRAFFIC = {
     "gemm_bf16_8192": 1080071040,
     # small-case captures (one launch each): profiles/gemm_bf16_i8_4096_pair_kernels_full.md and
     # profiles/fp32_3xtf32_kernels_conv_ttm_mttkrp_capsule_sgemm_full.md
-    "gemm_bf16_4096": 95056896 + 32553472,
+    "gemm_bf16_4096": 95151104 + 32033792,
     "gemm_i8_4096": 35462400 + 18725376,
     "conv_cfg2": 19220480 + 142336,
     "ttm_cfg3": 268876800 + 218153984,
     "mttkrp_cfg3": 537606400 + 3475456,
     "capsule_cfg4": 21994496 + 7168,
     "sgemm_1024": 8471808,
+    # profiles/ger_a10_rows_kernel_full.md
+    "ger_a10": 671217664 + 620295680,
 }
 
 if __name__ == "__main__":
