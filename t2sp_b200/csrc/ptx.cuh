@@ -158,6 +158,14 @@ __device__ __forceinline__ void bulk_wait_read_1() { asm volatile("cp.async.bulk
 // Wait until all committed bulk groups have completed (their global writes are done).
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
+// ---------------------------------------------------------------- programmatic dependent launch
+// In the earlier kernel: grids launched behind this one with programmatic stream serialization may be
+// scheduled from now on (they still see this grid's memory only after their own grid_dep_wait).
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// In the later kernel: returns once the grids it depends on have completed and their writes are visible
+// (at once when it was launched without the attribute).
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---------------------------------------------------------------- tcgen05: TMEM management
 template <int CTA_GROUP>
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_slot, uint32_t ncols) {

@@ -89,6 +89,7 @@ __global__ void splitk_finalize_kernel(const float* __restrict__ part, long long
     const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
     if (idx >= static_cast<long long>(f.M) * quads) return;
     const int m = static_cast<int>(idx / quads), n = static_cast<int>(idx % quads) * 4;
+    ptx::grid_dep_wait();  // launched while the kernel that writes the partial tiles may still be running
     const float* src = part + static_cast<long long>(m) * ld_part + n;
     float4 acc = *reinterpret_cast<const float4*>(src);
     for (int s = 1; s < splits; ++s) {
@@ -372,9 +373,19 @@ cudaError_t splitk_finalize_launch(const float* partials, long long ld_part, int
     const long long work = static_cast<long long>(final_p.M) * ((final_p.N + 3) / 4);
     if (work <= 0) return cudaSuccess;
     const int threads = 256;
-    splitk_finalize_kernel<<<static_cast<unsigned>((work + threads - 1) / threads), threads, 0, stream>>>(
-        partials, ld_part, static_cast<long long>(slab_rows) * ld_part, splits, final_p);
-    return cudaGetLastError();
+    // programmatic stream serialization: the launch is set up and its CTAs scheduled as the contraction
+    // kernel's CTAs retire; the kernel itself waits for that grid before it reads a partial tile
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>((work + threads - 1) / threads));
+    cfg.blockDim = dim3(threads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, splitk_finalize_kernel, partials, ld_part, static_cast<long long>(slab_rows) * ld_part,
+                              splits, final_p);
 }
 
 cudaError_t permute_copy_launch(const void* src, void* dst, const PermuteDesc& d, cudaStream_t stream) {

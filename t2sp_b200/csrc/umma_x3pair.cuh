@@ -109,6 +109,7 @@ umma_x3pair_kernel(const __grid_constant__ CoreParams p) {
         ptx::tmem_relinquish<2>();
     }
     ptx::tc_fence_before_sync();
+    ptx::grid_dep_launch();  // the split-K summing kernel may be scheduled while this grid runs
     __syncthreads();
     ptx::cluster_sync();
     ptx::tc_fence_after_sync();
