@@ -23,6 +23,7 @@ struct Pair2Cfg {
     static constexpr int kBoxElemsMn = 128 / AT::kElem;
     static constexpr int kThreads = 6 * 32;
     static constexpr int kTmemCols = 512;
+    static constexpr int kLead = STAGES - 1;  // k-blocks sub-tile 0 runs ahead of sub-tile 1 at a tile's ends
     static constexpr int kNumBars = 2 * STAGES + 4;
     // two 32 x 32 fp32 staging tiles per epilogue warp for the TMA-store epilogue; the scatter epilogue,
     // which does not stage, keeps its per-warp column tables (4 x 256 offsets) in the same bytes
@@ -44,7 +45,7 @@ umma_pair2_kernel(const __grid_constant__ CoreParams p) {
     uint8_t* tail = cstage + Cfg::kCStageBytes2;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);  // leader's: both CTAs' TMA data landed
     uint64_t* empty_bar = full_bar + STAGES;                 // per CTA: MMAs that read the stage retired
-    uint64_t* tfull_bar = empty_bar + STAGES;                // per CTA: the tile's accumulators are complete ([0] used)
+    uint64_t* tfull_bar = empty_bar + STAGES;                // per CTA: the tile's accumulator of sub-tile 0 / 1 is complete
     uint64_t* tempty_bar = tfull_bar + 2;                    // leader's: accumulator of sub-tile 0 / 1 drained by both CTAs
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
     uint32_t* abort_slot = tmem_slot + 1;
@@ -124,39 +125,75 @@ umma_pair2_kernel(const __grid_constant__ CoreParams p) {
             constexpr uint32_t kStepMn = (AT::kUmmaK * 128) >> 4;
             constexpr uint32_t kStepB = Cfg::kBMnMajor ? kStepMn : kStepK;
             constexpr uint32_t kLboB = Cfg::kBMnMajor ? Cfg::kBoxBytesMn : 16;
-            for (int t = pair; t < num_tiles && ok; t += num_pairs, ++lt) {
-                for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
-                    T2SP_TRACE(p, 8, it);
-                    if (!bounded_wait(&full_bar[s], ph, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
-                    ptx::tc_fence_after_sync();
-                    T2SP_TRACE(p, 3, it);
-                    const uint32_t sa = ptx::smem_u32(smem + s * Cfg::kStageBytes);
-                    const uint64_t db = ptx::make_smem_desc(sa + Cfg::kABytes, kLboB, 1024);
+            // Sub-tile 0 runs `lead` k-blocks ahead of sub-tile 1 at both ends of a tile: at the start its MMAs
+            // begin as soon as accumulator 0 has been drained, while accumulator 1 is still leaving; at the end
+            // it finishes early, so its drain runs under sub-tile 1's last MMAs. In between the two advance in
+            // step, one stage per k-block. All `lead` stages are held while a sub-tile runs alone.
+            int lead = Cfg::kLead < p.num_kb / 2 ? Cfg::kLead : p.num_kb / 2;
+#ifdef T2SP_DEBUG_KNOBS
+            if (p.debug > 0) lead = (p.debug - 1) < p.num_kb / 2 ? (p.debug - 1) : p.num_kb / 2;
+#endif
+            auto wait_full = [&](int i) -> bool {
+                T2SP_TRACE(p, 8, i);
+                if (!bounded_wait(&full_bar[i % STAGES], (i / STAGES) & 1, ab, ST_TIMEOUT_MMA)) return false;
+                ptx::tc_fence_after_sync();
+                T2SP_TRACE(p, 3, i);
+                return true;
+            };
+            auto issue = [&](int u, int kb, int i) {
+                const uint32_t sa = ptx::smem_u32(smem + (i % STAGES) * Cfg::kStageBytes);
+                const uint64_t db = ptx::make_smem_desc(sa + Cfg::kABytes, kLboB, 1024);
+                const uint64_t da = ptx::make_smem_desc(sa + u * Cfg::kSubBytes, 16, 1024);
 #pragma unroll
-                    for (int u = 0; u < 2; ++u) {
-                        if (kb == 0) {
-                            // the previous tile's accumulator u must have been drained by both CTAs
-                            if (!bounded_wait(&tempty_bar[u], (lt & 1) ^ 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
-                            ptx::tc_fence_after_sync();
-                            T2SP_TRACE(p, 10, lt * 2 + u);
-                        }
-                        const uint64_t da = ptx::make_smem_desc(sa + u * Cfg::kSubBytes, 16, 1024);
-#pragma unroll
-                        for (int j = 0; j < AT::kBlockK / AT::kUmmaK; ++j)
-                            ptx::umma<AT::kKind, 2>(tmem_base + u * Cfg::kUmmaN, da + j * kStepK, db + j * kStepB, p.idesc,
-                                                    (kb | j) ? 1u : 0u);
-                    }
+                for (int j = 0; j < AT::kBlockK / AT::kUmmaK; ++j)
+                    ptx::umma<AT::kKind, 2>(tmem_base + u * Cfg::kUmmaN, da + j * kStepK, db + j * kStepB, p.idesc,
+                                            (kb | j) ? 1u : 0u);
+            };
+            auto release = [&](int i) {  // both sub-tiles' MMAs on the stage have been issued
+                ptx::umma_commit_pair(ptx::map_to_cta(&empty_bar[i % STAGES], 0));
+                ptx::umma_commit_pair(ptx::map_to_cta(&empty_bar[i % STAGES], 1));
+                T2SP_TRACE(p, 4, i);
+            };
+            auto wait_drained = [&](int u) -> bool {  // the previous tile's accumulator u, by both CTAs
+                if (!bounded_wait(&tempty_bar[u], (lt & 1) ^ 1, ab, ST_TIMEOUT_MMA)) return false;
+                ptx::tc_fence_after_sync();
+                T2SP_TRACE(p, 10, lt * 2 + u);
+                return true;
+            };
+            auto accumulator_done = [&](int u) {
+                ptx::umma_commit_pair(ptx::map_to_cta(&tfull_bar[u], 0));
+                ptx::umma_commit_pair(ptx::map_to_cta(&tfull_bar[u], 1));
+            };
+            const int n = p.num_kb;
+            for (int t = pair; t < num_tiles && ok; t += num_pairs, ++lt, it += n) {
+                ok = wait_drained(0);
+                for (int kb = 0; kb < lead && ok; ++kb) {
+                    ok = wait_full(it + kb);
+                    if (ok) issue(0, kb, it + kb);
+                }
+                ok = ok && wait_drained(1);
+                for (int kb = 0; kb < lead && ok; ++kb) {
+                    issue(1, kb, it + kb);
+                    release(it + kb);
+                }
+                for (int kb = lead; kb < n - lead && ok; ++kb) {
+                    ok = wait_full(it + kb);
                     if (!ok) break;
-                    ptx::umma_commit_pair(ptx::map_to_cta(&empty_bar[s], 0));
-                    ptx::umma_commit_pair(ptx::map_to_cta(&empty_bar[s], 1));
-                    T2SP_TRACE(p, 4, it);
+                    issue(0, kb, it + kb);
+                    issue(1, kb, it + kb);
+                    release(it + kb);
                 }
-                if (ok) {
-                    ptx::umma_commit_pair(ptx::map_to_cta(&tfull_bar[0], 0));
-                    ptx::umma_commit_pair(ptx::map_to_cta(&tfull_bar[0], 1));
+                for (int kb = n - lead; kb < n && ok; ++kb) {
+                    ok = wait_full(it + kb);
+                    if (ok) issue(0, kb, it + kb);
                 }
+                if (!ok) break;
+                accumulator_done(0);
+                for (int kb = n - lead; kb < n; ++kb) {
+                    issue(1, kb, it + kb);
+                    release(it + kb);
+                }
+                accumulator_done(1);
             }
         }
     } else {
@@ -222,6 +259,10 @@ umma_pair2_kernel(const __grid_constant__ CoreParams p) {
                     ptx::tmem_ld_32x32(lane_base + (c + 1) * 32, rb);
                     put(ra, c);
                     loaded(c + 1);
+                    if (c + 2 == 8) {  // sub-tile 1's accumulator completes later than sub-tile 0's
+                        if (!bounded_wait_warp(&tfull_bar[1], lt & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
+                        ptx::tc_fence_after_sync();
+                    }
                     if (c + 2 < 16) ptx::tmem_ld_32x32(lane_base + (c + 2) * 32, ra);
                     put(rb, c + 1);
                     if (c + 2 < 16) loaded(c + 2);
@@ -230,6 +271,10 @@ umma_pair2_kernel(const __grid_constant__ CoreParams p) {
             } else {
 #pragma unroll 1
                 for (int u = 0; u < 2; ++u) {
+                    if (u == 1) {
+                        if (!bounded_wait_warp(&tfull_bar[1], lt & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
+                        ptx::tc_fence_after_sync();
+                    }
                     const int m = mb * 512 + u * 256 + static_cast<int>(rank) * kBlockM + q * 32 + lane;
                     const long long offm = (p.epi == EPI_SCATTER) ? digits_offset(p.dm, m) : 0;
 #pragma unroll 1
