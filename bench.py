@@ -452,10 +452,10 @@ def main():
 KNOWN_TRAFFIC = {
     # profiles/gemm_bf16_8192_pair_dram_traffic.md: mean of two launches of the 512 x 256 pair kernel
     # (837695488 + 237744128 and 849618944 + 235083520 bytes read + written)
-    "gemm_bf16_8192": 1080071040,
+    "gemm_bf16_8192": 1059237248,
     # small-case captures (one launch each): profiles/gemm_bf16_i8_4096_pair_kernels_full.md and
     # profiles/fp32_3xtf32_kernels_conv_ttm_mttkrp_capsule_sgemm_full.md
-    "gemm_bf16_4096": 95151104 + 32033792,
+    "gemm_bf16_4096": 94957312 + 32456192,
     "gemm_i8_4096": 35462400 + 18725376,
     "conv_cfg2": 19220480 + 142336,
     "ttm_cfg3": 268876800 + 218153984,
