@@ -321,7 +321,11 @@ int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool syn
     rt_count_launch(1);
     if (sync_after) cudaEventRecord(rt_event(1), s);
 #ifdef T2SP_DEBUG_KNOBS
-    if (trace_path) {
+    // T2SP_B200_TRACE_AT=<n>: only the n-th traced launch is waited for and written out, so that the
+    // launches before it run back to back as in a timed loop
+    static int trace_calls = 0;
+    const char* trace_at = getenv("T2SP_B200_TRACE_AT");
+    if (trace_path && (!trace_at || ++trace_calls == atoi(trace_at))) {
         std::vector<long long> host(48 * 1024);
         cudaStreamSynchronize(s);
         cudaMemcpy(host.data(), trace_dev, host.size() * sizeof(long long), cudaMemcpyDeviceToHost);

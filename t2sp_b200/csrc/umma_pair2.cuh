@@ -85,6 +85,7 @@ umma_pair2_kernel(const __grid_constant__ CoreParams p) {
         if (lane == 0) {
             ptx::prefetch_tensormap(&p.mapA[0]);
             ptx::prefetch_tensormap(&p.mapB);
+            T2SP_TRACE_CLOCK(p, 0);
             int it = 0;
             bool ok = true;
             for (int t = pair; t < num_tiles && ok; t += num_pairs) {
@@ -293,6 +294,7 @@ umma_pair2_kernel(const __grid_constant__ CoreParams p) {
     }
 
     // ---------------------------------------------------------------- teardown
+    if (threadIdx.x == 0) T2SP_TRACE_CLOCK(p, 1);
     if (warp >= 2 && lane == 0) ptx::bulk_wait_all();
     ptx::tc_fence_before_sync();
     __syncthreads();

@@ -96,8 +96,15 @@ struct CoreParams {
 #ifdef T2SP_DEBUG_KNOBS
 #define T2SP_TRACE(p, role, idx) \
     do { if ((p).trace && blockIdx.x < 2 && (idx) < 1024) (p).trace[((role) + 24 * blockIdx.x) * 1024 + (idx)] = clock64(); } while (0)
+// Pair of (SM cycle counter, nanosecond timer) stamps: their differences between two points give the
+// SM clock the kernel actually ran at.
+#define T2SP_TRACE_CLOCK(p, idx) \
+    do { if ((p).trace && blockIdx.x == 0) { (p).trace[23 * 1024 + 2 * (idx)] = clock64(); \
+         unsigned long long t2sp_ns_; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t2sp_ns_)); \
+         (p).trace[23 * 1024 + 2 * (idx) + 1] = static_cast<long long>(t2sp_ns_); } } while (0)
 #else
 #define T2SP_TRACE(p, role, idx) do { } while (0)
+#define T2SP_TRACE_CLOCK(p, idx) do { } while (0)
 #endif
 
 }  // namespace t2sp
