@@ -1,15 +1,18 @@
 #!/usr/bin/env python
-"""Benchmark of the hot path: one dense contraction per step on each GPU.
+"""Benchmark of the hot path: one dense contraction per step.
 
-Default workload (N=1): the 8192^3 bf16 GEMM with fp32 accumulation, the configuration
-the headline TFLOP/s figure is quoted on. With N>1 ranks (launched by torchrun, one rank per
-GPU) every rank multiplies the shared A by its own 8192-column slab of B: the N-column
-sharding of the GEMM with the per-GPU work held fixed (weak scaling); no collective is on
-the data path, NCCL is used only for the barrier and the max-over-ranks time.
+Default workload: the 8192^3 bf16 GEMM with fp32 accumulation, the configuration the headline
+TFLOP/s figure is quoted on. With N>1 ranks (launched by torchrun, one rank per GPU) the SAME
+problem is split: rank g computes columns [g N/G, (g+1) N/G) of C from all of A and its columns of
+B through the library's sharded entry (strong scaling; operands are placed before the timed
+region); no collective is on the data path, NCCL carries the barrier, the max-over-ranks time and,
+timed separately as `gather_ms`, the all-gather that puts all of C on every GPU.
 
 `value`   : operands already resident in HBM, kernels timed with CUDA events on the launching stream.
-`e2e`     : the same contraction through the C-ABI entry with pinned HOST buffers, so every step
-            pays the host->device copy of A and B and the device->host copy of C.
+`e2e`     : the same contraction through the C-ABI entry with HOST buffers (pinned; `pageable` beside it),
+            so every step pays the host->device copy of A and B and the device->host copy of C.
+`sustained`, `workloads`: the headline launch repeated for more than two seconds, and the other
+            configurations device-timed for `steps` launches each (single GPU).
 `--impl reference` times the CPU restatement of the reference specification (oracle/) on the
 host cores instead; it is the only arm that touches oracle/ besides the cpu_baseline sample.
 """
@@ -266,7 +269,7 @@ def run_reference(args, kind, w, name):
     line = {
         "impl": "reference", "metric": "throughput", "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": f / (tf * 1e12) * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w.get("dtype", "f32"),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": w.get("dtype", "f32"),
         "data": "synthetic", "config": {"workload": name, **{k: v for k, v in w.items()}},
         "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": "per step: " + desc},
         "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -278,15 +281,111 @@ def run_reference(args, kind, w, name):
 
 
 # ----------------------------------------------------------------------------------- GPU arm
+SIDE_WORKLOADS = ["sgemm_1024", "conv_cfg2", "ttm_cfg3", "mttkrp_cfg3", "capsule_cfg4", "gemm_bf16_4096",
+                  "gemm_bf16_16384", "gemm_i8_8192"]
+RATE = {"bf16": 1.0, "f16": 1.0, "i8": 2.0, "f32": 1.0 / 6.0}  # tensor ceiling relative to the bf16 peak
+
+
+class Resident:
+    """One workload with its operands resident in HBM, wrapped as halide buffers; call() enqueues one step
+    (this rank's shard of it when world > 1) on the library's stream."""
+
+    def __init__(self, name, rank, world, device_generated=False):
+        import numpy as np
+        import torch
+        import t2sp_b200
+        from t2sp_b200 import Buffer
+        self.name, self.rank, self.world = name, rank, world
+        self.kind, self.w = WORKLOADS[name]
+        kind, w = self.kind, self.w
+        self.desc = make_desc(kind, w)
+        self.flops, self.abytes = flops_bytes(kind, w)
+        if device_generated and kind == "gemm" and w["dtype"] in ("bf16", "i8"):
+            # large operands are drawn on the device (same distributions, torch's seeded generator)
+            g = torch.Generator(device="cuda")
+            g.manual_seed(1234)
+            M, N, K = w["M"], w["N"], w["K"]
+            if w["dtype"] == "bf16":
+                mk = lambda r, c: (torch.rand((r, c), generator=g, device="cuda") * 2 - 1).to(torch.bfloat16)
+                out_t = torch.float32
+            else:
+                mk = lambda r, c: torch.randint(-127, 128, (r, c), generator=g, device="cuda", dtype=torch.int8)
+                out_t = torch.int32
+            self.dev_in = [mk(M, K), mk(K, N)]
+            self.shapes, self.dts, self.out_shape, self.out_dt = [(M, K), (K, N)], [w["dtype"]] * 2, (M, N), out_t
+            self.host_in = None
+        else:
+            arrs, out_shape, out_dtype, dts = make_inputs(kind, w, seed=0, rank=0)
+            self.host_in = arrs
+            self.dev_in = [torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).cuda() for a in arrs]
+            self.shapes, self.dts, self.out_shape = [a.shape for a in arrs], dts, out_shape
+            self.out_dt = torch.int32 if out_dtype == np.int32 else torch.float32
+        self.dev_out = torch.empty(self.out_shape, dtype=self.out_dt, device="cuda")
+        self.bufs = []
+        for shp, t, dt in zip(self.shapes, self.dev_in, self.dts):
+            b = Buffer(tuple(reversed(shp)), dt)
+            t2sp_b200.wrap_device(b, t.data_ptr())
+            self.bufs.append(b)
+        self.ob = Buffer(tuple(reversed(self.out_shape)), "i32" if self.out_dt == torch.int32 else "f32")
+        t2sp_b200.wrap_device(self.ob, self.dev_out.data_ptr())
+
+    def call(self):
+        if self.world == 1:
+            return call_op(self.kind, self.bufs, self.ob, self.desc)
+        from t2sp_b200 import shard
+        k, b, r, n = self.kind, self.bufs, self.rank, self.world
+        if k == "gemm":
+            return shard.gemm_shard(b[0], b[1], self.ob, r, n)
+        if k == "conv":
+            return shard.conv_shard(b[0], b[1], self.ob, self.desc, r, n)
+        if k == "capsule":
+            return shard.capsule_shard(b[0], b[1], self.ob, self.desc, r, n)
+        if k == "ttm":
+            return shard.ttm_shard(b[0], b[1], self.ob, r, n)
+        if k == "mttkrp":
+            return shard.mttkrp_shard(b[0], b[1], b[2], self.ob, r, n)
+        raise SystemExit(f"workload kind {k} does not shard")
+
+    SHARDING = {"gemm": "one problem, N-column slabs of B and C per GPU, A replicated, placement outside the timed region",
+                "conv": "one problem, batch items per GPU, weights replicated",
+                "capsule": "one problem, batch items per GPU, weights replicated",
+                "ttm": "one problem, j slabs per GPU, b replicated",
+                "mttkrp": "one problem, k ranges (the contraction) per GPU; partial results are not summed inside the timed region",
+                "ger": "not sharded"}
+
+
+def roofline_of(name, kernel_ms, long_run=False):
+    """Which roofline bounds the workload (the longer of bytes / HBM bandwidth and FLOPs / tensor ceiling) and
+    how close kernel_ms comes to it."""
+    kind, w = WORKLOADS[name]
+    flops, abytes = flops_bytes(kind, w)
+    pk = peaks()
+    scale = RATE[w.get("dtype", "f32")]
+    t_hbm = abytes / (pk["hbm"] * 1e9)
+    t_tensor = flops / (pk["burst"] * scale * 1e12)
+    if t_hbm > t_tensor:
+        achieved, peak, unit, bound = abytes / (kernel_ms * 1e-3) / 1e9, pk["hbm"], "GB/s", "hbm"
+        note = f"{pk['src']} HBM copy bandwidth"
+    else:
+        bf16_peak = pk["sustained"] if long_run else pk["burst"]
+        achieved, peak, unit, bound = flops / (kernel_ms * 1e-3) / 1e12, bf16_peak * scale, "TFLOP/s", "tensor"
+        note = (f"{pk['src']} cuBLAS bf16 {'sustained' if long_run else 'burst'} {bf16_peak} TFLOP/s"
+                + {1.0: "", 2.0: " x2 (int8 rate)", 1.0 / 6.0: " /2 (tf32 rate) /3 (three MMAs per product)"}[scale])
+    return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
+            "traffic": KNOWN_TRAFFIC.get(name), "peak_source": note, "kernel_ms": kernel_ms,
+            "algorithmic_flops": flops, "algorithmic_bytes": abytes}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm_bf16_8192", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the sustained run, the other workloads and the gather timing")
     args = ap.parse_args()
     kind, w = WORKLOADS[args.workload]
     if args.impl == "reference":
@@ -313,93 +412,173 @@ def main():
         dist.barrier()
     L = t2sp_b200.lib()
     L.t2sp_b200_set_device(local_rank)
-    stream = torch.cuda.current_stream()
+    stream = torch.cuda.Stream()  # the library launches on this stream; the timing events are recorded on it
+    torch.cuda.set_stream(stream)
     L.t2sp_b200_set_stream(ctypes.c_void_p(stream.cuda_stream))
-
-    arrs, out_shape, out_dtype, dts = make_inputs(kind, w, seed=0, rank=rank)
-    desc = make_desc(kind, w)
-    flops, abytes = flops_bytes(kind, w)
-
-    # ---- resident arm: device tensors wrapped as halide buffers
-    dev_in = [torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).cuda() for a in arrs]
-    dev_out = torch.empty(out_shape, dtype=torch.int32 if out_dtype == np.int32 else torch.float32, device="cuda")
-    bufs = []
-    for a, t, dt in zip(arrs, dev_in, dts):
-        b = Buffer(tuple(reversed(a.shape)), dt)
-        t2sp_b200.wrap_device(b, t.data_ptr())
-        bufs.append(b)
-    ob = Buffer(tuple(reversed(out_shape)), "i32" if out_dtype == np.int32 else "f32")
-    t2sp_b200.wrap_device(ob, dev_out.data_ptr())
-    L.t2sp_b200_set_async(1)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")  # twice the 126 MB L2
 
     def sync_all():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        rc = call_op(kind, bufs, ob, desc)
-        if rc != 0:
-            raise SystemExit(f"hot path failed with halide error {rc}")
-    rc = L.t2sp_b200_sync()
-    if rc != 0:
-        raise SystemExit(f"hot path failed with halide error {rc}")
-    sync_all()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    launches0 = L.t2sp_b200_kernel_launches()
-    evs = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    evs[0].record(stream)
-    for i in range(args.steps):
-        call_op(kind, bufs, ob, desc)
-        evs[i + 1].record(stream)
-    sync_all()
-    clocks = sampler.stop() if sampler else None
-    launches = int(L.t2sp_b200_kernel_launches() - launches0)
-    rc = L.t2sp_b200_sync()
-    if rc != 0:
-        raise SystemExit(f"hot path failed with halide error {rc}")
-    total_ms = evs[0].elapsed_time(evs[-1])
-    step_ms = [evs[i].elapsed_time(evs[i + 1]) for i in range(args.steps)]
-    if dist is not None:
-        t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
-    L.t2sp_b200_set_async(0)
-    ms_per_step = total_ms / args.steps
-    value = world * flops / (ms_per_step * 1e-3) / 1e12
+        return float(t.item())
 
-    # ---- end-to-end arm: pinned host buffers through the synchronous C-ABI call
+    def check(rc, what="hot path"):
+        if rc != 0:
+            raise SystemExit(f"{what} failed with halide error {rc}")
+
+    def timed_region(job, steps, warmup):
+        """W warm-up steps, then exactly `steps` steps between two events, barrier + synchronize on both
+        sides; returns (total ms as the max over ranks, per-step ms of this rank, launches)."""
+        L.t2sp_b200_set_async(1)
+        for _ in range(warmup):
+            check(job.call())
+        check(L.t2sp_b200_sync())
+        sync_all()
+        n0 = L.t2sp_b200_kernel_launches()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        evs[0].record(stream)
+        for i in range(steps):
+            job.call()
+            evs[i + 1].record(stream)
+        sync_all()
+        launches = int(L.t2sp_b200_kernel_launches() - n0)
+        check(L.t2sp_b200_sync())
+        L.t2sp_b200_set_async(0)
+        total = max_over_ranks(evs[0].elapsed_time(evs[-1]))
+        return total, [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)], launches
+
+    def flushed_steps(job, steps, warmup):
+        """Per-step device times with L2 flushed (a 256 MB write) between steps; for working sets that fit L2."""
+        L.t2sp_b200_set_async(1)
+        for _ in range(warmup):
+            check(job.call())
+        check(L.t2sp_b200_sync())
+        pairs = []
+        for _ in range(steps):
+            flush_buf.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            job.call()
+            e1.record(stream)
+            pairs.append((e0, e1))
+        torch.cuda.synchronize()
+        check(L.t2sp_b200_sync())
+        L.t2sp_b200_set_async(0)
+        return [a.elapsed_time(b) for a, b in pairs]
+
+    # ---- headline: operands resident in HBM
+    job = Resident(args.workload, rank, world)
+    flops, abytes = job.flops, job.abytes
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    total_ms, step_ms, launches = timed_region(job, args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    ms_per_step = total_ms / args.steps
+    value = flops / (ms_per_step * 1e-3) / 1e12  # one problem whatever the number of GPUs
+
+    extras = {}
+    if not args.no_extras:
+        # ---- the same launch back to back for more than two seconds: the power-capped regime
+        n_sus = int(min(20000, max(50, 2200.0 / max(ms_per_step, 1e-3))))
+        sus_total, _, _ = timed_region(job, n_sus, 1)
+        sus_ms = sus_total / n_sus
+        sus_tf = flops / (sus_ms * 1e-3) / 1e12
+        pk = peaks()
+        extras["sustained"] = {"steps": n_sus, "ms_per_step": sus_ms, "value": sus_tf, "unit": "TFLOP/s",
+                               "region_s": sus_total * 1e-3,
+                               "frac": (sus_tf / (pk["sustained"] * RATE[w.get("dtype", "f32")])) if kind == "gemm" else None,
+                               "peak_source": f"{pk['src']} cuBLAS bf16 sustained {pk['sustained']} TFLOP/s"}
+        # ---- what the caller pays to have all of C on every GPU afterwards: NCCL all-gather of the column slabs
+        if world > 1 and kind == "gemm":
+            from t2sp_b200 import shard
+            comm = shard.Comm(rank, world, shard.torch_id_exchange(dist, torch.device("cuda", local_rank)))
+            L.t2sp_b200_set_async(1)
+            for _ in range(2):
+                check(comm.gather_columns(job.ob), "gather_columns")
+            sync_all()
+            g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            g0.record(stream)
+            for _ in range(5):
+                comm.gather_columns(job.ob)
+            g1.record(stream)
+            sync_all()
+            L.t2sp_b200_set_async(0)
+            extras["gather_ms"] = max_over_ranks(g0.elapsed_time(g1) / 5)
+            extras["gather_bytes_received_per_gpu"] = int(4 * w["M"] * (w["N"] - w["N"] // world))
+            comm.destroy()
+
+    # ---- end-to-end arm: host buffers through the synchronous C-ABI call (single GPU, or each rank its shard)
     e2e = None
     if not args.no_e2e:
-        pin_in = []
-        for a in arrs:
-            t = torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).pin_memory()
-            pin_in.append(t)
-        pin_out = torch.empty(out_shape, dtype=torch.int32 if out_dtype == np.int32 else torch.float32).pin_memory()
-        hb = [Buffer(tuple(reversed(a.shape)), dt, host=t.data_ptr(), keepalive=t) for a, t, dt in zip(arrs, pin_in, dts)]
-        hob = Buffer(tuple(reversed(out_shape)), "i32" if out_dtype == np.int32 else "f32", host=pin_out.data_ptr(),
-                     keepalive=pin_out)
+        arrs = job.host_in
+        out_shape = job.out_shape
+        out_np = np.int32 if job.out_dt == torch.int32 else np.float32
+
+        def host_job(pinned):
+            class J:
+                pass
+            j = J()
+            if pinned:
+                tin = [torch.from_numpy(a.view(np.int16) if a.dtype == np.uint16 else a).pin_memory() for a in arrs]
+                tout = torch.empty(out_shape, dtype=job.out_dt).pin_memory()
+                hb = [Buffer(tuple(reversed(a.shape)), dt, host=t.data_ptr(), keepalive=t) for a, t, dt in zip(arrs, tin, job.dts)]
+                hob = Buffer(tuple(reversed(out_shape)), "i32" if out_np == np.int32 else "f32", host=tout.data_ptr(), keepalive=tout)
+            else:
+                hb = [Buffer.from_numpy(a, dtype=dt) for a, dt in zip(arrs, job.dts)]  # plain malloc'ed (pageable) memory
+                hob = Buffer.from_numpy(np.empty(out_shape, out_np))
+            h = Resident.__new__(Resident)
+            h.kind, h.desc, h.rank, h.world, h.bufs, h.ob = kind, job.desc, rank, world, hb, hob
+            return h
+
+        def time_host(pinned, steps):
+            h = host_job(pinned)
+            for _ in range(2):
+                check(h.call(), "end-to-end call")
+            sync_all()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                h.call()
+            e1.record(stream)
+            sync_all()
+            return max_over_ranks(e0.elapsed_time(e1)) / steps
+
+        in_bytes = int(sum(a.nbytes for a in arrs))
+        out_bytes = int(np.prod(out_shape)) * 4
         e2e_steps = max(1, min(args.steps, 10))
-        for _ in range(2):
-            rc = call_op(kind, hb, hob, desc)
-            if rc != 0:
-                raise SystemExit(f"end-to-end call failed with halide error {rc}")
-        sync_all()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(e2e_steps):
-            call_op(kind, hb, hob, desc)
-        e1.record(stream)
-        sync_all()
-        e2e_ms = e0.elapsed_time(e1)
-        if dist is not None:
-            t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_ms = float(t.item())
-        e2e = {"value": world * flops / (e2e_ms / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
-               "h2d_bytes_per_step": int(sum(a.nbytes for a in arrs)),
-               "d2h_bytes_per_step": int(np.prod(out_shape)) * 4, "steps": e2e_steps,
-               "ms_per_step": e2e_ms / e2e_steps}
+        ms_pin = time_host(True, e2e_steps)
+        e2e = {"value": flops / (ms_pin * 1e-3) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": in_bytes,
+               "d2h_bytes_per_step": out_bytes, "steps": e2e_steps, "ms_per_step": ms_pin, "host_memory": "pinned"}
+        if not args.no_extras:
+            ms_page = time_host(False, max(1, min(args.steps, 3)))
+            e2e["pageable"] = {"value": flops / (ms_page * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_page,
+                               "note": "the same call on plain malloc'ed host arrays, as Halide::Runtime::Buffer allocates them"}
+
+    # ---- the other configurations, device-timed (single GPU): ~steps launches each, L2 flushed between steps
+    # where the working set fits L2
+    side = []
+    if not args.no_extras and world == 1 and args.workload == "gemm_bf16_8192":
+        del job
+        torch.cuda.empty_cache()
+        for name in SIDE_WORKLOADS:
+            sj = Resident(name, 0, 1, device_generated=True)
+            fits_l2 = sj.abytes <= 126e6
+            if fits_l2:
+                t = flushed_steps(sj, args.steps, 3)
+            else:
+                _, t, _ = timed_region(sj, args.steps, 3)
+            r = roofline_of(name, statistics.mean(t))
+            side.append({"workload": name, "ms_per_step": statistics.mean(t), "ms_min": min(t), "steps": args.steps,
+                         "achieved": r["achieved"], "peak": r["peak"], "unit": r["unit"], "frac": r["frac"], "bound": r["bound"],
+                         "peak_source": r["peak_source"], "l2": "flushed between steps" if fits_l2 else "inputs larger than L2"})
+            del sj
+            torch.cuda.empty_cache()
 
     if rank != 0:
         if dist is not None:
@@ -407,37 +586,27 @@ def main():
             dist.destroy_process_group()
         return
 
-    pk = peaks()
     kernel_ms = statistics.mean(step_ms)
-    # fp32 contractions run as 3xTF32: their tensor ceiling is the bf16 peak / 2 / 3. The bound is
-    # whichever of (bytes / HBM bandwidth) and (FLOPs / tensor ceiling) is the longer time.
-    t_hbm = abytes / (pk["hbm"] * 1e9)
-    t_tensor = flops / (pk["burst"] * {"bf16": 1.0, "f16": 1.0, "i8": 2.0, "f32": 1.0 / 6.0}[w.get("dtype", "f32")] * 1e12)
-    hbm_bound = t_hbm > t_tensor
-    if hbm_bound:
-        achieved, peak, unit = abytes / (kernel_ms * 1e-3) / 1e9, pk["hbm"], "GB/s"
-        peak_note = f"{pk['src']} HBM copy bandwidth"
-    else:
-        long_run = total_ms > 1000.0
-        bf16_peak = pk["sustained"] if long_run else pk["burst"]
-        dt = w.get("dtype", "f32")
-        scale = {"bf16": 1.0, "f16": 1.0, "i8": 2.0, "f32": 1.0 / 6.0}[dt]
-        achieved, peak, unit = flops / (kernel_ms * 1e-3) / 1e12, bf16_peak * scale, "TFLOP/s"
-        peak_note = (f"{pk['src']} cuBLAS bf16 {'sustained' if long_run else 'burst'} {bf16_peak} TFLOP/s"
-                     + {1.0: "", 2.0: " x2 (int8 rate)", 1.0 / 6.0: " /2 (tf32 rate) /3 (three MMAs per product)"}[scale])
-    traffic = KNOWN_TRAFFIC.get(args.workload)
+    roof = roofline_of(args.workload, kernel_ms, long_run=total_ms > 1000.0)
+    if world > 1:
+        # per GPU: its share of the work against one GPU's peak (every rank's launch does 1/world of the FLOPs)
+        roof["achieved"] /= world
+        roof["frac"] /= world
+        roof["note"] = "per GPU: this rank's share of the problem over its own kernel time"
     line = {
         "metric": "throughput", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "strong",
         "vs_baseline": None, "dtype": w.get("dtype", "f32"), "data": "synthetic",
-        "config": {"workload": args.workload, **w, "sharding": "N-column slab per GPU (A replicated)" if kind == "gemm" else "independent batch/slab per GPU",
-                   "l2": "inputs+output larger than L2" if abytes > 126e6 else "operands fit in L2 (working set smaller than 126 MB)"},
-        "e2e": e2e, "gpu_launches": launches,
-        "roofline": {"bound": "hbm" if hbm_bound else "tensor", "achieved": achieved, "peak": peak, "unit": unit,
-                     "frac": achieved / peak, "traffic": traffic, "peak_source": peak_note,
-                     "kernel_ms": kernel_ms, "algorithmic_flops": flops, "algorithmic_bytes": abytes},
-        "clocks": clocks,
+        "config": {"workload": args.workload, **w},
+        "sharding": Resident.SHARDING[kind] if world > 1 else "single GPU",
+        "l2": "inputs+output larger than L2, no flush" if abytes / world > 126e6 else "operands fit in L2 (working set smaller than 126 MB), no flush in the headline region",
+        "e2e": e2e, "gpu_launches": launches, "roofline": roof, "clocks": clocks,
+        "step_ms_min_max": [min(step_ms), max(step_ms)],
     }
+    line.update(extras)
+    if side:
+        line["workloads"] = side
     if not args.no_cpu_baseline and world == 1:
         v, sample, threads = cpu_sample(kind, w)
         line["cpu_baseline"] = {"value": v / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample}

@@ -44,7 +44,36 @@ typedef struct halide_dimension_t {
     uint32_t flags;
 } halide_dimension_t;
 
-struct halide_device_interface_t;
+struct halide_buffer_t;
+struct halide_device_interface_impl_t;
+
+/* 128 bytes: the table of device functions a buffer's `device_interface` points to
+ * (HalideRuntime.h:713-738). Halide::Runtime::Buffer calls through it, e.g. device_free
+ * in its destructor and copy_to_host (HalideBuffer.h:229-252,1615). */
+struct halide_device_interface_t {
+    int (*device_malloc)(void *user_context, struct halide_buffer_t *buf,
+                         const struct halide_device_interface_t *device_interface);
+    int (*device_free)(void *user_context, struct halide_buffer_t *buf);
+    int (*device_sync)(void *user_context, struct halide_buffer_t *buf);
+    void (*device_release)(void *user_context, const struct halide_device_interface_t *device_interface);
+    int (*copy_to_host)(void *user_context, struct halide_buffer_t *buf);
+    int (*copy_to_device)(void *user_context, struct halide_buffer_t *buf,
+                          const struct halide_device_interface_t *device_interface);
+    int (*device_and_host_malloc)(void *user_context, struct halide_buffer_t *buf,
+                                  const struct halide_device_interface_t *device_interface);
+    int (*device_and_host_free)(void *user_context, struct halide_buffer_t *buf);
+    int (*buffer_copy)(void *user_context, struct halide_buffer_t *src,
+                       const struct halide_device_interface_t *dst_device_interface, struct halide_buffer_t *dst);
+    int (*device_crop)(void *user_context, const struct halide_buffer_t *src, struct halide_buffer_t *dst);
+    int (*device_slice)(void *user_context, const struct halide_buffer_t *src, int slice_dim, int slice_pos,
+                        struct halide_buffer_t *dst);
+    int (*device_release_crop)(void *user_context, struct halide_buffer_t *buf);
+    int (*wrap_native)(void *user_context, struct halide_buffer_t *buf, uint64_t handle,
+                       const struct halide_device_interface_t *device_interface);
+    int (*detach_native)(void *user_context, struct halide_buffer_t *buf);
+    int (*compute_capability)(void *user_context, int *major, int *minor);
+    const struct halide_device_interface_impl_t *impl;
+};
 
 enum { halide_buffer_flag_host_dirty = 1, halide_buffer_flag_device_dirty = 2 };
 
@@ -71,6 +100,7 @@ typedef struct halide_buffer_t {
 static_assert(sizeof(struct halide_type_t) == 4, "halide_type_t must be 4 bytes");
 static_assert(sizeof(halide_dimension_t) == 16, "halide_dimension_t must be 16 bytes");
 static_assert(sizeof(halide_buffer_t) == 56, "halide_buffer_t must be 56 bytes");
+static_assert(sizeof(struct halide_device_interface_t) == 16 * sizeof(void *), "halide_device_interface_t is 15 functions and impl");
 static_assert(offsetof(halide_buffer_t, host) == 16 && offsetof(halide_buffer_t, flags) == 24 &&
                   offsetof(halide_buffer_t, type) == 32 && offsetof(halide_buffer_t, dimensions) == 36 &&
                   offsetof(halide_buffer_t, dim) == 40,

@@ -224,6 +224,11 @@ int t2sp_b200_mttkrp_noalloc(const float *a, int64_t a_stride_i, int64_t a_strid
  * inputs are copied from `host` only if no device copy exists or host_dirty is set;
  * outputs stay on the device (device_dirty is set) when the output buffer has a device
  * allocation, otherwise they are copied to `host` and host_dirty is set.             */
+/* The interface is a full function table (HalideRuntime.h:713-738): Halide::Runtime::Buffer's
+ * copy_to_host(), device_free(), crops, slices and destructor work on buffers this library filled.
+ * Host threads: each thread works on a stream, timing events and a kernel status word of its own
+ * (or on the stream given with t2sp_b200_set_stream); cached device blocks that change streams are
+ * ordered by events, so threads may call concurrently. */
 const struct halide_device_interface_t *t2sp_b200_device_interface(void);
 int t2sp_b200_device_malloc(halide_buffer_t *buf);
 int t2sp_b200_device_free(halide_buffer_t *buf);
@@ -232,14 +237,62 @@ int t2sp_b200_copy_to_host(halide_buffer_t *buf);
 int t2sp_b200_wrap_device_ptr(halide_buffer_t *buf, uint64_t device_ptr);
 int t2sp_b200_detach_device_ptr(halide_buffer_t *buf);
 
+/* ---- several GPUs of one box: one process (or host thread) per GPU -----------------------
+ * No counterpart in the reference, which drives one device (AOT-OpenCL-Runtime.cpp:186-213).
+ * Every rank calls the same entry with its rank and the world size, on FULL-SIZE buffers (host
+ * or device-resident); the entry works on this rank's slab of them, which is a view (shifted
+ * base address, unchanged strides), never a copy:
+ *   gemm     columns of B and C (A replicated; plain 2-D output layout)
+ *   conv     batch items n of I and O (weights replicated; plain layout)
+ *   capsule  batch items n of P and V (weights replicated; plain layout)
+ *   ttm      index j of a(l,i,j) and c(i,j,k) (b replicated; plain layout)
+ *   mttkrp   index k of a(l,i,k) and b(k,r), i.e. the contraction: d_partial is this rank's
+ *            full-size partial result, to be summed over the ranks
+ * Slabs are contiguous and near-equal (t2sp_b200_split_range); a rank whose slab is empty does
+ * nothing and returns 0. The contractions themselves exchange nothing between GPUs. */
+void t2sp_b200_split_range(int64_t total, int32_t world, int32_t rank, int64_t *lo, int64_t *hi);
+/* dst (with room for src->dimensions entries in dst_dims) becomes the view of src restricted, in
+ * dimension `dim`, to this rank's share of its extent / unit groups of `unit` consecutive indices. */
+int t2sp_b200_shard_view(const halide_buffer_t *src, int32_t dim, int32_t unit, int32_t rank, int32_t world,
+                         halide_buffer_t *dst, halide_dimension_t *dst_dims);
+int t2sp_b200_gemm_shard(halide_buffer_t *A, halide_buffer_t *B, halide_buffer_t *C, const t2sp_gemm_desc *desc,
+                         int32_t rank, int32_t world);
+int t2sp_b200_conv_shard(halide_buffer_t *I, halide_buffer_t *K, halide_buffer_t *O, const t2sp_conv_desc *desc,
+                         int32_t rank, int32_t world);
+int t2sp_b200_capsule_shard(halide_buffer_t *P, halide_buffer_t *W, halide_buffer_t *V, const t2sp_capsule_desc *desc,
+                            int32_t rank, int32_t world);
+int t2sp_b200_ttm_shard(halide_buffer_t *a, halide_buffer_t *b, halide_buffer_t *c, const t2sp_ttm_desc *desc,
+                        int32_t rank, int32_t world);
+int t2sp_b200_mttkrp_shard(halide_buffer_t *a, halide_buffer_t *b, halide_buffer_t *c, halide_buffer_t *d_partial,
+                           const t2sp_mttkrp_desc *desc, int32_t rank, int32_t world);
+/* The exchange steps, for callers that want a result on every GPU; NCCL over NVLink, enqueued on the
+ * calling thread's stream. libnccl.so.2 is looked up on the first of these calls. `comm` is an
+ * ncclComm_t: the caller's own, or one made here (rank 0 obtains the 128-byte id and hands it to the
+ * other ranks by whatever means the host program has; every rank then calls t2sp_b200_comm_init with
+ * its device selected by t2sp_b200_set_device).
+ *   gather_columns   C (2-D, device-resident, full size on every rank, each rank's slab computed):
+ *                    afterwards every rank holds all columns.
+ *   reduce_partials  d (2-D fp32, device-resident): the sum over the ranks, in place on every rank;
+ *                    ordered != 0 adds the partials in rank order (bitwise reproducible), else ncclAllReduce.
+ *   broadcast        the buffer's device copy on `root` replaces everyone's (replicating an operand). */
+int t2sp_b200_nccl_unique_id(void *id_bytes, int32_t size); /* size >= 128 */
+int t2sp_b200_comm_init(void **comm, int32_t world, const void *id_bytes, int32_t rank);
+int t2sp_b200_comm_destroy(void *comm);
+int t2sp_b200_gather_columns(halide_buffer_t *C, void *comm, int32_t rank, int32_t world);
+int t2sp_b200_reduce_partials(halide_buffer_t *d, void *comm, int32_t rank, int32_t world, int32_t ordered);
+int t2sp_b200_broadcast(halide_buffer_t *buf, void *comm, int32_t root);
+
 /* ---- execution control -------------------------------------------------------------
  * Calls are synchronous by default, like the reference's (clFinish per call,
  * AOT-OpenCL-Runtime.cpp:312-358). */
 int t2sp_b200_set_device(int ordinal);          /* CUDA device for the calling thread (default 0) */
-int t2sp_b200_set_stream(void *cuda_stream);    /* stream for the calling thread; NULL = library's own */
+int t2sp_b200_set_stream(void *cuda_stream);    /* stream for the calling thread; NULL = the thread's own library stream */
 int t2sp_b200_set_async(int enable);            /* 1: calls on device-resident buffers return after enqueue */
 int t2sp_b200_sync(void);                       /* wait for the thread's stream; reports kernel status */
-void t2sp_b200_release(void);                   /* free cached device allocations and streams */
+void t2sp_b200_release(void);                   /* wait for the devices and free cached device allocations */
+/* The T2SP_B200_* environment variables (and BITSTREAM) are read once, at the first call; this reads
+ * them again. Not to be called while another thread is inside the library. */
+void t2sp_b200_reload_env(void);
 uint64_t t2sp_b200_kernel_launches(void);       /* kernels launched by this library since load */
 /* Device time of the last synchronous call's kernels in nanoseconds, as the reference's
  * runtime records per kernel (AOT-OpenCL-Runtime.cpp:360-396). It is also written to

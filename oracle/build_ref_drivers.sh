@@ -27,6 +27,10 @@ $CXX $FLAGS $OFLAGS -DTINY -DREF_GER -I $PERF/ger $PERF/ger/ger-run-fpga.cpp $HE
 ONEC="$REF/t2s/tests/correctness/oneapi-integration"
 $CXX -I $HERE/pin_include $FLAGS $OFLAGS -DTINY -DFPGA_EMULATOR -DREF_ONEAPI_CONV    -I $ONEC $ONEC/oneapi-target-5-run.cpp $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_oneapi_conv_tiny
 $CXX -I $HERE/pin_include $FLAGS $OFLAGS -DTINY -DFPGA_EMULATOR -DREF_ONEAPI_CAPSULE -I $ONEC $ONEC/oneapi-target-6-run.cpp $HERE/ref_interface.cpp $ORACLE_SRC -o $HERE/_ref/pin_oneapi_capsule_tiny
+# TTM and MTTKRP: the golden loops of the reference's test helper (correctness/util/util.h), compiled with
+# a stand-in for the compiler's umbrella header (pin_include/Halide.h), against the oracle's restatements
+UTIL="$REF/t2s/tests/correctness/util"
+$CXX -I $HERE/pin_include $FLAGS $OFLAGS -I $UTIL $HERE/pin_contractions.cpp $ORACLE_SRC -o $HERE/_ref/pin_contractions
 
 # (2) the same drivers against the product
 LINK="-L $ROOT/t2sp_b200 -lt2sp_b200 -Wl,-rpath,\$ORIGIN/../../t2sp_b200"
@@ -72,5 +76,7 @@ if [ -f "$ROOT/t2sp_b200/libt2sp_b200.so" ]; then
   $CXX $FLAGS -I $PERF/gemm    $PERF/gemm/gemm-run-fpga.cpp       $STUBS/gemm-interface.cpp    $SHIM $LINK -o $ROOT/tests/_bin/gemm_large_a10
   $CXX $FLAGS -I $PERF/conv    $PERF/conv/conv-run-fpga.cpp       $STUBS/conv-interface.cpp    $SHIM $LINK -o $ROOT/tests/_bin/conv_large_a10
   $CXX $FLAGS -I $PERF/capsule $PERF/capsule/capsule-run-fpga.cpp $STUBS/capsule-interface.cpp $SHIM $LINK -o $ROOT/tests/_bin/capsule_large_a10
+  # a caller written with the reference tree's Halide::Runtime::Buffer class: the device interface table in use
+  $CXX $FLAGS -O1 $ROOT/tests/drivers/runtime_buffer_flow.cpp $LINK -o $ROOT/tests/_bin/runtime_buffer_flow
 fi
 echo "reference drivers built"

@@ -160,12 +160,7 @@ extern "C" int t2sp_b200_mttkrp_noalloc(const float* a, int64_t a_stride_i, int6
         return halide_error_code_device_run_failed;
     }
     const float* parts = g_partials_addr[dev];
-    if (d_stride_r == I) {
-        e = reduce_partials_launch(parts, d, int64_t(I) * R, splits, stream);
-    } else {
-        for (int r = 0; r < R && e == cudaSuccess; ++r)
-            e = reduce_partials_launch(parts + int64_t(r) * I, d + int64_t(r) * d_stride_r, I, splits, stream);
-    }
+    e = reduce_partials_launch(parts, d, I, R, d_stride_r, splits, stream);
     if (e != cudaSuccess) {
         fprintf(stderr, "t2sp_b200_mttkrp_noalloc: reduction launch failed: %s\n", cudaGetErrorString(e));
         return halide_error_code_device_run_failed;

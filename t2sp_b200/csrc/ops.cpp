@@ -154,7 +154,7 @@ int tma_unsupported(const char* name) {
 void set_rowmajor_epilogue(CoreParams& p, void* out, int M, int N, int64_t ld) {
     p.epi = EPI_ROWMAJOR;
     p.ldo = ld;
-    if (getenv("T2SP_B200_NO_TMA_STORE")) return;
+    if (rt_env().no_tma_store) return;
     if (p.tile_rows != kBlockM) return;  // a warp's 32-row store would spill into the next tile's rows
     if ((reinterpret_cast<uintptr_t>(out) & 15) || (ld * 4) % 16 || ld <= 0) return;
     uint64_t dims[2] = {uint64_t(N), uint64_t(M)}, str[2] = {4, uint64_t(ld) * 4};
@@ -179,8 +179,8 @@ int x3_pick_splits(int tiles, int total_kb, bool scatter = false);
 int x3_pair_width(long long M, int N, int tile_rows, int num_kb) {
     // 256 x 128 pair tiles did not beat the single-CTA kernel (capsule, N = 128: 133 us vs 108 us), so
     // pairs are used for wide outputs only unless $T2SP_B200_PAIR128 asks otherwise.
-    if (getenv("T2SP_B200_NO_PAIR") || tile_rows != kBlockM || N < 128) return 0;
-    if (N <= 128 && !getenv("T2SP_B200_PAIR128")) return 0;
+    if (rt_env().no_pair || tile_rows != kBlockM || N < 128) return 0;
+    if (N <= 128 && !rt_env().pair128) return 0;
     const int un = N > 128 ? 256 : 128;
     const long long tiles = ((M + 255) / 256) * ((N + un - 1) / un);
     if (tiles > (1 << 20)) return un;
@@ -191,9 +191,9 @@ int x3_pair_width(long long M, int N, int tile_rows, int num_kb) {
 // (waves of work items) x (k-blocks per item) plus the cost of the summing pass, counted in
 // k-block times; 1 when the tiles already fill the SM pairs or the contraction is short.
 int x3_pick_splits(int tiles, int total_kb, bool scatter) {
-    if (getenv("T2SP_B200_NO_SPLITK") || total_kb <= 1) return 1;
-    if (const char* f = getenv("T2SP_B200_SPLITK")) {  // forced number of ranges (tests)
-        const int s = std::max(1, std::min(atoi(f), total_kb));
+    if (rt_env().no_splitk || total_kb <= 1) return 1;
+    if (rt_env().splitk) {  // forced number of ranges (tests)
+        const int s = std::max(1, std::min(rt_env().splitk, total_kb));
         const int per = (total_kb + s - 1) / s;
         return (total_kb + per - 1) / per;
     }
@@ -214,13 +214,7 @@ int x3_pick_splits(int tiles, int total_kb, bool scatter) {
 }
 
 int resolve_precision(int p) {
-    if (p == T2SP_PRECISION_DEFAULT) {
-        const char* e = getenv("T2SP_B200_PRECISION");
-        if (e && strcmp(e, "tf32") == 0) return T2SP_PRECISION_TF32;
-        if (e && strcmp(e, "tf32x3") != 0 && strcmp(e, "") != 0)
-            fprintf(stderr, "t2sp_b200: unknown T2SP_B200_PRECISION '%s', using tf32x3\n", e);
-        return T2SP_PRECISION_TF32X3;
-    }
+    if (p == T2SP_PRECISION_DEFAULT) return rt_env().precision;
     return p == T2SP_PRECISION_TF32 ? T2SP_PRECISION_TF32 : T2SP_PRECISION_TF32X3;
 }
 
@@ -255,9 +249,10 @@ int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool syn
     ThreadState& ts = tls();
     cudaStream_t s = rt_stream();
     p.status = rt_status_word();
+    p.wait_cycles = rt_env().wait_cycles;
+    p.skip_stage = rt_env().test_skip_stage;
     if (p.group_m <= 0) p.group_m = pair ? 8 : 16;
 #ifdef T2SP_DEBUG_KNOBS
-    if (const char* d = getenv("T2SP_B200_DEBUG")) p.debug = atoi(d);
     static long long* trace_dev = nullptr;
     const char* trace_path = getenv("T2SP_B200_TRACE");
     p.trace = nullptr;
@@ -267,7 +262,7 @@ int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool syn
         p.trace = trace_dev;
     }
 #endif
-    if (const char* g = getenv("T2SP_B200_GROUP_M")) p.group_m = std::max(1, atoi(g));
+    if (rt_env().group_m) p.group_m = rt_env().group_m;
     const int tiles = p.tiles_m * p.tiles_n;
     // fp32 pair kernel with fewer tiles than SM pairs: cut the contraction into ranges that run as
     // work items of their own, partial tiles go to scratch and a second kernel sums them in order
@@ -345,7 +340,7 @@ int finish_call(const char* who, const char* kernel_name, bool sync_after) {
         tls().last_kernel_ns = double(ms) * 1e6;
         rt_write_exec_time(kernel_name, tls().last_kernel_ns);
     }
-    if (getenv("T2SP_B200_LOG")) fprintf(stderr, "t2sp_b200: %s: kernels %.1f us\n", who, tls().last_kernel_ns * 1e-3);
+    if (rt_env().log) fprintf(stderr, "t2sp_b200: %s: kernels %.1f us\n", who, tls().last_kernel_ns * 1e-3);
     return 0;
 }
 
@@ -423,7 +418,7 @@ namespace {
 int gemm_host_pipelined(halide_buffer_t* A, halide_buffer_t* B, halide_buffer_t* C, const t2sp_gemm_desc* desc,
                         int M, int N, int K, bool* done) {
     *done = false;
-    if (getenv("T2SP_B200_NO_PIPELINE")) return 0;
+    if (rt_env().no_pipeline) return 0;
     if (desc && (desc->layout || desc->trans_a || desc->trans_b || desc->scale)) return 0;
     if (A->device || B->device || C->device) return 0;
     if (A->dim[0].min || A->dim[1].min || B->dim[0].min || B->dim[1].min || C->dim[0].min || C->dim[1].min) return 0;
@@ -642,8 +637,8 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
     if (K == 0 && scale) {
         return constraint("A.extent.0", 0, "positive when alpha/beta scaling is requested", 1);
     } else if (K == 0) {
-        // empty contraction: the result is all zeros
-        cudaMemsetAsync(vw.v[2].ptr, 0, vw.v[2].bytes, rt_stream());
+        // empty contraction: the result is all zeros (inside C's extents; padding between rows is not C's)
+        rt_zero_region(C, vw.v[2].ptr);
     } else {
         const int arith = arith_for(in_t);
         const int prec = arith == AR_TF32X3 ? resolve_precision(desc ? desc->precision : 0) : 0;
@@ -651,7 +646,7 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         const int op = trans_b ? OP_TTM : OP_GEMM;  // OP_TTM is the "both operands K-major" loader
         // Large 16-bit / 8-bit problems run on CTA pairs with 256 x 256 tiles.
         const int x3un = arith == AR_TF32X3 ? x3_pair_width(M, N, kBlockM, (K + bk - 1) / bk) : 0;
-        const bool pair = x3un || (arith != AR_TF32X3 && M >= 512 && N >= 512 && !getenv("T2SP_B200_NO_PAIR"));
+        const bool pair = x3un || (arith != AR_TF32X3 && M >= 512 && N >= 512 && !rt_env().no_pair);
         const int bn = x3un ? x3un : (pair ? 256 : core_pick_bn(arith, op, N, M));
         int64_t lda = int64_t(A->dim[1].stride) * es;
         const int64_t ldb = int64_t(B->dim[1].stride) * es;
@@ -696,11 +691,10 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         p.tiles_m = (M + kBlockM - 1) / kBlockM; p.tiles_n = (N + bn - 1) / bn;
         p.idesc = idesc_for(arith, in_t, !trans_b, bn);
         // 512-row pair tiles when there are enough of them to fill the SM pairs several times over
-        const char* p2env = getenv("T2SP_B200_PAIR2");
         // (measured: 8192^3 bf16 1436 -> 1536 TFLOP/s, 16384^3 1367 -> 1481; with K = 1024 the tile's
         // drain no longer hides behind the next tile and the 256-row tiles win, 1191 vs 957)
         const bool long_k = (K + bk - 1) / bk >= 64;
-        const bool pair2 = pair && !x3un && M >= 1024 && (p2env ? atoi(p2env) != 0 : long_k);
+        const bool pair2 = pair && !x3un && M >= 1024 && (rt_env().pair2 >= 0 ? rt_env().pair2 != 0 : long_k);
         if (pair) {
             p.tiles_m = pair2 ? (M + 511) / 512 : (M + 255) / 256;
             p.idesc = make_instr_desc(arith == AR_I8 ? 2 : 1, arith == AR_I8 ? 1 : (arith == AR_TF32X3 ? 2 : (in_t == kBF16 ? 1 : 0)),
@@ -823,7 +817,7 @@ extern "C" int t2sp_b200_ttm(halide_buffer_t* a, halide_buffer_t* b, halide_buff
     char* pb = static_cast<char*>(vw.v[1].ptr) + origin_offset(b) * 4;
     uint32_t* pc = static_cast<uint32_t*>(vw.v[2].ptr) + origin_offset(c);
     if (L == 0) {
-        cudaMemsetAsync(vw.v[2].ptr, 0, vw.v[2].bytes, rt_stream());
+        rt_zero_region(c, vw.v[2].ptr);
     } else {
         const int prec = resolve_precision(desc ? desc->precision : 0);
         const int M = static_cast<int>(Mrows), N = Kn;
@@ -1172,7 +1166,7 @@ extern "C" int t2sp_b200_capsule(halide_buffer_t* P, halide_buffer_t* W, halide_
             add_digit(p.dn, 1, 1 << 30, 1);
         }
     } else {
-        if (slots > OY * OX) cudaMemsetAsync(vw.v[2].ptr, 0, vw.v[2].bytes, rt_stream());
+        if (slots > OY * OX) rt_zero_region(V, vw.v[2].ptr);
         p.epi = EPI_SCATTER;
         const halide_dimension_t* d = V->dim;
         add_digit(p.dm, 1, MX, d[5].stride);
@@ -1233,15 +1227,9 @@ int mttkrp_launch(const char* who, float* pa, int64_t lda1, int64_t lda2, const 
     p.L = L; p.Kdim = Kd; p.R = R;
     p.single_pass = single_pass;
     if (int e = run_core(who, AR_TF32X3, OP_MTTKRP, bn, p, sync_after)) return e;
-    if (ldd == I) {
-        if (reduce_partials_launch(scratch, pd, int64_t(I) * R, splits, rt_stream()) != cudaSuccess)
-            return halide_error_code_device_run_failed;
-    } else {
-        for (int r = 0; r < R; ++r)
-            if (reduce_partials_launch(scratch + int64_t(r) * I, pd + int64_t(r) * ldd, I, splits, rt_stream()) != cudaSuccess)
-                return halide_error_code_device_run_failed;
-    }
-    rt_count_launch(ldd == I ? 1 : R);
+    if (reduce_partials_launch(scratch, pd, I, R, ldd, splits, rt_stream()) != cudaSuccess)
+        return halide_error_code_device_run_failed;
+    rt_count_launch(1);
     if (sync_after) cudaEventRecord(rt_event(1), rt_stream());
     return 0;
 }
@@ -1310,7 +1298,7 @@ extern "C" int t2sp_b200_mttkrp(halide_buffer_t* a, halide_buffer_t* b, halide_b
     float* pc = static_cast<float*>(vw.v[2].ptr) + origin_offset(c);
     float* pd = static_cast<float*>(vw.v[3].ptr) + origin_offset(d);
     if (L == 0 || Kd == 0) {
-        cudaMemsetAsync(vw.v[3].ptr, 0, vw.v[3].bytes, rt_stream());
+        rt_zero_region(d, vw.v[3].ptr);
     } else {
         const int prec = resolve_precision(desc ? desc->precision : 0);
         int splits = 0, num_kb = 0;

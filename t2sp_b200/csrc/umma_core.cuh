@@ -18,7 +18,7 @@
 // the hi*hi accumulator run for only kChunkKb k-blocks before the epilogue warps add it,
 // round-to-nearest, into fp32 registers.
 //
-// Every wait on an mbarrier is bounded: after kWaitTimeoutCycles the waiting thread raises a
+// Every wait on an mbarrier is bounded: after CoreParams::wait_cycles (kWaitTimeoutCycles by default) the waiting thread raises a
 // status bit in global memory, tells the rest of the CTA to stop, and the CTA drains and
 // frees its TMEM before returning.
 #pragma once
@@ -96,6 +96,7 @@ struct CoreCfg {
 struct AbortCtx {
     volatile uint32_t* flag;  // shared memory, CTA-wide
     unsigned* status;         // global memory
+    long long limit;          // SM cycles a wait may last
 };
 
 __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ab, unsigned code) {
@@ -107,7 +108,7 @@ __device__ __forceinline__ bool bounded_wait(uint64_t* bar, uint32_t parity, con
         if (ptx::mbar_try_wait(bar, parity)) return true;
         if ((++polls & 0x3Fu) == 0) {
             if (*ab.flag) return false;
-            if (clock64() - t0 > kWaitTimeoutCycles) {
+            if (clock64() - t0 > ab.limit) {
                 *ab.flag = 1u;
                 atomicOr(ab.status, code);
                 return false;
@@ -228,7 +229,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const AbortCtx ab{abort_slot, p.status};
+    const AbortCtx ab{abort_slot, p.status, p.wait_cycles > 0 ? p.wait_cycles : kWaitTimeoutCycles};
     const int num_tiles = p.tiles_m * p.tiles_n;
 
     if (threadIdx.x == 0) {
@@ -281,6 +282,9 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                     T2SP_TRACE(p, 0, it);
                     uint8_t* sa = smem + s * Cfg::kStageBytes;
                     uint8_t* sb = sa + Cfg::kABytes;
+                    // Test hook for the bounded waits: this k-block's copies are left out, so its `full` barrier
+                    // never completes, the consumer's wait runs out and the CTA takes the abort path.
+                    if (p.skip_stage && it + 1 == p.skip_stage) continue;
                     ptx::mbar_expect_tx(&full_bar[s], p.a_tx_bytes + Cfg::kBBytes);
                     if constexpr (OP == OP_GEMM || OP == OP_TTM) {
                         ptx::tma_load_2d(sa, &p.mapA[0], &full_bar[s], kb * AT::kBlockK, m0);

@@ -1,85 +1,22 @@
-// Instantiations of the contraction kernel and their launch table.
+// The small kernels around the contraction kernels (split-K sums, layout changes, SYRK fold, GER) and
+// their launchers; the contraction kernels themselves are instantiated in launch_*.cu.
+#include "launch_util.cuh"
 #include "umma_core.cuh"
-#include "umma_pair.cuh"
-#include "umma_pair2.cuh"
-#include "umma_x3pair.cuh"
 #include "umma_launch.h"
 
 namespace t2sp {
 
 namespace {
 
-template <int ARITH, int OP, int BN, int STAGES>
-cudaError_t launch_one(const CoreParams& p, int grid, cudaStream_t stream) {
-    using Cfg = CoreCfg<ARITH, OP, BN, STAGES>;
-    auto kern = umma_contract_kernel<ARITH, OP, BN, STAGES>;
-    static bool configured[16] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 16 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-        if (e != cudaSuccess) return e;
-        configured[dev] = true;
-    }
-    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
-    return cudaGetLastError();
-}
-
-template <int ARITH, int OP, int STAGES>
-cudaError_t launch_pair(const CoreParams& p, int grid, cudaStream_t stream) {
-    using Cfg = PairCfg<ARITH, OP, STAGES>;
-    auto kern = umma_pair_kernel<ARITH, OP, STAGES>;
-    static bool configured[16] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 16 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-        if (e != cudaSuccess) return e;
-        configured[dev] = true;
-    }
-    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
-    return cudaGetLastError();
-}
-
-template <int ARITH, int OP, int STAGES>
-cudaError_t launch_pair2(const CoreParams& p, int grid, cudaStream_t stream) {
-    using Cfg = Pair2Cfg<ARITH, OP, STAGES>;
-    auto kern = umma_pair2_kernel<ARITH, OP, STAGES>;
-    static bool configured[16] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 16 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-        if (e != cudaSuccess) return e;
-        configured[dev] = true;
-    }
-    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
-    return cudaGetLastError();
-}
-
-template <int OP, int UN, int STAGES, int LOSLOTS>
-cudaError_t launch_x3pair(const CoreParams& p, int grid, cudaStream_t stream) {
-    using Cfg = X3PairCfg<OP, UN, STAGES, LOSLOTS>;
-    auto kern = umma_x3pair_kernel<OP, UN, STAGES, LOSLOTS>;
-    static bool configured[16] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 16 && !configured[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-        if (e != cudaSuccess) return e;
-        configured[dev] = true;
-    }
-    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
-    return cudaGetLastError();
-}
-
-__global__ void reduce_partials_kernel(const float* __restrict__ partials, float* __restrict__ out, long long elems,
-                                       int splits) {
-    const long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-    if (i >= elems) return;
+// Partial slabs [split][col][row] (dense, `rows` fastest) summed in split order into out[col * ld_out + row].
+__global__ void reduce_partials_kernel(const float* __restrict__ partials, float* __restrict__ out, int rows, int cols,
+                                       long long ld_out, int splits) {
+    const long long elems = static_cast<long long>(rows) * cols;
+    const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    if (idx >= elems) return;
     float acc = 0.f;
-    for (int s = 0; s < splits; ++s) acc += partials[s * elems + i];
-    out[i] = acc;
+    for (int s = 0; s < splits; ++s) acc += partials[s * elems + idx];
+    out[(idx / rows) * ld_out + idx % rows] = acc;
 }
 
 // One thread per row and four consecutive columns; the sum over the slabs runs in slab order.
@@ -241,16 +178,16 @@ ger_rows_kernel(const float* __restrict__ a, const float* __restrict__ x, const 
 }  // namespace
 
 int core_sm_count() {
-    static int cached[16] = {};
+    static std::atomic<int> cached[kMaxDev];
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev < 0 || dev >= 16) dev = 0;
-    if (cached[dev] == 0) {
-        int n = 0;
+    const bool in_table = dev >= 0 && dev < kMaxDev;
+    int n = in_table ? cached[dev].load(std::memory_order_relaxed) : 0;
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        cached[dev] = n;
+        if (in_table) cached[dev].store(n, std::memory_order_relaxed);
     }
-    return cached[dev];
+    return n;
 }
 
 int core_pick_bn(int arith, int op, int n_extent, long long m_extent) {
@@ -268,76 +205,6 @@ int core_pick_bn(int arith, int op, int n_extent, long long m_extent) {
             return 0;
     }
     return 0;
-}
-
-// Raw-ring depth of the single-CTA fp32 kernels: what fits beside the lo ring, which holds B tiles only
-// when the A operand lives in tensor memory.
-constexpr int x3_stages(int op, int bn) {
-    const bool a_tmem = bn <= T2SP_ATMEM_MAX_BN;
-    if (op == OP_MTTKRP) return bn <= 64 ? (a_tmem ? 7 : 6) : (a_tmem ? 4 : 3);
-    return bn <= 64 ? (a_tmem ? 6 : 5) : (a_tmem ? 4 : 3);
-}
-
-cudaError_t core_launch(int arith, int op, int bn, const CoreParams& p, int grid, cudaStream_t stream) {
-#define T2SP_CASE(AR, OPC, BNV, ST) \
-    if (arith == AR && op == OPC && bn == BNV) return launch_one<AR, OPC, BNV, ST>(p, grid, stream)
-    T2SP_CASE(AR_F16, OP_GEMM, 256, 4);
-    T2SP_CASE(AR_F16, OP_GEMM, 128, 6);
-    T2SP_CASE(AR_F16, OP_TTM, 256, 4);
-    T2SP_CASE(AR_F16, OP_TTM, 128, 6);
-    T2SP_CASE(AR_I8, OP_GEMM, 256, 4);
-    T2SP_CASE(AR_I8, OP_GEMM, 128, 6);
-    T2SP_CASE(AR_I8, OP_TTM, 256, 4);
-    T2SP_CASE(AR_I8, OP_TTM, 128, 6);
-    T2SP_CASE(AR_TF32X3, OP_GEMM, 128, x3_stages(OP_GEMM, 128));
-    T2SP_CASE(AR_TF32X3, OP_GEMM, 64, x3_stages(OP_GEMM, 64));
-    T2SP_CASE(AR_TF32X3, OP_TTM, 128, x3_stages(OP_TTM, 128));
-    T2SP_CASE(AR_TF32X3, OP_TTM, 64, x3_stages(OP_TTM, 64));
-    T2SP_CASE(AR_TF32X3, OP_CONV, 128, x3_stages(OP_CONV, 128));
-    T2SP_CASE(AR_TF32X3, OP_CONV, 64, x3_stages(OP_CONV, 64));
-    T2SP_CASE(AR_TF32X3, OP_CAPSULE, 128, x3_stages(OP_CAPSULE, 128));
-    T2SP_CASE(AR_TF32X3, OP_CAPSULE, 64, x3_stages(OP_CAPSULE, 64));
-    T2SP_CASE(AR_TF32X3, OP_MTTKRP, 64, x3_stages(OP_MTTKRP, 64));
-    T2SP_CASE(AR_TF32X3, OP_MTTKRP, 128, x3_stages(OP_MTTKRP, 128));
-#undef T2SP_CASE
-    return cudaErrorInvalidValue;
-}
-
-cudaError_t pair_launch(int arith, int op, const CoreParams& p, int grid, cudaStream_t stream) {
-    if (arith == AR_F16 && op == OP_GEMM) return launch_pair<AR_F16, OP_GEMM, 6>(p, grid, stream);
-    if (arith == AR_F16 && op == OP_TTM) return launch_pair<AR_F16, OP_TTM, 6>(p, grid, stream);
-    if (arith == AR_I8 && op == OP_GEMM) return launch_pair<AR_I8, OP_GEMM, 6>(p, grid, stream);
-    if (arith == AR_I8 && op == OP_TTM) return launch_pair<AR_I8, OP_TTM, 6>(p, grid, stream);
-    return cudaErrorInvalidValue;
-}
-
-cudaError_t pair2_launch(int arith, int op, const CoreParams& p, int grid, cudaStream_t stream) {
-    if (arith == AR_F16 && op == OP_GEMM) return launch_pair2<AR_F16, OP_GEMM, 4>(p, grid, stream);
-    if (arith == AR_F16 && op == OP_TTM) return launch_pair2<AR_F16, OP_TTM, 4>(p, grid, stream);
-    if (arith == AR_I8 && op == OP_GEMM) return launch_pair2<AR_I8, OP_GEMM, 4>(p, grid, stream);
-    if (arith == AR_I8 && op == OP_TTM) return launch_pair2<AR_I8, OP_TTM, 4>(p, grid, stream);
-    return cudaErrorInvalidValue;
-}
-
-cudaError_t x3pair_launch(int op, int un, const CoreParams& p, int grid, cudaStream_t stream) {
-#define T2SP_X3(OPC, UNV, ST, LO) \
-    if (op == OPC && un == UNV) return launch_x3pair<OPC, UNV, ST, LO>(p, grid, stream)
-#ifdef T2SP_DEBUG_KNOBS
-    if (p.debug & 64) {  // timing experiment: the earlier ring split (4 raw stages, 2 lo slots)
-        T2SP_X3(OP_TTM, 256, 4, 2);
-        T2SP_X3(OP_CONV, 256, 4, 2);
-    }
-#endif
-    T2SP_X3(OP_GEMM, 256, 3, 3);
-    T2SP_X3(OP_GEMM, 128, 5, 3);
-    T2SP_X3(OP_TTM, 256, 3, 3);
-    T2SP_X3(OP_TTM, 128, 5, 3);
-    T2SP_X3(OP_CONV, 256, 3, 3);
-    T2SP_X3(OP_CONV, 128, 5, 3);
-    T2SP_X3(OP_CAPSULE, 256, 3, 3);
-    T2SP_X3(OP_CAPSULE, 128, 5, 3);
-#undef T2SP_X3
-    return cudaErrorInvalidValue;
 }
 
 // dst[z][c][r] = src[z][r][c] for `batch` matrices of rows x cols 32-bit elements (pitches and batch
@@ -436,11 +303,13 @@ cudaError_t ger_launch(const float* a, const float* x, const float* y, float* o,
     return cudaGetLastError();
 }
 
-cudaError_t reduce_partials_launch(const float* partials, float* out, long long elems, int splits,
+cudaError_t reduce_partials_launch(const float* partials, float* out, int rows, int cols, long long ld_out, int splits,
                                    cudaStream_t stream) {
     const int threads = 256;
+    const long long elems = static_cast<long long>(rows) * cols;
+    if (elems <= 0) return cudaSuccess;
     const long long blocks = (elems + threads - 1) / threads;
-    reduce_partials_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(partials, out, elems, splits);
+    reduce_partials_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(partials, out, rows, cols, ld_out, splits);
     return cudaGetLastError();
 }
 

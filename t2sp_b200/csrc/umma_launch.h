@@ -36,9 +36,9 @@ cudaError_t transpose32_launch(const void* src, long long ld_src, void* dst, lon
 // Number of SMs of the current device (cached).
 int core_sm_count();
 
-// Sums `splits` partial slabs of `elems` fp32 values each into `out` in slab order
-// (deterministic), used by the split-K MTTKRP.
-cudaError_t reduce_partials_launch(const float* partials, float* out, long long elems, int splits,
+// Sums `splits` dense partial slabs [split][col][row] (rows * cols fp32 values each, row fastest) in
+// slab order (deterministic) into out[col * ld_out + row]; used by the split-K MTTKRP.
+cudaError_t reduce_partials_launch(const float* partials, float* out, int rows, int cols, long long ld_out, int splits,
                                    cudaStream_t stream);
 
 // Split-K epilogue of the fp32 pair kernel: sums the `splits` partial tiles (row-major slabs of

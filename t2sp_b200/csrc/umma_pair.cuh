@@ -55,7 +55,7 @@ umma_pair_kernel(const __grid_constant__ CoreParams p) {
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t rank = ptx::cluster_ctarank();
-    const AbortCtx ab{abort_slot, p.status};
+    const AbortCtx ab{abort_slot, p.status, p.wait_cycles > 0 ? p.wait_cycles : kWaitTimeoutCycles};
     const int num_tiles = p.tiles_m * p.tiles_n;  // tiles of 256 x 256
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
@@ -100,13 +100,6 @@ umma_pair_kernel(const __grid_constant__ CoreParams p) {
                     uint8_t* sa = smem + s * Cfg::kStageBytes;
                     uint8_t* sb = sa + Cfg::kABytes;
                     const uint32_t leader_full = ptx::map_to_cta(&full_bar[s], 0);
-#ifdef T2SP_DEBUG_KNOBS
-                    if (p.debug & 1) {  // timing experiment: no B traffic
-                        if (rank == 0) ptx::mbar_expect_tx(&full_bar[s], 2 * Cfg::kABytes);
-                        ptx::tma_load_2d_pair(sa, &p.mapA[0], leader_full, kb * AT::kBlockK, m0);
-                        continue;
-                    }
-#endif
                     if (rank == 0) ptx::mbar_expect_tx(&full_bar[s], 2 * Cfg::kStageBytes);
                     ptx::tma_load_2d_pair(sa, &p.mapA[0], leader_full, kb * AT::kBlockK, m0);
                     if constexpr (Cfg::kBMnMajor) {
@@ -142,11 +135,6 @@ umma_pair_kernel(const __grid_constant__ CoreParams p) {
                     const uint32_t sa = ptx::smem_u32(smem + s * Cfg::kStageBytes);
                     const uint64_t da = ptx::make_smem_desc(sa, 16, 1024);
                     const uint64_t db = ptx::make_smem_desc(sa + Cfg::kABytes, kLboB, 1024);
-#ifdef T2SP_DEBUG_KNOBS
-                    if (p.debug & 2) {  // timing experiment: a quarter of the MMAs
-                        ptx::umma<AT::kKind, 2>(d_tmem, da, db, p.idesc, kb ? 1u : 0u);
-                    } else
-#endif
 #pragma unroll
                     for (int j = 0; j < AT::kBlockK / AT::kUmmaK; ++j)
                         ptx::umma<AT::kKind, 2>(d_tmem, da + j * kStepK, db + j * kStepB, p.idesc, (kb | j) ? 1u : 0u);

@@ -54,7 +54,7 @@ umma_pair2_kernel(const __grid_constant__ CoreParams p) {
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t rank = ptx::cluster_ctarank();
-    const AbortCtx ab{abort_slot, p.status};
+    const AbortCtx ab{abort_slot, p.status, p.wait_cycles > 0 ? p.wait_cycles : kWaitTimeoutCycles};
     const int num_tiles = p.tiles_m * p.tiles_n;  // tiles of 512 x 256
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
@@ -130,10 +130,7 @@ umma_pair2_kernel(const __grid_constant__ CoreParams p) {
             // begin as soon as accumulator 0 has been drained, while accumulator 1 is still leaving; at the end
             // it finishes early, so its drain runs under sub-tile 1's last MMAs. In between the two advance in
             // step, one stage per k-block. All `lead` stages are held while a sub-tile runs alone.
-            int lead = Cfg::kLead < p.num_kb / 2 ? Cfg::kLead : p.num_kb / 2;
-#ifdef T2SP_DEBUG_KNOBS
-            if (p.debug > 0) lead = (p.debug - 1) < p.num_kb / 2 ? (p.debug - 1) : p.num_kb / 2;
-#endif
+            const int lead = Cfg::kLead < p.num_kb / 2 ? Cfg::kLead : p.num_kb / 2;
             auto wait_full = [&](int i) -> bool {
                 T2SP_TRACE(p, 8, i);
                 if (!bounded_wait(&full_bar[i % STAGES], (i / STAGES) & 1, ab, ST_TIMEOUT_MMA)) return false;

@@ -86,7 +86,8 @@ struct CoreParams {
     int use_ab;       // EPI_ROWMAJOR, fp32: out = alpha * acc + beta * out
     float alpha, beta;
     int single_pass;  // fp32 data: 1 = one TF32 MMA per product (raw tiles, no hi/lo split)
-    int debug;        // only read by builds with T2SP_DEBUG_KNOBS (timing experiments)
+    long long wait_cycles;  // limit of every mbarrier wait in SM cycles (kWaitTimeoutCycles unless a test shortens it)
+    int skip_stage;   // test hook for the bounded waits: the producer leaves out the copies of this k-block (1-based; 0 = none)
     unsigned* status;
 #ifdef T2SP_DEBUG_KNOBS
     long long* trace;  // per-role cycle stamps of CTAs 0 and 1 (timing experiments), or null

@@ -79,7 +79,7 @@ umma_x3pair_kernel(const __grid_constant__ CoreParams p) {
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const uint32_t rank = ptx::cluster_ctarank();
-    const AbortCtx ab{abort_slot, p.status};
+    const AbortCtx ab{abort_slot, p.status, p.wait_cycles > 0 ? p.wait_cycles : kWaitTimeoutCycles};
     // Work items: tiles of 256 x UN, each cut along the contraction into `splits` ranges of num_kb
     // k-blocks (the last one may be shorter). Item t is range t % splits of tile t / splits; with
     // splits > 1 range s writes its partial tile to rows [s * slab_rows, ...) of the output map.

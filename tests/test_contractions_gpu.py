@@ -95,6 +95,21 @@ def test_mttkrp_random(lib, L, I, K, R, splits):
     assert rc2 == 0 and np.array_equal(d, d2)
 
 
+@pytest.mark.parametrize("splits", [1, 5])
+def test_mttkrp_padded_output_pitch(lib, splits):
+    """d with a row pitch wider than I (d.stride.1 = I + 12): the ordered sum over the split slabs must
+    address slab s of column r, and the 12 elements between the columns are the caller's (NaN stays NaN)."""
+    L, I, K, R, pad = 96, 200, 17, 40, 12
+    a, b, c = O.uniform(5, 1, (K, I, L)), O.uniform(5, 2, (R, K)), O.uniform(5, 3, (R, L))
+    d = np.full((R, I + pad), np.nan, np.float32)
+    db = Buffer((I, R), "f32", host=d.ctypes.data, strides=(1, I + pad), keepalive=d)
+    rc = t2sp_b200.mttkrp(Buffer.from_numpy(a), Buffer.from_numpy(b), Buffer.from_numpy(c), db, t2sp_b200.MttkrpDesc(0, splits))
+    assert rc == 0
+    assert np.isnan(d[:, I:]).all()
+    assert not np.isnan(d[:, :I]).any()
+    assert normwise(d[:, :I], O.mttkrp_f32(a, b, c, acc64=True)) <= TOL_FP32
+
+
 @pytest.mark.parametrize("III,II,I,K", [(12, 8, 8, 1024), (4, 2, 4, 40), (8, 4, 2, 100)])
 def test_syrk_folded_output(lib, III, II, I, K):
     """O(jjj,iii,jj,ii,j,i) = Alpha * (A A^T)(r,c) + Beta * C(r,c) with the fold of

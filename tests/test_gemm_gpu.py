@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 
 from tests import oracle_lib as O
-from tests.util import TOL_BF16, TOL_FP32, call_gemm, componentwise, normwise
+from tests.util import TOL_BF16, TOL_FP32, call_gemm, componentwise, library_env, normwise
 
 pytestmark = pytest.mark.gpu
 
@@ -194,26 +194,24 @@ def test_fp32_cta_pair_kernel(lib, M, N, K, trans_b):
 
 
 @pytest.mark.parametrize("M,N,K,trans_b,force", [(1024, 1024, 1024, 0, None), (1024, 1000, 2048, 1, "3"), (2048, 300, 520, 0, "5")])
-def test_fp32_split_k(lib, monkeypatch, M, N, K, trans_b, force):
+def test_fp32_split_k(lib, M, N, K, trans_b, force):
     """fp32 problems with fewer 256-row tiles than SM pairs cut the contraction into ranges (work items of
     their own) and sum the partial tiles in range order in a second kernel; uneven ranges included."""
     import t2sp_b200
     from t2sp_b200 import Buffer, GemmDesc
-    if force:
-        monkeypatch.setenv("T2SP_B200_SPLITK", force)
     A, B = O.uniform(12, 1, (M, K)), O.uniform(12, 2, (K, N))
     d = GemmDesc()
     d.trans_b = trans_b
     Bin = np.ascontiguousarray(B.T) if trans_b else B
     outs = []
     for no_split in (False, True):
-        if no_split:
-            monkeypatch.setenv("T2SP_B200_NO_SPLITK", "1")
-        C = np.full((M, N), np.nan, np.float32)
-        cb = Buffer.from_numpy(C)
-        before = lib.t2sp_b200_kernel_launches()
-        assert t2sp_b200.gemm(Buffer.from_numpy(A), Buffer.from_numpy(Bin), cb, d) == 0
-        outs.append((cb.keepalive.copy(), lib.t2sp_b200_kernel_launches() - before))
+        env = {"T2SP_B200_NO_SPLITK": "1"} if no_split else ({"T2SP_B200_SPLITK": force} if force else {})
+        with library_env(**env):
+            C = np.full((M, N), np.nan, np.float32)
+            cb = Buffer.from_numpy(C)
+            before = lib.t2sp_b200_kernel_launches()
+            assert t2sp_b200.gemm(Buffer.from_numpy(A), Buffer.from_numpy(Bin), cb, d) == 0
+            outs.append((cb.keepalive.copy(), lib.t2sp_b200_kernel_launches() - before))
     (split, n_split), (whole, n_whole) = outs
     assert n_split == n_whole + 1, "the split path launches the summing kernel as well"
     truth = O.gemm_f32(A, B, acc64=True)
@@ -222,24 +220,24 @@ def test_fp32_split_k(lib, monkeypatch, M, N, K, trans_b, force):
     assert componentwise(split, truth, O.gemm_f32(np.abs(A), np.abs(B), acc64=True)) <= TOL_FP32
 
 
-def test_fp32_split_k_tiled_layout_and_blas_epilogue(lib, monkeypatch):
+def test_fp32_split_k_tiled_layout_and_blas_epilogue(lib):
     """The summing kernel applies the call's own epilogue: the 6-D tiled layout and alpha/beta.
     (Split-K is forced: by itself the library avoids it for tiled layouts, whose summing pass is dear.)"""
-    monkeypatch.setenv("T2SP_B200_SPLITK", "4")
-    JJJ, III, JJ, II = 8, 16, 2, 4
-    M, N, K = III * II * 32, JJJ * JJ * 32, 1024
-    A, B = O.uniform(13, 1, (M, K)), O.uniform(13, 2, (K, N))
-    rc, C6 = call_gemm(A, B, "f32", tiled=(JJJ, III, JJ, II))
-    assert rc == 0
-    ref6 = O.gemm_tile_layout(O.gemm_f32(A, B, acc64=True), JJJ, III, JJ, II)
-    assert not np.isnan(C6).any()
-    assert normwise(C6, ref6) <= TOL_FP32
-    m = n = k = 1024
-    a, b, c0 = O.uniform(13, 3, (m, k)), O.uniform(13, 4, (k, n)), O.uniform(13, 5, (m, n))
-    c = c0.copy()
-    assert lib.t2sp_b200_sgemm(b"N", b"N", m, n, k, 1.75, a.ctypes.data, 0, b.ctypes.data, 0, -0.5, c.ctypes.data, 0) == 0
-    truth = 1.75 * (a.astype(np.float64) @ b.astype(np.float64)) - 0.5 * c0.astype(np.float64)
-    assert normwise(c, truth) <= TOL_FP32
+    with library_env(T2SP_B200_SPLITK="4"):
+        JJJ, III, JJ, II = 8, 16, 2, 4
+        M, N, K = III * II * 32, JJJ * JJ * 32, 1024
+        A, B = O.uniform(13, 1, (M, K)), O.uniform(13, 2, (K, N))
+        rc, C6 = call_gemm(A, B, "f32", tiled=(JJJ, III, JJ, II))
+        assert rc == 0
+        ref6 = O.gemm_tile_layout(O.gemm_f32(A, B, acc64=True), JJJ, III, JJ, II)
+        assert not np.isnan(C6).any()
+        assert normwise(C6, ref6) <= TOL_FP32
+        m = n = k = 1024
+        a, b, c0 = O.uniform(13, 3, (m, k)), O.uniform(13, 4, (k, n)), O.uniform(13, 5, (m, n))
+        c = c0.copy()
+        assert lib.t2sp_b200_sgemm(b"N", b"N", m, n, k, 1.75, a.ctypes.data, 0, b.ctypes.data, 0, -0.5, c.ctypes.data, 0) == 0
+        truth = 1.75 * (a.astype(np.float64) @ b.astype(np.float64)) - 0.5 * c0.astype(np.float64)
+        assert normwise(c, truth) <= TOL_FP32
 
 
 @pytest.mark.parametrize("ta,tb,m,n,k", [("N", "N", 256, 192, 128), ("T", "N", 300, 200, 100), ("N", "T", 128, 260, 64),
@@ -286,11 +284,8 @@ def test_large_host_gemm_is_pipelined_and_identical(lib):
     A, B = O.to_bf16(O.uniform(12, 1, (M, K))), O.to_bf16(O.uniform(12, 2, (K, N)))
     rc, C1 = call_gemm(A, B, "bf16")
     assert rc == 0 and not np.isnan(C1).any()
-    os.environ["T2SP_B200_NO_PIPELINE"] = "1"
-    try:
+    with library_env(T2SP_B200_NO_PIPELINE="1"):
         rc, C2 = call_gemm(A, B, "bf16")
-    finally:
-        del os.environ["T2SP_B200_NO_PIPELINE"]
     assert rc == 0
     assert np.array_equal(C1, C2)
     rows = slice(1000, 1064)
@@ -298,8 +293,9 @@ def test_large_host_gemm_is_pipelined_and_identical(lib):
 
 
 def test_concurrent_host_threads(lib):
-    """The library is re-entrant (per-thread stream and status word, reference: single-shot globals in
-    t2s/src/AOT-OpenCL-Runtime.cpp:25-34): two host threads issue different contractions at once."""
+    """The library is re-entrant (every host thread works on its own stream, event pair and status word;
+    reference: single-shot globals in t2s/src/AOT-OpenCL-Runtime.cpp:25-34): two host threads issue
+    different contractions at once."""
     import threading
     import t2sp_b200
     from t2sp_b200 import Buffer
@@ -327,3 +323,106 @@ def test_concurrent_host_threads(lib):
     for t in threads:
         t.join()
     assert not errors, errors
+
+
+def test_sgemm_padded_output_keeps_its_padding(lib):
+    """ldc > n with beta == 0: only the m x n region of the host array may change; the elements between
+    the rows belong to the caller (they are NaN here and must stay NaN)."""
+    m, n, k, ldc = 300, 200, 96, 232
+    a, b = O.uniform(21, 1, (m, k)), O.uniform(21, 2, (k, n))
+    c = np.full((m, ldc), np.nan, np.float32)
+    assert lib.t2sp_b200_sgemm(b"N", b"N", m, n, k, 1.0, a.ctypes.data, 0, b.ctypes.data, 0, 0.0, c.ctypes.data, ldc) == 0
+    assert np.isnan(c[:, n:]).all()
+    assert not np.isnan(c[:, :n]).any()
+    assert normwise(c[:, :n], a.astype(np.float64) @ b.astype(np.float64)) <= TOL_FP32
+
+
+def test_host_column_slab_output_leaves_other_columns_alone(lib):
+    """C given as a column slab of a wider host matrix (row pitch = the full width), as a column-sharded
+    caller passes it: the other slabs' columns must not be touched."""
+    import t2sp_b200
+    from t2sp_b200 import Buffer
+    M, K, NT, c0, cols = 256, 128, 640, 256, 128
+    A, B = O.to_bf16(O.uniform(22, 1, (M, K))), O.to_bf16(O.uniform(22, 2, (K, NT)))
+    C = np.full((M, NT), np.nan, np.float32)
+    a = Buffer.from_numpy(A, dtype="bf16")
+    b = Buffer((cols, K), "bf16", host=B.ctypes.data + 2 * c0, strides=(1, NT), keepalive=B)
+    c = Buffer((cols, M), "f32", host=C.ctypes.data + 4 * c0, strides=(1, NT), keepalive=C)
+    assert t2sp_b200.gemm(a, b, c) == 0
+    assert np.isnan(C[:, :c0]).all() and np.isnan(C[:, c0 + cols:]).all()
+    ref = O.gemm_h16(A, np.ascontiguousarray(B[:, c0:c0 + cols]), 0, acc64=True)
+    assert normwise(C[:, c0:c0 + cols], ref) <= 1e-5
+
+
+def test_empty_contraction_zeroes_only_the_region(lib):
+    """K == 0: C becomes zero inside its extents; a device-resident C with padded rows keeps its padding."""
+    import torch
+    import t2sp_b200
+    from t2sp_b200 import Buffer
+    M, N, ld = 64, 48, 80
+    t = torch.full((M, ld), float("nan"), dtype=torch.float32, device="cuda")
+    a = Buffer((0, M), "f32", host=None)
+    b = Buffer((N, 0), "f32", host=None)
+    c = Buffer((N, M), "f32", strides=(1, ld))
+    za = torch.zeros(16, device="cuda")
+    for x, ptr in ((a, za.data_ptr()), (b, za.data_ptr()), (c, t.data_ptr())):
+        assert t2sp_b200.wrap_device(x, ptr) == 0
+    torch.cuda.synchronize()
+    assert t2sp_b200.gemm(a, b, c) == 0
+    assert lib.t2sp_b200_sync() == 0
+    out = t.cpu().numpy()
+    assert np.all(out[:, :N] == 0) and np.isnan(out[:, N:]).all()
+
+
+def test_two_threads_on_their_own_streams(lib):
+    """Each host thread has its own stream, timing events and status word, and cached device blocks are
+    ordered by events when they change streams: two threads, one on a stream it set itself and one on
+    the library's per-thread stream, run host-buffer calls of different sizes at once (scratch, staging
+    and split-K blocks keep moving between the two streams through the cache)."""
+    import threading
+    import torch
+    import t2sp_b200
+    errors = []
+
+    def work(seed, own_stream, shapes):
+        try:
+            lib.t2sp_b200_set_device(0)
+            stream = torch.cuda.Stream() if own_stream else None
+            if stream is not None:
+                lib.t2sp_b200_set_stream(ctypes.c_void_p(stream.cuda_stream))
+            for it in range(6):
+                M, N, K = shapes[it % len(shapes)]
+                A, B = O.uniform(seed + it, 1, (M, K)), O.uniform(seed + it, 2, (K, N))
+                rc, C = call_gemm(A, B, "f32")
+                err = normwise(C, A.astype(np.float64) @ B.astype(np.float64)) if rc == 0 else None
+                if rc != 0 or err > TOL_FP32:
+                    errors.append((seed, it, rc, err))
+            if stream is not None:
+                lib.t2sp_b200_set_stream(None)
+        except Exception as e:  # surfaced by the assertion below
+            errors.append((seed, repr(e)))
+
+    import ctypes
+    shapes_a = [(1024, 1024, 1024), (384, 320, 520), (512, 512, 2048)]
+    shapes_b = [(512, 512, 2048), (1024, 1024, 1024), (200, 136, 72)]
+    threads = [threading.Thread(target=work, args=(50, True, shapes_a)), threading.Thread(target=work, args=(60, False, shapes_b))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+
+
+def test_bounded_wait_runs_out_and_the_library_stays_usable(lib):
+    """A wait inside a kernel that can never be satisfied ends by itself: the producer of a small
+    single-tile GEMM leaves out one k-block's copies (a test hook), the tensor-core warp's wait on that
+    stage runs out after the shortened limit, every role leaves its loop, the CTA frees its tensor memory
+    and returns, and the host reports halide_error_code_device_run_failed. The next call works."""
+    A = O.to_bf16(O.uniform(23, 1, (128, 512)))
+    B = O.to_bf16(O.uniform(23, 2, (512, 128)))
+    with library_env(T2SP_B200_WAIT_CYCLES="20000000", T2SP_B200_TEST_SKIP_STAGE="3"):
+        rc, _ = call_gemm(A, B, "bf16")
+    assert rc == -23
+    rc, C = call_gemm(A, B, "bf16")
+    assert rc == 0
+    assert normwise(C, O.gemm_h16(A, B, 0, acc64=True)) <= 1e-5

@@ -1,7 +1,8 @@
 """Two ranks on two GPUs (skipped on a one-GPU box): every rank runs its shard of a GEMM (columns of B
-and C, A replicated) and of an MTTKRP (a range of the contraction index k) through the C ABI on its own
-device, with device-resident buffers; the column slabs are gathered and the MTTKRP partials summed in
-rank order over NCCL. No data-path collective is involved in the contractions themselves."""
+and C, A replicated), of an MTTKRP (a range of the contraction index k) and of a convolution (batch
+items) through the library's sharded C entries on its own device; the column slabs are gathered and the
+MTTKRP partials summed in rank order by the library's NCCL entries (t2sp_b200_gather_columns,
+t2sp_b200_reduce_partials). No data-path collective is involved in the contractions themselves."""
 import os
 import socket
 import sys
@@ -37,34 +38,49 @@ def _worker(rank, world, port, q):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         dev = torch.device("cuda", rank)
-        # ---- GEMM: bf16, N not divisible by 256 * world
+        comm = shard.Comm(rank, world, shard.torch_id_exchange(dist, dev))   # the library's own NCCL communicator
+        # ---- GEMM: bf16, N not divisible by 256 * world; full-size device buffers, the entry takes its columns
         M, N, K = 1024, 1280, 512
         A, B = O.to_bf16(O.uniform(51, 1, (M, K))), O.to_bf16(O.uniform(51, 2, (K, N)))
         dA = torch.from_numpy(A.view(np.int16)).to(dev)
         dB = torch.from_numpy(B.view(np.int16)).to(dev)
         dC = torch.full((M, N), float("nan"), dtype=torch.float32, device=dev)
-        a = Buffer((K, M), "bf16")
-        t2sp_b200.wrap_device(a, dA.data_ptr())
-        _, b, c, (lo, hi) = shard.gemm_shard(a, dB.data_ptr(), dC.data_ptr(), "bf16", "f32", M, N, K, world, rank,
-                                             on_device=True)
-        assert t2sp_b200.gemm(a, b, c) == 0
+        a, b, c = Buffer((K, M), "bf16"), Buffer((N, K), "bf16"), Buffer((N, M), "f32")
+        for buf, t in ((a, dA), (b, dB), (c, dC)):
+            t2sp_b200.wrap_device(buf, t.data_ptr())
+        assert shard.gemm_shard(a, b, c, rank, world) == 0
         torch.cuda.synchronize()
-        full = shard.gather_columns(dC[:, lo:hi].contiguous(), N, dist).cpu().numpy()
+        lo, hi = shard.split_range(N, world, rank)
+        untouched = bool(torch.isnan(dC[:, :lo]).all().item() and torch.isnan(dC[:, hi:]).all().item())
+        assert comm.gather_columns(c) == 0                                   # ncclAllGather of the column slabs
+        full = dC.cpu().numpy()
         truth = O.bf16_to_f32(A).astype(np.float64) @ O.bf16_to_f32(B).astype(np.float64)
         err_gemm = float(np.max(np.abs(full - truth)) / np.max(np.abs(truth)))
-        untouched = bool(torch.isnan(dC[:, :lo]).all().item() and torch.isnan(dC[:, hi:]).all().item())
-        # ---- MTTKRP: this rank's range of k, partials added in rank order
+        # ---- MTTKRP: this rank's range of k from the full-size operands, partials added in rank order
         L, I, Kd, R = 128, 256, 48, 64
         at, bt, ct = O.uniform(52, 1, (Kd, I, L)), O.uniform(52, 2, (R, Kd)), O.uniform(52, 3, (R, L))
-        k0, k1 = shard.split_range(Kd, world, rank)
-        part = np.full((R, I), np.nan, np.float32)
-        pb = Buffer.from_numpy(part)
-        assert t2sp_b200.mttkrp(Buffer.from_numpy(np.ascontiguousarray(at[k0:k1])),
-                                Buffer.from_numpy(np.ascontiguousarray(bt[:, k0:k1])), Buffer.from_numpy(ct), pb) == 0
-        total = shard.reduce_partials(torch.from_numpy(pb.keepalive).to(dev), dist, ordered=True).cpu().numpy()
+        dD = torch.full((R, I), float("nan"), dtype=torch.float32, device=dev)
+        d = Buffer((I, R), "f32")
+        t2sp_b200.wrap_device(d, dD.data_ptr())
+        assert shard.mttkrp_shard(Buffer.from_numpy(at), Buffer.from_numpy(bt), Buffer.from_numpy(ct), d, rank, world) == 0
+        assert comm.reduce_partials(d, ordered=True) == 0
+        total = dD.cpu().numpy()
         ref = O.mttkrp_f32(at, bt, ct, acc64=True)
         err_mttkrp = float(np.max(np.abs(total - ref)) / np.max(np.abs(ref)))
-        q.put((rank, err_gemm, untouched, err_mttkrp, (lo, hi)))
+        # ---- conv by batch items on host buffers: each rank fills its images of the full-size output
+        Nb, CI, CO, KY, KX, OY, OX = 6, 64, 64, 3, 3, 6, 6
+        IY, IX = OY + KY - 1, OX + KX - 1
+        I2, K2 = O.uniform(53, 1, (IY * IX, CI * Nb)), O.uniform(53, 2, (CI * KY, CO * KX))
+        O2 = np.zeros((OY * OX, CO * Nb), np.float32)
+        cd = t2sp_b200.ConvDesc()
+        cd.CI, cd.CO, cd.KY, cd.KX, cd.OY, cd.OX = CI, CO, KY, KX, OY, OX
+        assert shard.conv_shard(Buffer.from_numpy(I2), Buffer.from_numpy(K2), Buffer.from_numpy(O2), cd, rank, world) == 0
+        parts = [None] * world
+        dist.all_gather_object(parts, O2)
+        refc = O.conv_f32(I2, K2, Nb, CI, CO, KY, KX, OY, OX, acc64=True)
+        err_conv = float(np.max(np.abs(sum(parts) - refc)) / np.max(np.abs(refc)))
+        comm.destroy()
+        q.put((rank, err_gemm, untouched, err_mttkrp, (lo, hi), err_conv))
     finally:
         dist.destroy_process_group()
 
@@ -86,6 +102,6 @@ def test_two_gpus_sharded_gemm_and_mttkrp():
         assert p.exitcode == 0
     results.sort()
     print(results)
-    for rank, err_gemm, untouched, err_mttkrp, _ in results:
-        assert err_gemm <= 1e-2 and untouched and err_mttkrp <= 1e-5, results
+    for rank, err_gemm, untouched, err_mttkrp, _, err_conv in results:
+        assert err_gemm <= 1e-2 and untouched and err_mttkrp <= 1e-5 and err_conv <= 1e-5, results
     assert results[0][4] == (0, 640) and results[1][4] == (640, 1280)

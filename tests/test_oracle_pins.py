@@ -1,6 +1,8 @@
 """The CPU oracle against everything that pins it (no GPU needed):
  - the reference's own, unmodified host drivers, linked against the oracle exposed under the
    interface symbols (oracle/ref_interface.cpp); they need the mounted reference tree to build;
+ - the golden loops of the reference's test helper for TTM and MTTKRP (correctness/util/util.h:428-441,
+   464-481), compiled unmodified into oracle/_ref/pin_contractions, which must give the oracle's bits;
  - the reference's deterministic fixtures evaluated exactly (tests/golden/kat.npz);
  - independent numpy formulations of conv and capsule."""
 import os
@@ -12,12 +14,12 @@ import pytest
 from tests import oracle_lib as O
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = "/root/reference"
+REF = os.environ.get("T2SP_REFERENCE", "/root/reference")
 KAT = np.load(os.path.join(ROOT, "tests", "golden", "kat.npz"))
 
 
 @pytest.mark.parametrize("name", ["pin_gemm_tiny", "pin_conv_tiny", "pin_capsule_tiny", "pin_aot_gemm", "pin_syrk_tiny", "pin_ger_tiny",
-                                  "pin_oneapi_conv_tiny", "pin_oneapi_capsule_tiny"])
+                                  "pin_oneapi_conv_tiny", "pin_oneapi_capsule_tiny", "pin_contractions"])
 def test_reference_driver_accepts_oracle(name):
     exe = os.path.join(ROOT, "oracle", "_ref", name)
     if not os.path.exists(exe):

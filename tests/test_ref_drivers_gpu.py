@@ -14,7 +14,7 @@ import pytest
 
 import t2sp_b200
 from t2sp_b200 import Buffer
-from tests.util import call_gemm
+from tests.util import call_gemm, library_env
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -46,6 +46,37 @@ def test_unmodified_gpu_flow_driver(lib, name, tmp_path):
     res = subprocess.run([exe], capture_output=True, text=True, timeout=600, cwd=str(tmp_path))
     assert res.returncode == 0, (res.stdout[-300:], res.stderr[-500:])
     assert res.stdout.strip().splitlines()[-1].startswith("Pass")
+
+
+def test_runtime_buffer_class_through_the_device_interface(lib, tmp_path):
+    """tests/drivers/runtime_buffer_flow.cpp: a caller that holds Halide::Runtime::Buffer objects, as the
+    reference's hosts do. The class calls through buffer.device_interface (copy_to_host, crops, slices,
+    device_free in the destructor: HalideBuffer.h:229-252,388,418,1615), so the interface must be the
+    real 15-entry function table of HalideRuntime.h:713-738."""
+    exe = os.path.join(ROOT, "tests", "_bin", "runtime_buffer_flow")
+    if not os.path.exists(exe):
+        pytest.skip("driver binary not built (needs the reference tree's HalideBuffer.h at build time)")
+    res = subprocess.run([exe], capture_output=True, text=True, timeout=300, cwd=str(tmp_path))
+    assert res.returncode == 0, (res.stdout[-600:], res.stderr[-500:])
+    assert res.stdout.strip().splitlines()[-1].startswith("Success")
+
+
+@pytest.mark.parametrize("name", ["gemm_large_a10", "conv_large_a10", "capsule_large_a10"])
+def test_large_mode_driver_reports_throughput_and_roofline(lib, name, tmp_path):
+    """The reference's drivers in performance mode (no -DTINY: A10 design constants, e.g. a
+    10240 x 8192 x 16384 GEMM): after the run they read exec_time.txt back through ExecTime(), print a
+    GFlops line and call roofline(), which writes roofline.png (gemm-run-fpga.cpp:88-108); here those
+    helpers are csrc/roofline_shim.cpp."""
+    exe = os.path.join(ROOT, "tests", "_bin", name)
+    if not os.path.exists(exe):
+        pytest.skip("driver binary not built (needs the reference tree at build time)")
+    env = dict(os.environ, BITSTREAM=str(tmp_path / "a.aocx"))
+    res = subprocess.run([exe], capture_output=True, text=True, timeout=900, cwd=str(tmp_path), env=env)
+    assert res.returncode == 0, (res.stdout[-600:], res.stderr[-500:])
+    assert "GFlops" in res.stdout, res.stdout[-600:]
+    png = tmp_path / "roofline.png"
+    assert png.exists() and png.stat().st_size > 100 and png.read_bytes()[:8] == b"\x89PNG\r\n\x1a\n"
+    assert (tmp_path / "exec_time.txt").exists()
 
 
 def test_golden_aot_gemm_fixture(lib):
@@ -84,11 +115,8 @@ def test_device_resident_buffers_and_exec_time(lib, tmp_path):
     for x in (a, b):
         assert lib.t2sp_b200_copy_to_device(x.ptr) == 0
     assert lib.t2sp_b200_device_malloc(c.ptr) == 0
-    os.environ["T2SP_B200_EXEC_TIME_FILE"] = str(tmp_path / "exec_time.txt")
-    try:
+    with library_env(T2SP_B200_EXEC_TIME_FILE=str(tmp_path / "exec_time.txt")):
         assert t2sp_b200.gemm(a, b, c) == 0
-    finally:
-        del os.environ["T2SP_B200_EXEC_TIME_FILE"]
     assert c.raw.flags & 2 and not np.any(C)              # device_dirty set, host copy untouched
     assert lib.t2sp_b200_copy_to_host(c.ptr) == 0
     assert np.array_equal(c.keepalive, (A.astype(np.float64) @ B.astype(np.float64)).astype(np.float32))
@@ -102,11 +130,8 @@ def test_device_resident_buffers_and_exec_time(lib, tmp_path):
 def test_injected_allocation_failure_is_an_error_code(lib):
     A = np.ones((512, 512), np.float32)
     C = np.zeros((512, 512), np.float32)
-    os.environ["T2SP_B200_FAIL_ALLOC_ABOVE"] = "1"
-    try:
+    with library_env(T2SP_B200_FAIL_ALLOC_ABOVE="1"):
         rc = t2sp_b200.gemm(Buffer.from_numpy(A), Buffer.from_numpy(A), Buffer.from_numpy(C))
-    finally:
-        del os.environ["T2SP_B200_FAIL_ALLOC_ABOVE"]
     assert rc == -16                                       # halide_error_code_device_malloc_failed
     rc = t2sp_b200.gemm(Buffer.from_numpy(A), Buffer.from_numpy(A), Buffer.from_numpy(C))
     assert rc == 0                                         # the library stays usable

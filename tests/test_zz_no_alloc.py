@@ -51,6 +51,22 @@ def test_no_alloc_matches_regular_entry_twice(lib):
         assert normwise(got, O.mttkrp_f32(a, b, c, acc64=True)) <= TOL_FP32
 
 
+def test_no_alloc_padded_output_pitch(lib):
+    """d_stride_r > I: the columns of d are I + 12 elements apart; what lies between them is the caller's."""
+    import torch
+    L, I, K, R, pad = 96, 200, 17, 40, 12
+    a, b, c = O.uniform(6, 1, (K, I, L)), O.uniform(6, 2, (R, K)), O.uniform(6, 3, (R, L))
+    ta, tb, tc = (torch.from_numpy(x).cuda() for x in (a, b, c))
+    td = torch.full((R, I + pad), float("nan"), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    rc = lib.t2sp_b200_mttkrp_noalloc(ta.data_ptr(), L, L * I, tb.data_ptr(), K, tc.data_ptr(), L, td.data_ptr(), I + pad,
+                                      L, I, K, R, None, 1)
+    assert rc == 0
+    got = td.cpu().numpy()
+    assert np.isnan(got[:, I:]).all() and not np.isnan(got[:, :I]).any()
+    assert normwise(got[:, :I], O.mttkrp_f32(a, b, c, acc64=True)) <= TOL_FP32
+
+
 def test_no_alloc_rejects_oversized_problem(lib):
     # one partial slab of 4*I*R bytes beyond the 16 MiB array: refused before anything is launched
     I, R = 40000, 128

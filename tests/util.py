@@ -1,4 +1,7 @@
 """Shared helpers for the parity tests: the error metric and C-ABI call wrappers."""
+import contextlib
+import os
+
 import numpy as np
 
 import t2sp_b200
@@ -45,3 +48,24 @@ def call_gemm(A, B, dtype_in, out_dtype=np.float32, tiled=None):
         c = Buffer.from_numpy(C)
         rc = t2sp_b200.gemm(a, b, c)
     return rc, c.keepalive
+
+
+@contextlib.contextmanager
+def library_env(**values):
+    """Sets T2SP_B200_* variables for the duration of a block. The library reads its environment
+    once, so it is told to read it again on the way in and on the way out."""
+    L = t2sp_b200.lib()
+    L.t2sp_b200_reload_env.restype = None
+    old = {k: os.environ.get(k) for k in values}
+    try:
+        for k, v in values.items():
+            os.environ[k] = str(v)
+        L.t2sp_b200_reload_env()
+        yield
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+        L.t2sp_b200_reload_env()
