@@ -1234,6 +1234,66 @@ int mttkrp_launch(const char* who, float* pa, int64_t lda1, int64_t lda2, const 
     return 0;
 }
 
+// The accumulate-then-scale kernel (umma_mttkrp.cuh), for R <= 64: work items are (row tile, up to 4 l-blocks,
+// up to 64 k values); as many k-ranges as fill the SMs once. `want_slabs` > 0 asks for about that many partial
+// slabs instead (tests). Returns the number of partial slabs (l-ranges x k-ranges).
+int mttkrp2_plan(int L, int I, int Kd, int want_slabs, CoreParams* p) {
+    const int lblks = (L + 31) / 32, tiles_m = (I + kBlockM - 1) / kBlockM;
+    const int lb_per = std::min(4, lblks), lranges = (lblks + lb_per - 1) / lb_per;
+    int kranges = want_slabs > 0 ? std::max(1, (want_slabs + lranges / 2) / lranges)
+                                 : std::max(1, core_sm_count() / std::max(1, tiles_m * lranges));
+    kranges = std::max(1, std::min(kranges, Kd));
+    int k_per = std::min(64, (Kd + kranges - 1) / kranges);
+    kranges = (Kd + k_per - 1) / k_per;
+    p->tiles_m = tiles_m; p->lblks = lblks;
+    p->mt_lb_per = lb_per; p->mt_lranges = lranges; p->mt_k_per = k_per; p->mt_kranges = kranges;
+    return lranges * kranges;
+}
+
+int mttkrp2_run(const char* who, float* pa, int64_t lda1, int64_t lda2, const float* pb, int64_t ldb, const float* pc,
+                int64_t ldc, float* pd, int64_t ldd, int L, int I, int Kd, int R, int want_slabs, bool sync_after,
+                bool single_pass) {
+    if (!tma_ok(pa, {lda1 * 4, lda2 * 4})) return tma_unsupported("a");
+    if (!tma_ok(pc, {ldc * 4})) return tma_unsupported("c");
+    CoreParams p;
+    memset(&p, 0, sizeof(p));
+    const int slabs = mttkrp2_plan(L, I, Kd, want_slabs, &p);
+    {
+        uint64_t dims[3] = {uint64_t(L), uint64_t(I), uint64_t(Kd)};
+        uint64_t str[3] = {4, uint64_t(lda1) * 4, uint64_t(lda2) * 4};
+        uint32_t box[3] = {32, uint32_t(kBlockM), 1};
+        if (!rt_encode_tmap(&p.mapA[0], CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, pa, dims, str, box)) return tma_unsupported("a");
+    }
+    {
+        // factor c(l, r): one box = 32 consecutive l of 64 columns r (columns beyond R read as zero), a K-major B tile
+        uint64_t dims[2] = {uint64_t(L), uint64_t(R)};
+        uint64_t str[2] = {4, uint64_t(ldc) * 4};
+        uint32_t box[2] = {32, 64};
+        if (!rt_encode_tmap(&p.mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(pc), dims, str, box)) return tma_unsupported("c");
+    }
+    float* scratch = static_cast<float*>(rt_alloc(size_t(slabs) * I * R * sizeof(float)));
+    if (!scratch) return halide_error_code_device_malloc_failed;
+    p.M = I; p.N = R; p.R = R; p.L = L; p.Kdim = Kd;
+    p.fb = pb; p.ldfb = ldb;
+    p.out = scratch;
+    p.single_pass = single_pass;
+    p.status = rt_status_word();
+    p.wait_cycles = rt_env().wait_cycles;
+    cudaStream_t s = rt_stream();
+    const int items = p.tiles_m * slabs;
+    if (sync_after) cudaEventRecord(rt_event(0), s);
+    cudaError_t e = mttkrp2_launch(p, std::max(1, std::min(items, core_sm_count())), s);
+    if (e == cudaSuccess) e = reduce_partials_launch(scratch, pd, I, R, ldd, slabs, s);
+    rt_free(scratch);  // whoever takes the block over on another stream waits for this stream's work so far
+    if (e != cudaSuccess) {
+        fprintf(stderr, "t2sp_b200: %s: kernel launch failed: %s\n", who, cudaGetErrorString(e));
+        return halide_error_code_device_run_failed;
+    }
+    rt_count_launch(2);
+    if (sync_after) cudaEventRecord(rt_event(1), s);
+    return 0;
+}
+
 // Split plan: enough (row tile, split) pairs to give every SM one CTA, never an empty split.
 void mttkrp_plan(int L, int I, int Kd, int want_splits, int* splits, int* num_kb) {
     const int total_kb = ((L + 31) / 32) * Kd;
@@ -1301,6 +1361,13 @@ extern "C" int t2sp_b200_mttkrp(halide_buffer_t* a, halide_buffer_t* b, halide_b
         rt_zero_region(d, vw.v[3].ptr);
     } else {
         const int prec = resolve_precision(desc ? desc->precision : 0);
+        if (R <= 64 && !rt_env().mttkrp_v1) {
+            if (int rc = mttkrp2_run("mttkrp", pa, a->dim[1].stride, a->dim[2].stride, pb, b->dim[1].stride, pc, c->dim[1].stride, pd,
+                                     d->dim[1].stride, L, I, Kd, R, desc ? desc->splits : 0, sync_after, prec == T2SP_PRECISION_TF32))
+                return rc;
+            if (int e = rt_finish_output(d, "d", &vw.v[3])) return e;
+            return finish_call("mttkrp", "kernel_unloader", sync_after);
+        }
         int splits = 0, num_kb = 0;
         mttkrp_plan(L, I, Kd, desc ? desc->splits : 0, &splits, &num_kb);
         float* scratch = static_cast<float*>(rt_alloc(size_t(splits) * I * R * sizeof(float)));

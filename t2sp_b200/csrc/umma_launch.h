@@ -28,6 +28,10 @@ cudaError_t pair2_launch(int arith, int op, const CoreParams& p, int grid, cudaS
 // p.idesc describes a 256 x un TF32 MMA.
 cudaError_t x3pair_launch(int op, int un, const CoreParams& p, int grid, cudaStream_t stream);
 
+// Launches the accumulate-then-scale MTTKRP kernel (umma_mttkrp.cuh; R <= 64) with `grid` persistent CTAs over the
+// work items that p.tiles_m, p.mt_lranges and p.mt_kranges describe; partial slabs go to p.out.
+cudaError_t mttkrp2_launch(const CoreParams& p, int grid, cudaStream_t stream);
+
 // dst[z][c][r] = src[z][r][c] for `batch` rows x cols matrices of 32-bit elements (pitches and batch
 // strides in elements; batch <= 65535).
 cudaError_t transpose32_launch(const void* src, long long ld_src, void* dst, long long ld_dst, int rows, int cols,

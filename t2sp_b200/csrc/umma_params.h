@@ -1,6 +1,7 @@
 // Parameter block shared by the host lowering code and the contraction kernel.
 #pragma once
 #include <cuda.h>
+#include <cuda_runtime.h>
 #include <stdint.h>
 
 namespace t2sp {
@@ -37,7 +38,7 @@ struct Digits {
 //   [4,6) D format (0 f16, 1 f32, 2 s32)   [7,10) A format   [10,13) B format
 //   (f16 kind: 0 f16, 1 bf16; tf32 kind: 2; i8 kind: 0 u8, 1 s8)
 //   [15] A is MN-major   [16] B is MN-major   [17,23) N>>3   [24,29) M>>4
-constexpr uint32_t make_instr_desc(uint32_t d_fmt, uint32_t ab_fmt, bool a_mn_major, bool b_mn_major, uint32_t m,
+__host__ __device__ constexpr uint32_t make_instr_desc(uint32_t d_fmt, uint32_t ab_fmt, bool a_mn_major, bool b_mn_major, uint32_t m,
                                    uint32_t n) {
     return (d_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | (uint32_t(a_mn_major) << 15) |
            (uint32_t(b_mn_major) << 16) | ((n >> 3) << 17) | ((m >> 4) << 24);
@@ -82,6 +83,9 @@ struct CoreParams {
     const float* fb;  // b(k,r), k fastest, column pitch ldfb
     long long ldfc, ldfb;
     int L, Kdim, R;
+    // MTTKRP, accumulate-then-scale kernel: work item = (row tile, range of l-blocks, range of k)
+    int mt_lb_per, mt_lranges;  // l-blocks per l-range (at most 4), number of l-ranges
+    int mt_k_per, mt_kranges;   // k values per k-range (at most 64), number of k-ranges
     int slab_rows;    // fp32 pair kernel, splits > 1: rows between the partial tiles of successive k-ranges
     int use_ab;       // EPI_ROWMAJOR, fp32: out = alpha * acc + beta * out
     float alpha, beta;
