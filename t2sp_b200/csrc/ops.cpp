@@ -1281,6 +1281,16 @@ int mttkrp2_run(const char* who, float* pa, int64_t lda1, int64_t lda2, const fl
     p.wait_cycles = rt_env().wait_cycles;
     cudaStream_t s = rt_stream();
     const int items = p.tiles_m * slabs;
+#ifdef T2SP_DEBUG_KNOBS
+    static long long* trace_dev = nullptr;
+    const char* trace_path = getenv("T2SP_B200_TRACE");
+    if (trace_path) {
+        if (!trace_dev) cudaMalloc(&trace_dev, 48 * 1024 * sizeof(long long));
+        cudaMemsetAsync(trace_dev, 0, 48 * 1024 * sizeof(long long), s);
+        p.trace = trace_dev;
+    }
+    if (const char* kn = getenv("T2SP_B200_KNOBS")) p.knobs = atoi(kn);
+#endif
     if (sync_after) cudaEventRecord(rt_event(0), s);
     cudaError_t e = mttkrp2_launch(p, std::max(1, std::min(items, core_sm_count())), s);
     if (e == cudaSuccess) e = reduce_partials_launch(scratch, pd, I, R, ldd, slabs, s);
@@ -1291,6 +1301,16 @@ int mttkrp2_run(const char* who, float* pa, int64_t lda1, int64_t lda2, const fl
     }
     rt_count_launch(2);
     if (sync_after) cudaEventRecord(rt_event(1), s);
+#ifdef T2SP_DEBUG_KNOBS
+    static int trace_calls = 0;
+    const char* trace_at = getenv("T2SP_B200_TRACE_AT");
+    if (trace_path && (!trace_at || ++trace_calls == atoi(trace_at))) {
+        std::vector<long long> host(48 * 1024);
+        cudaStreamSynchronize(s);
+        cudaMemcpy(host.data(), trace_dev, host.size() * sizeof(long long), cudaMemcpyDeviceToHost);
+        if (FILE* f = fopen(trace_path, "wb")) { fwrite(host.data(), sizeof(long long), host.size(), f); fclose(f); }
+    }
+#endif
     return 0;
 }
 

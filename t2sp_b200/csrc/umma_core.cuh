@@ -350,7 +350,7 @@ umma_contract_kernel(const __grid_constant__ CoreParams p) {
                 for (int s = 0; s < STAGES; ++s) {
                     const int last = it - 1 - ((it - 1 - s) % STAGES + STAGES) % STAGES;
                     if (last >= 0) {
-                        for (int spin = 0; spin < 100000; ++spin)
+                        for (int spin = 0; spin < 4000; ++spin)
                             if (ptx::mbar_try_wait(&full_bar[s], (last / STAGES) & 1)) break;
                     }
                 }

@@ -21,8 +21,9 @@
 // truncating adds stay far below the 1e-5 tolerance); the sum over k runs in fp32 registers, rounded
 // to nearest.
 //
-// The A operand of all MMAs is in tensor memory: eight split warps read each raw tile of a once and
-// write hi (fp32), bf16(a) and bf16(lo) into one of four 64-column A slots with tcgen05.st.
+// The A operand of all MMAs is in tensor memory: split warps read each raw tile of a once and write hi
+// (fp32), bf16(a) and bf16(lo) into one of four 64-column A slots with tcgen05.st; two groups of four
+// warps take the k-blocks in turn.
 // Every mbarrier wait is bounded as in the other kernels.
 #pragma once
 #include <cuda_bf16.h>
@@ -48,7 +49,8 @@ struct Mttkrp2Cfg {
     static constexpr int kAccBufs = 4, kASlots = 4;
     static constexpr int kATmemCol0 = kAccBufs * kBN;             // A slots behind the accumulators
     static constexpr int kTmemCols = 512;
-    static constexpr int kNumBars = 2 * kStages + 2 * kASlots + 2 * kAccBufs + 4;
+    static constexpr int kNumBars = 2 * kStages + 2 * kASlots + 2 * kAccBufs + 5;
+    static_assert(kStages % 2 == 0 && kASlots % 2 == 0, "the two split groups own the even and the odd stages / A slots");
     static constexpr int kSmemBytes = kStages * kABytes + kCF32Bytes + 2 * kCB16Bytes + kBvalBytes + kNumBars * 8 + 16 + 1024;
     static_assert(kAccBufs * kBN + kASlots * 64 <= kTmemCols, "accumulators and A slots must fit tensor memory");
     static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
@@ -79,11 +81,18 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
     uint64_t* cfree_bar = cfull_bar + 1;                 // the item's MMAs retired: c may be replaced
     uint64_t* bready_bar = cfree_bar + 1;                // the item's values of b are staged (one arrival per drain warp)
     uint64_t* bdone_bar = bready_bar + 1;                // every drain warp is done with them
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bdone_bar + 1);
+    uint64_t* cconv_bar = bdone_bar + 1;                 // every split warp has converted its share of c
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cconv_bar + 1);
     uint32_t* abort_slot = tmem_slot + 1;
 
-    const int warp = threadIdx.x >> 5;
+    int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+#ifdef T2SP_DEBUG_KNOBS
+    const int knobs = p.knobs;
+    if ((knobs & 2) && warp < 2) warp ^= 1;  // variant: producer and MMA issuer trade warps (and scheduler partitions)
+#else
+    constexpr int knobs = 0;
+#endif
     const AbortCtx ab{abort_slot, p.status, p.wait_cycles > 0 ? p.wait_cycles : kWaitTimeoutCycles};
     const int slabs = p.mt_lranges * p.mt_kranges;
     const int num_items = p.tiles_m * slabs;
@@ -91,10 +100,10 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
             ptx::mbar_init(&full_bar[s], 1);
-            ptx::mbar_init(&empty_bar[s], Cfg::kSplitWarps);
+            ptx::mbar_init(&empty_bar[s], Cfg::kSplitWarps / 2);
         }
         for (int a = 0; a < Cfg::kASlots; ++a) {
-            ptx::mbar_init(&ready_bar[a], Cfg::kSplitWarps);
+            ptx::mbar_init(&ready_bar[a], Cfg::kSplitWarps / 2);
             ptx::mbar_init(&afree_bar[a], 1);
         }
         for (int a = 0; a < Cfg::kAccBufs; ++a) {
@@ -105,6 +114,7 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
         ptx::mbar_init(cfree_bar, 1);
         ptx::mbar_init(bready_bar, 4);
         ptx::mbar_init(bdone_bar, 4);
+        ptx::mbar_init(cconv_bar, Cfg::kSplitWarps);
         *abort_slot = 0u;
         ptx::fence_mbar_init();
     }
@@ -146,6 +156,7 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
                     for (int j = 0; j < lb_cnt; ++j, ++it) {
                         const int s = it % S;
                         if (!bounded_wait(&empty_bar[s], ((it / S) & 1) ^ 1, ab, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
+                        T2SP_TRACE(p, 0, it);
                         ptx::mbar_expect_tx(&full_bar[s], Cfg::kABytes);
                         ptx::tma_load_3d(smem + s * Cfg::kABytes, &p.mapA[0], &full_bar[s], (lb0 + j) * 32, mb * kBlockM, k0 + kc);
                     }
@@ -155,10 +166,10 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
                 for (int s = 0; s < S; ++s) {
                     const int last = it - 1 - ((it - 1 - s) % S + S) % S;
                     if (last >= 0)
-                        for (int spin = 0; spin < 100000; ++spin)
+                        for (int spin = 0; spin < 4000; ++spin)
                             if (ptx::mbar_try_wait(&full_bar[s], (last / S) & 1)) break;
                 }
-                for (int spin = 0; spin < 100000 && n > 0; ++spin)
+                for (int spin = 0; spin < 4000 && n > 0; ++spin)
                     if (ptx::mbar_try_wait(cfull_bar, (n - 1) & 1)) break;
             }
         }
@@ -168,6 +179,46 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
         const uint32_t idesc16 = make_instr_desc(1, 1, false, false, kBlockM, Cfg::kBN);
         int it = 0, g = 0;
         bool ok = true;
+        if (knobs & 1) {
+            // variant: one thread issues everything, the other lanes leave
+            if (lane == 0) {
+                for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x) {
+                    int mb, slab, lb0, lb_cnt, k0, k_cnt;
+                    decode(t, mb, slab, lb0, lb_cnt, k0, k_cnt);
+                    for (int kc = 0; kc < k_cnt && ok; ++kc, ++g) {
+                        const int acc = g % Cfg::kAccBufs;
+                        if (!bounded_wait(&tempty_bar[acc], ((g / Cfg::kAccBufs) & 1) ^ 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
+                        ptx::tc_fence_after_sync();
+                        const uint32_t d_tmem = tmem_base + acc * Cfg::kBN;
+                        for (int j = 0; j < lb_cnt; ++j, ++it) {
+                            const int ls = it % Cfg::kASlots;
+                            if (!bounded_wait(&ready_bar[ls], (it / Cfg::kASlots) & 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
+                            ptx::tc_fence_after_sync();
+                            T2SP_TRACE(p, 3, it);
+                            const uint32_t a_hi = tmem_base + Cfg::kATmemCol0 + ls * 64, a_hb = a_hi + 32, a_lb = a_hi + 48;
+                            const uint64_t db = ptx::make_smem_desc(ptx::smem_u32(c_f32 + j * Cfg::kCTile), 16, 1024);
+                            const uint32_t off16 = (j >> 1) * Cfg::kCTile + (j & 1) * 64;
+                            const uint64_t dhb = ptx::make_smem_desc(ptx::smem_u32(c_hb + off16), 16, 1024);
+                            const uint64_t dlb = ptx::make_smem_desc(ptx::smem_u32(c_lb + off16), 16, 1024);
+#pragma unroll
+                            for (int jj = 0; jj < 4; ++jj)
+                                ptx::umma_a_tmem<ptx::KIND_TF32>(d_tmem, a_hi + 8 * jj, db + jj * 2, idesc32, (j | jj) ? 1u : 0u);
+                            if (!p.single_pass) {
+#pragma unroll
+                                for (int jj = 0; jj < 2; ++jj) {
+                                    ptx::umma_a_tmem<ptx::KIND_F16>(d_tmem, a_lb + 8 * jj, dhb + jj * 2, idesc16, 1u);
+                                    ptx::umma_a_tmem<ptx::KIND_F16>(d_tmem, a_hb + 8 * jj, dlb + jj * 2, idesc16, 1u);
+                                }
+                            }
+                            ptx::umma_commit(&afree_bar[ls]);
+                            T2SP_TRACE(p, 4, it);
+                        }
+                        if (ok) ptx::umma_commit(&tfull_bar[acc]);
+                    }
+                    if (ok) ptx::umma_commit(cfree_bar);
+                }
+            }
+        } else
         for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x) {
             int mb, slab, lb0, lb_cnt, k0, k_cnt;
             decode(t, mb, slab, lb0, lb_cnt, k0, k_cnt);
@@ -182,15 +233,17 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
                     // item) after they have converted c, so this wait covers both
                     if (!bounded_wait_warp(&ready_bar[ls], (it / Cfg::kASlots) & 1, ab, ST_TIMEOUT_MMA, lane)) { ok = false; break; }
                     ptx::tc_fence_after_sync();
+                    if (lane == 0) T2SP_TRACE(p, 3, it);
                     const uint32_t a_hi = tmem_base + Cfg::kATmemCol0 + ls * 64, a_hb = a_hi + 32, a_lb = a_hi + 48;
                     const uint64_t db = ptx::make_smem_desc(ptx::smem_u32(c_f32 + j * Cfg::kCTile), 16, 1024);
                     const uint32_t off16 = (j >> 1) * Cfg::kCTile + (j & 1) * 64;
                     const uint64_t dhb = ptx::make_smem_desc(ptx::smem_u32(c_hb + off16), 16, 1024);
                     const uint64_t dlb = ptx::make_smem_desc(ptx::smem_u32(c_lb + off16), 16, 1024);
+                    if (!(knobs & 8))
 #pragma unroll
                     for (int jj = 0; jj < 4; ++jj)
                         ptx::umma_tf32_a_tmem_warp(d_tmem, a_hi + 8 * jj, db + jj * 2, idesc32, (j | jj) ? 1u : 0u);
-                    if (!p.single_pass) {
+                    if (!p.single_pass && !(knobs & 12)) {
 #pragma unroll
                         for (int jj = 0; jj < 2; ++jj) {
                             ptx::umma_f16_a_tmem_warp(d_tmem, a_lb + 8 * jj, dhb + jj * 2, idesc16, 1u);
@@ -198,6 +251,7 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
                         }
                     }
                     ptx::umma_commit_warp(&afree_bar[ls]);
+                    if (lane == 0) T2SP_TRACE(p, 4, it);
                 }
                 if (ok) ptx::umma_commit_warp(&tfull_bar[acc]);
             }
@@ -227,6 +281,7 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
                 const int acc = g % Cfg::kAccBufs;
                 if (!bounded_wait_warp(&tfull_bar[acc], (g / Cfg::kAccBufs) & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
                 ptx::tc_fence_after_sync();
+                if (et == 0) T2SP_TRACE(p, 5, g);
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     uint32_t e[32];
@@ -249,6 +304,7 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
                 ptx::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&tempty_bar[acc]);
+                if (et == 0) T2SP_TRACE(p, 6, g);
             }
             if (!ok) break;
             __syncwarp();
@@ -263,10 +319,13 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
         }
     } else {
         // ------------------------------------------------------------ split warps: c once per item, then every tile of a into tensor memory
+        // Two groups of four warps (one warp per TMEM lane quarter) take the k-blocks in turn, so two tiles are
+        // being converted at any time: one warp's chain of waits, shared-memory loads, conversions and TMEM stores
+        // for a k-block is longer than the k-block period the memory system allows.
         const int sw = warp - 6;
         const int st = sw * 32 + lane;
-        const int q = warp & 3;   // TMEM lane quarter this warp may write
-        const int h = sw >> 2;    // which 16 of the tile's 32 l values this warp converts
+        const int q = warp & 3;    // TMEM lane quarter this warp may write
+        const int grp = sw >> 2;   // this warp's group takes the k-blocks with (it & 1) == grp
         const int row = q * 32 + lane;
         int it = 0, n = 0;
         bool ok = true;
@@ -288,38 +347,51 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
                 }
                 ptx::fence_proxy_async_smem();
             }
-            for (int kc = 0; kc < k_cnt && ok; ++kc)
-                for (int j = 0; j < lb_cnt; ++j, ++it) {
-                    const int s = it % S, ls = it % Cfg::kASlots;
-                    if (!bounded_wait_warp(&full_bar[s], (it / S) & 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
-                    if (!bounded_wait_warp(&afree_bar[ls], ((it / Cfg::kASlots) & 1) ^ 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
-                    ptx::tc_fence_after_sync();
-                    // this thread's tile row: 16-byte chunk c sits at c ^ (row & 7), which also spreads a warp's
-                    // reads over all banks
-                    const uint8_t* rp = smem + s * Cfg::kABytes + row * 128;
-                    uint32_t vh[16], vb[8], vl[8];
+            // every split warp has converted its share before any of them reports a tile of a as ready
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(cconv_bar);
+            if (!bounded_wait_warp(cconv_bar, n & 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
+            const int total = k_cnt * lb_cnt;
+            const int it_end = it + total;
+            for (int i = it + ((it & 1) != grp ? 1 : 0); i < it_end; i += 2) {
+                const int s = i % S, ls = i % Cfg::kASlots;
+                if (sw == 0 || sw == 4) T2SP_TRACE(p, 20 + grp, i >> 1);
+                if (!bounded_wait_warp(&full_bar[s], (i / S) & 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
+                if (st == 0) T2SP_TRACE(p, 1, i >> 1);
+                // This thread's tile row: 16-byte chunk c sits at c ^ (row & 7), which also spreads a warp's reads
+                // over all banks. The row is converted in registers and the stage handed back to the producer
+                // BEFORE the wait for a free A slot: at full memory bandwidth a copy takes about as long as eight
+                // k-blocks, so every stage has to be back in flight as soon as its data has been read.
+                const uint8_t* rp = smem + s * Cfg::kABytes + row * 128;
+                uint32_t vh[32], vb[16], vl[16];
 #pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) {
-                        const float4 v = *reinterpret_cast<const float4*>(rp + (((4 * h + cc) ^ (row & 7)) << 4));
-                        vh[4 * cc + 0] = __float_as_uint(v.x); vh[4 * cc + 1] = __float_as_uint(v.y);
-                        vh[4 * cc + 2] = __float_as_uint(v.z); vh[4 * cc + 3] = __float_as_uint(v.w);
-                        vb[2 * cc + 0] = pack_bf16(v.x, v.y); vb[2 * cc + 1] = pack_bf16(v.z, v.w);
-                        vl[2 * cc + 0] = pack_bf16(tf32_lo(v.x), tf32_lo(v.y)); vl[2 * cc + 1] = pack_bf16(tf32_lo(v.z), tf32_lo(v.w));
-                    }
-                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::kATmemCol0 + ls * 64;
-                    ptx::tmem_st_32x16(taddr + 16 * h, vh);
-                    if (!p.single_pass) {
-                        ptx::tmem_st_32x8(taddr + 32 + 8 * h, vb);
-                        ptx::tmem_st_32x8(taddr + 48 + 8 * h, vl);
-                    }
-                    ptx::tmem_st_wait();
-                    ptx::tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) {
-                        ptx::mbar_arrive(&ready_bar[ls]);
-                        ptx::mbar_arrive(&empty_bar[s]);  // the raw tile has been read: the producer may refill the stage
-                    }
+                for (int cc = 0; cc < 8; ++cc) {
+                    const float4 v = *reinterpret_cast<const float4*>(rp + ((cc ^ (row & 7)) << 4));
+                    vh[4 * cc + 0] = __float_as_uint(v.x); vh[4 * cc + 1] = __float_as_uint(v.y);
+                    vh[4 * cc + 2] = __float_as_uint(v.z); vh[4 * cc + 3] = __float_as_uint(v.w);
+                    vb[2 * cc + 0] = pack_bf16(v.x, v.y); vb[2 * cc + 1] = pack_bf16(v.z, v.w);
+                    vl[2 * cc + 0] = pack_bf16(tf32_lo(v.x), tf32_lo(v.y)); vl[2 * cc + 1] = pack_bf16(tf32_lo(v.z), tf32_lo(v.w));
                 }
+                // the conversions above consumed every loaded value, so the loads have completed
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&empty_bar[s]);
+                if (st == 0) T2SP_TRACE(p, 7, i >> 1);
+                if (!bounded_wait_warp(&afree_bar[ls], ((i / Cfg::kASlots) & 1) ^ 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
+                ptx::tc_fence_after_sync();
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + Cfg::kATmemCol0 + ls * 64;
+                ptx::tmem_st_32x32(taddr, vh);
+                if (!p.single_pass) {
+                    ptx::tmem_st_32x16(taddr + 32, vb);
+                    ptx::tmem_st_32x16(taddr + 48, vl);
+                }
+                if (st == 0) T2SP_TRACE(p, 9, i >> 1);
+                ptx::tmem_st_wait();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&ready_bar[ls]);
+                if (lane == 0) T2SP_TRACE(p, 10 + sw, i >> 1);
+            }
+            it = it_end;
         }
     }
 
