@@ -32,6 +32,8 @@ WORKLOADS = {
     # name: (kind, dims)
     "gemm_bf16_8192": ("gemm", dict(M=8192, N=8192, K=8192, dtype="bf16")),
     "gemm_bf16_4096": ("gemm", dict(M=4096, N=4096, K=4096, dtype="bf16")),
+    # what one of 8 GPUs computes of the 8192^3 problem when it is sharded by N-column slabs
+    "gemm_bf16_slab8": ("gemm", dict(M=8192, N=1024, K=8192, dtype="bf16")),
     "gemm_bf16_16384": ("gemm", dict(M=16384, N=16384, K=16384, dtype="bf16")),
     "gemm_i8_8192": ("gemm", dict(M=8192, N=8192, K=8192, dtype="i8")),
     "gemm_i8_4096": ("gemm", dict(M=4096, N=4096, K=4096, dtype="i8")),
@@ -492,7 +494,7 @@ def main():
         pk = peaks()
         extras["sustained"] = {"steps": n_sus, "ms_per_step": sus_ms, "value": sus_tf, "unit": "TFLOP/s",
                                "region_s": sus_total * 1e-3,
-                               "frac": (sus_tf / (pk["sustained"] * RATE[w.get("dtype", "f32")])) if kind == "gemm" else None,
+                               "frac": (sus_tf / world / (pk["sustained"] * RATE[w.get("dtype", "f32")])) if kind == "gemm" else None,
                                "peak_source": f"{pk['src']} cuBLAS bf16 sustained {pk['sustained']} TFLOP/s"}
         # ---- what the caller pays to have all of C on every GPU afterwards: NCCL all-gather of the column slabs
         if world > 1 and kind == "gemm":
