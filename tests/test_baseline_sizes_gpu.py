@@ -1,12 +1,13 @@
 """Parity at the full sizes of the published configurations (the other GPU tests run scaled-down
 shapes so that the CPU oracle finishes quickly):
 
- * GEMM 8192^3 and 16384^3: 64 random 64 x 64 output tiles each, recomputed on the CPU in fp64 from
+ * GEMM 8192^3 and 16384^3 (bf16 and int8): 64 random 64 x 64 output tiles each, recomputed on the CPU in fp64 from
    the K-length rows and columns they need (exact for the bf16 and int8 products); int8 bit-exact;
  * GEMM 4096^3: the whole matrix, against an fp64 BLAS product (exact for int8: |sum| < 2^53);
  * conv (64 x 256 x 14 x 14, 3x3), TTM (512.512.256 -> 256), MTTKRP (512^3, R = 64) and capsule
    (batch 32, 32 -> 32 channels, 4x4 poses, 16 x 16, 3x3, stride 1) at their full sizes, against
-   fp64 references (numpy BLAS for TTM / MTTKRP, the oracle's fp64-accumulated form for conv / capsule).
+   fp64 references (numpy BLAS for TTM / MTTKRP, the oracle's fp64-accumulated form for conv / capsule), in the
+   normwise form and element by element against sum |a||b| (the same reference run on the absolute values).
 """
 import numpy as np
 import pytest
@@ -14,7 +15,7 @@ import pytest
 import t2sp_b200
 from t2sp_b200 import Buffer, CapsuleDesc, ConvDesc
 from tests import oracle_lib as O
-from tests.util import TOL_BF16, TOL_FP32, call_gemm, normwise
+from tests.util import TOL_BF16, TOL_FP32, call_gemm, componentwise, normwise
 
 pytestmark = pytest.mark.gpu
 
@@ -30,7 +31,7 @@ def _as_f64(x, dtype):
     return x.astype(np.float64) if dtype == "i8" else O.bf16_to_f32(x).astype(np.float64)
 
 
-@pytest.mark.parametrize("dtype,n", [("bf16", 8192), ("i8", 8192), ("bf16", 16384)])
+@pytest.mark.parametrize("dtype,n", [("bf16", 8192), ("i8", 8192), ("bf16", 16384), ("i8", 16384)])
 def test_gemm_large_sampled_tiles(lib, dtype, n):
     A, B = _gemm_inputs(dtype, n, 31)
     rc, C = call_gemm(A, B, dtype, out_dtype=np.int32 if dtype == "i8" else np.float32)
@@ -79,6 +80,9 @@ def test_conv_published_size(lib):
     truth = O.conv_f32(I2, K2, N, CI, CO, KY, KX, OY, OX, acc64=True)
     assert not np.isnan(ob.keepalive).any()
     assert normwise(ob.keepalive, truth) <= TOL_FP32
+    # and element by element against sum |input| |weight|: one more oracle pass on the absolute values
+    absprod = O.conv_f32(np.abs(I2), np.abs(K2), N, CI, CO, KY, KX, OY, OX, acc64=True)
+    assert componentwise(ob.keepalive, truth, absprod) <= TOL_FP32
 
 
 def test_ttm_published_size(lib):
@@ -90,6 +94,8 @@ def test_ttm_published_size(lib):
     assert t2sp_b200.ttm(Buffer.from_numpy(a), Buffer.from_numpy(b), cb) == 0
     truth = b.astype(np.float64) @ a.reshape(J * I, L).astype(np.float64).T  # [k, (j, i)]
     assert normwise(cb.keepalive.reshape(K, J * I), truth) <= TOL_FP32
+    absprod = np.abs(b).astype(np.float64) @ np.abs(a).reshape(J * I, L).astype(np.float64).T
+    assert componentwise(cb.keepalive.reshape(K, J * I), truth, absprod) <= TOL_FP32
 
 
 def test_mttkrp_published_size(lib):
@@ -100,11 +106,14 @@ def test_mttkrp_published_size(lib):
     d = np.full((R, I), np.nan, np.float32)
     db = Buffer.from_numpy(d)
     assert t2sp_b200.mttkrp(Buffer.from_numpy(a), Buffer.from_numpy(b), Buffer.from_numpy(c), db) == 0
-    truth = np.zeros((R, I))
+    truth, absprod = np.zeros((R, I)), np.zeros((R, I))
     c64, b64 = c.astype(np.float64), b.astype(np.float64)
     for k in range(K):  # d(i, r) = sum_k (sum_l a(l, i, k) c(l, r)) b(k, r), one k-slice at a time
-        truth += (c64 @ a[k].astype(np.float64).T) * b64[:, k:k + 1]
+        ak = a[k].astype(np.float64).T
+        truth += (c64 @ ak) * b64[:, k:k + 1]
+        absprod += (np.abs(c64) @ np.abs(ak)) * np.abs(b64[:, k:k + 1])
     assert normwise(db.keepalive, truth) <= TOL_FP32
+    assert componentwise(db.keepalive, truth, absprod) <= TOL_FP32
 
 
 def test_capsule_published_size(lib):
@@ -122,3 +131,5 @@ def test_capsule_published_size(lib):
     truth = O.capsule_f32(P2, W2, N, NN, CI, CI, CO, KY, KX, OY, OX, M, M, M, s, acc64=True)
     assert not np.isnan(vb.keepalive).any()
     assert normwise(vb.keepalive, truth) <= TOL_FP32
+    absprod = O.capsule_f32(np.abs(P2), np.abs(W2), N, NN, CI, CI, CO, KY, KX, OY, OX, M, M, M, s, acc64=True)
+    assert componentwise(vb.keepalive, truth, absprod) <= TOL_FP32
