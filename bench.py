@@ -630,7 +630,8 @@ KNOWN_TRAFFIC = {
     "gemm_i8_4096": 35462400 + 18725376,
     "conv_cfg2": 19220480 + 142336,
     "ttm_cfg3": 268876800 + 218153984,
-    "mttkrp_cfg3": 537606400 + 3475456,
+    # profiles/mttkrp_cfg3_mttkrp2_kernel_full.md
+    "mttkrp_cfg3": 537377536 + 4376064,
     "capsule_cfg4": 21994496 + 7168,
     "sgemm_1024": 8471808,
     # profiles/ger_a10_rows_kernel_full.md
