@@ -44,9 +44,9 @@ struct Mttkrp2Cfg {
     static constexpr int kBvalBytes = kMaxK * kBN * 4;
     static constexpr int kSplitWarps = 8;
     static constexpr int kSplitThreads = kSplitWarps * 32;
-    static constexpr int kWarps = 2 + 4 + kSplitWarps;
+    static constexpr int kWarps = 2 + 4 + kSplitWarps + 1;        // producer, issuer 0, 4 drain, split, issuer 1
     static constexpr int kThreads = kWarps * 32;
-    static constexpr int kAccBufs = 4, kASlots = 4;
+    static constexpr int kAccBufs = 4, kASlots = 4;               // accumulators: [pipeline][2]; A slots: even ones pipeline 0, odd ones pipeline 1
     static constexpr int kATmemCol0 = kAccBufs * kBN;             // A slots behind the accumulators
     static constexpr int kTmemCols = 512;
     static constexpr int kNumBars = 2 * kStages + 2 * kASlots + 2 * kAccBufs + 5;
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
             ptx::mbar_init(&tempty_bar[a], 4);
         }
         ptx::mbar_init(cfull_bar, 1);
-        ptx::mbar_init(cfree_bar, 1);
+        ptx::mbar_init(cfree_bar, 2);
         ptx::mbar_init(bready_bar, 4);
         ptx::mbar_init(bdone_bar, 4);
         ptx::mbar_init(cconv_bar, Cfg::kSplitWarps);
@@ -173,77 +173,46 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
                     if (ptx::mbar_try_wait(cfull_bar, (n - 1) & 1)) break;
             }
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------ MMA issuer (whole warp, one elected lane per instruction)
+    } else if (warp == 1 || warp == 6 + Cfg::kSplitWarps) {
+        // ------------------------------------------------------------ MMA issuers (whole warp, one elected lane per instruction)
+        // Two independent pipelines: the k-blocks with an even position in the stream of copies go from split group 0
+        // through A slots 0 and 2 to issuer 0 (warp 1), the odd ones from group 1 through slots 1 and 3 to issuer 1,
+        // and each pipeline sums its k-blocks of a k into accumulators of its own, which the drain warps add. An
+        // issuing warp is held up for as long as its MMAs take to execute (about 53 cycles each at N = 64) and needs
+        // about 630 cycles more per k-block for the barrier round (measured: 330 until the `ready` wait has returned,
+        // 50 fence, 60 commit, 190 loop) plus 650 at every k: one issuer went round in 1170 cycles per k-block with the
+        // tensor pipe busy a third of the time.
+        const int pipe = warp == 1 ? 0 : 1;
         const uint32_t idesc32 = make_instr_desc(1, 2, false, false, kBlockM, Cfg::kBN);
         const uint32_t idesc16 = make_instr_desc(1, 1, false, false, kBlockM, Cfg::kBN);
-        int it = 0, g = 0;
+        int it = 0, kcount = 0;  // kcount: the k values this pipeline has had a k-block of
         bool ok = true;
-        if (knobs & 1) {
-            // variant: one thread issues everything, the other lanes leave
-            if (lane == 0) {
-                for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x) {
-                    int mb, slab, lb0, lb_cnt, k0, k_cnt;
-                    decode(t, mb, slab, lb0, lb_cnt, k0, k_cnt);
-                    for (int kc = 0; kc < k_cnt && ok; ++kc, ++g) {
-                        const int acc = g % Cfg::kAccBufs;
-                        if (!bounded_wait(&tempty_bar[acc], ((g / Cfg::kAccBufs) & 1) ^ 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
-                        ptx::tc_fence_after_sync();
-                        const uint32_t d_tmem = tmem_base + acc * Cfg::kBN;
-                        for (int j = 0; j < lb_cnt; ++j, ++it) {
-                            const int ls = it % Cfg::kASlots;
-                            if (!bounded_wait(&ready_bar[ls], (it / Cfg::kASlots) & 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
-                            ptx::tc_fence_after_sync();
-                            T2SP_TRACE(p, 3, it);
-                            const uint32_t a_hi = tmem_base + Cfg::kATmemCol0 + ls * 64, a_hb = a_hi + 32, a_lb = a_hi + 48;
-                            const uint64_t db = ptx::make_smem_desc(ptx::smem_u32(c_f32 + j * Cfg::kCTile), 16, 1024);
-                            const uint32_t off16 = (j >> 1) * Cfg::kCTile + (j & 1) * 64;
-                            const uint64_t dhb = ptx::make_smem_desc(ptx::smem_u32(c_hb + off16), 16, 1024);
-                            const uint64_t dlb = ptx::make_smem_desc(ptx::smem_u32(c_lb + off16), 16, 1024);
-#pragma unroll
-                            for (int jj = 0; jj < 4; ++jj)
-                                ptx::umma_a_tmem<ptx::KIND_TF32>(d_tmem, a_hi + 8 * jj, db + jj * 2, idesc32, (j | jj) ? 1u : 0u);
-                            if (!p.single_pass) {
-#pragma unroll
-                                for (int jj = 0; jj < 2; ++jj) {
-                                    ptx::umma_a_tmem<ptx::KIND_F16>(d_tmem, a_lb + 8 * jj, dhb + jj * 2, idesc16, 1u);
-                                    ptx::umma_a_tmem<ptx::KIND_F16>(d_tmem, a_hb + 8 * jj, dlb + jj * 2, idesc16, 1u);
-                                }
-                            }
-                            ptx::umma_commit(&afree_bar[ls]);
-                            T2SP_TRACE(p, 4, it);
-                        }
-                        if (ok) ptx::umma_commit(&tfull_bar[acc]);
-                    }
-                    if (ok) ptx::umma_commit(cfree_bar);
-                }
-            }
-        } else
         for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x) {
             int mb, slab, lb0, lb_cnt, k0, k_cnt;
             decode(t, mb, slab, lb0, lb_cnt, k0, k_cnt);
-            for (int kc = 0; kc < k_cnt && ok; ++kc, ++g) {
-                const int acc = g % Cfg::kAccBufs;
-                if (!bounded_wait_warp(&tempty_bar[acc], ((g / Cfg::kAccBufs) & 1) ^ 1, ab, ST_TIMEOUT_MMA, lane)) { ok = false; break; }
+            for (int kc = 0; kc < k_cnt && ok; ++kc, it += lb_cnt) {
+                const int first = it + ((it & 1) != pipe ? 1 : 0);  // this pipeline's first k-block of the k
+                if (first >= it + lb_cnt) continue;
+                const int acc = pipe * 2 + (kcount & 1);
+                if (!bounded_wait_warp(&tempty_bar[acc], ((kcount >> 1) & 1) ^ 1, ab, ST_TIMEOUT_MMA, lane)) { ok = false; break; }
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + acc * Cfg::kBN;
-                for (int j = 0; j < lb_cnt; ++j, ++it) {
-                    const int ls = it % Cfg::kASlots;
+                for (int i = first; i < it + lb_cnt; i += 2) {
+                    const int j = i - it, ls = i % Cfg::kASlots;
                     // the split warps arrive here after they have seen the tile land and (first k-block of an
                     // item) after they have converted c, so this wait covers both
-                    if (!bounded_wait_warp(&ready_bar[ls], (it / Cfg::kASlots) & 1, ab, ST_TIMEOUT_MMA, lane)) { ok = false; break; }
+                    if (!bounded_wait_warp(&ready_bar[ls], (i / Cfg::kASlots) & 1, ab, ST_TIMEOUT_MMA, lane)) { ok = false; break; }
                     ptx::tc_fence_after_sync();
-                    if (lane == 0) T2SP_TRACE(p, 3, it);
+                    if (lane == 0) T2SP_TRACE(p, 3, i);
                     const uint32_t a_hi = tmem_base + Cfg::kATmemCol0 + ls * 64, a_hb = a_hi + 32, a_lb = a_hi + 48;
                     const uint64_t db = ptx::make_smem_desc(ptx::smem_u32(c_f32 + j * Cfg::kCTile), 16, 1024);
                     const uint32_t off16 = (j >> 1) * Cfg::kCTile + (j & 1) * 64;
                     const uint64_t dhb = ptx::make_smem_desc(ptx::smem_u32(c_hb + off16), 16, 1024);
                     const uint64_t dlb = ptx::make_smem_desc(ptx::smem_u32(c_lb + off16), 16, 1024);
-                    if (!(knobs & 8))
 #pragma unroll
                     for (int jj = 0; jj < 4; ++jj)
-                        ptx::umma_tf32_a_tmem_warp(d_tmem, a_hi + 8 * jj, db + jj * 2, idesc32, (j | jj) ? 1u : 0u);
-                    if (!p.single_pass && !(knobs & 12)) {
+                        ptx::umma_tf32_a_tmem_warp(d_tmem, a_hi + 8 * jj, db + jj * 2, idesc32, (i != first || jj) ? 1u : 0u);
+                    if (!p.single_pass) {
 #pragma unroll
                         for (int jj = 0; jj < 2; ++jj) {
                             ptx::umma_f16_a_tmem_warp(d_tmem, a_lb + 8 * jj, dhb + jj * 2, idesc16, 1u);
@@ -251,18 +220,20 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
                         }
                     }
                     ptx::umma_commit_warp(&afree_bar[ls]);
-                    if (lane == 0) T2SP_TRACE(p, 4, it);
+                    if (lane == 0) T2SP_TRACE(p, 4, i);
                 }
                 if (ok) ptx::umma_commit_warp(&tfull_bar[acc]);
+                ++kcount;
             }
-            if (ok) ptx::umma_commit_warp(cfree_bar);
+            if (ok) ptx::umma_commit_warp(cfree_bar);  // tracks this warp's own MMAs: both issuers report
         }
     } else if (warp < 6) {
         // ------------------------------------------------------------ drain: d += E_k * b(k, :), then the partial slab
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         const int et = (warp - 2) * 32 + lane;
         const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-        int g = 0, n = 0;
+        int g = 0, n = 0, it = 0;
+        int kcount[2] = {0, 0};  // per pipeline: the k values it has had a k-block of (as the issuers count them)
         bool ok = true;
         for (int t = blockIdx.x; t < num_items && ok; t += gridDim.x, ++n) {
             int mb, slab, lb0, lb_cnt, k0, k_cnt;
@@ -277,21 +248,40 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
             if (lane == 0) ptx::mbar_arrive(bready_bar);
             if (!bounded_wait_warp(bready_bar, n & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
             float d[Cfg::kBN];
-            for (int kc = 0; kc < k_cnt; ++kc, ++g) {
-                const int acc = g % Cfg::kAccBufs;
-                if (!bounded_wait_warp(&tfull_bar[acc], (g / Cfg::kAccBufs) & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
+            for (int kc = 0; kc < k_cnt; ++kc, ++g, it += lb_cnt) {
+                // E_k is the sum of what the two pipelines accumulated; a pipeline has part in this k if one of the
+                // k's k-blocks has its parity in the stream of copies (both whenever the k has two or more k-blocks)
+                int acc[2];
+                bool part[2];
+#pragma unroll
+                for (int pp = 0; pp < 2; ++pp) {
+                    part[pp] = it + ((it & 1) != pp ? 1 : 0) < it + lb_cnt;
+                    acc[pp] = pp * 2 + (kcount[pp] & 1);
+                    if (part[pp]) {
+                        if (!bounded_wait_warp(&tfull_bar[acc[pp]], (kcount[pp] >> 1) & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
+                    }
+                }
+                if (!ok) break;
                 ptx::tc_fence_after_sync();
                 if (et == 0) T2SP_TRACE(p, 5, g);
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t e[32];
-                    ptx::tmem_ld_32x32(lane_base + acc * Cfg::kBN + half * 32, e);
-                    ptx::tmem_ld_wait();
-                    const float4* bv = reinterpret_cast<const float4*>(bvals + kc * Cfg::kBN + half * 32);
+                for (int qt = 0; qt < 4; ++qt) {  // 16 columns at a time: two accumulators' worth of registers stay few
+                    uint32_t e[16];
+                    ptx::tmem_ld_32x16(lane_base + acc[part[0] ? 0 : 1] * Cfg::kBN + qt * 16, e);
+                    if (part[0] && part[1]) {
+                        uint32_t e2[16];
+                        ptx::tmem_ld_32x16(lane_base + acc[1] * Cfg::kBN + qt * 16, e2);
+                        ptx::tmem_ld_wait();
 #pragma unroll
-                    for (int j4 = 0; j4 < 8; ++j4) {
+                        for (int z = 0; z < 16; ++z) e[z] = __float_as_uint(__uint_as_float(e[z]) + __uint_as_float(e2[z]));
+                    } else {
+                        ptx::tmem_ld_wait();
+                    }
+                    const float4* bv = reinterpret_cast<const float4*>(bvals + kc * Cfg::kBN + qt * 16);
+#pragma unroll
+                    for (int j4 = 0; j4 < 4; ++j4) {
                         const float4 b4 = bv[j4];  // the same address in every lane: a broadcast read
-                        float* dd = &d[half * 32 + 4 * j4];
+                        float* dd = &d[qt * 16 + 4 * j4];
                         if (kc == 0) {
                             dd[0] = __uint_as_float(e[4 * j4 + 0]) * b4.x; dd[1] = __uint_as_float(e[4 * j4 + 1]) * b4.y;
                             dd[2] = __uint_as_float(e[4 * j4 + 2]) * b4.z; dd[3] = __uint_as_float(e[4 * j4 + 3]) * b4.w;
@@ -303,7 +293,12 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
                 }
                 ptx::tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(&tempty_bar[acc]);
+#pragma unroll
+                for (int pp = 0; pp < 2; ++pp)
+                    if (part[pp]) {
+                        if (lane == 0) ptx::mbar_arrive(&tempty_bar[acc[pp]]);
+                        ++kcount[pp];
+                    }
                 if (et == 0) T2SP_TRACE(p, 6, g);
             }
             if (!ok) break;
