@@ -631,7 +631,7 @@ KNOWN_TRAFFIC = {
     "conv_cfg2": 19220480 + 142336,
     "ttm_cfg3": 268876800 + 218153984,
     # profiles/mttkrp_cfg3_mttkrp2_kernel_full.md
-    "mttkrp_cfg3": 537377536 + 4376064,
+    "mttkrp_cfg3": 537191168 + 4868352,
     "capsule_cfg4": 21994496 + 7168,
     "sgemm_1024": 8471808,
     # profiles/ger_a10_rows_kernel_full.md

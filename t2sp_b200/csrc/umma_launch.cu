@@ -8,15 +8,23 @@ namespace t2sp {
 
 namespace {
 
-// Partial slabs [split][col][row] (dense, `rows` fastest) summed in split order into out[col * ld_out + row].
+// Partial slabs [split][col][row] (dense, `rows` fastest) summed into out[col * ld_out + row]. Four neighbouring
+// lanes share an element: lane part p adds slabs p, p + 4, p + 8, ... in that order, then the four sums are added
+// as (s0 + s1) + (s2 + s3): a fixed order whatever the launch, so the result is reproducible bit for bit.
 __global__ void reduce_partials_kernel(const float* __restrict__ partials, float* __restrict__ out, int rows, int cols,
                                        long long ld_out, int splits) {
     const long long elems = static_cast<long long>(rows) * cols;
-    const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-    if (idx >= elems) return;
+    const long long tid = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    const long long idx = tid >> 2;
+    const int part = static_cast<int>(tid & 3);
+    ptx::grid_dep_wait();  // launched while the kernel that writes the partial slabs may still be running
     float acc = 0.f;
-    for (int s = 0; s < splits; ++s) acc += partials[s * elems + idx];
-    out[(idx / rows) * ld_out + idx % rows] = acc;
+    if (idx < elems)
+        for (int s = part; s < splits; s += 4) acc += partials[s * elems + idx];
+    const float other = __shfl_xor_sync(0xffffffffu, acc, 1);
+    const float pair = (part & 1) ? other + acc : acc + other;   // (s0 + s1) resp. (s2 + s3), same operand order in both lanes
+    const float far = __shfl_xor_sync(0xffffffffu, pair, 2);
+    if (idx < elems && part == 0) out[(idx / rows) * ld_out + idx % rows] = pair + far;
 }
 
 // One thread per row and four consecutive columns; the sum over the slabs runs in slab order.
@@ -308,9 +316,18 @@ cudaError_t reduce_partials_launch(const float* partials, float* out, int rows, 
     const int threads = 256;
     const long long elems = static_cast<long long>(rows) * cols;
     if (elems <= 0) return cudaSuccess;
-    const long long blocks = (elems + threads - 1) / threads;
-    reduce_partials_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(partials, out, rows, cols, ld_out, splits);
-    return cudaGetLastError();
+    // programmatic stream serialization: the blocks are scheduled as the CTAs of the kernel before it retire; the
+    // kernel itself waits for that grid before it reads a partial slab
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>((elems * 4 + threads - 1) / threads));
+    cfg.blockDim = dim3(threads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, reduce_partials_kernel, partials, out, rows, cols, ld_out, splits);
 }
 
 }  // namespace t2sp

@@ -123,6 +123,7 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
         ptx::tmem_relinquish<1>();
     }
     ptx::tc_fence_before_sync();
+    ptx::grid_dep_launch();  // the kernel that sums the partial slabs may be scheduled while this grid runs
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
