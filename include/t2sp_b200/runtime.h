@@ -209,7 +209,9 @@ int t2sp_b200_mttkrp(halide_buffer_t *a, halide_buffer_t *b, halide_buffer_t *c,
  *    because each split rewrites its slab), so calls that overlap on the GPU race.
  *  - the first call on each device looks up the array's address; make it outside stream capture.
  *  - sync != 0: waits for `cuda_stream` and returns the kernels' status; sync == 0: returns
- *    after enqueueing on `cuda_stream` (NULL = default stream).                            */
+ *    after enqueueing on `cuda_stream` (NULL = default stream). A status that a sync == 0 call's
+ *    kernels raise (a bounded wait that ran out) is reported, and cleared, by the next sync != 0
+ *    call on that device.                                                                  */
 #define T2SP_B200_NOALLOC_SCRATCH_BYTES (16u << 20)
 int t2sp_b200_mttkrp_noalloc(const float *a, int64_t a_stride_i, int64_t a_stride_k, const float *b,
                              int64_t b_stride_r, const float *c, int64_t c_stride_r, float *d, int64_t d_stride_r,

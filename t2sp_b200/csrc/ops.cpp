@@ -1289,7 +1289,6 @@ int mttkrp2_run(const char* who, float* pa, int64_t lda1, int64_t lda2, const fl
         cudaMemsetAsync(trace_dev, 0, 48 * 1024 * sizeof(long long), s);
         p.trace = trace_dev;
     }
-    if (const char* kn = getenv("T2SP_B200_KNOBS")) p.knobs = atoi(kn);
 #endif
     if (sync_after) cudaEventRecord(rt_event(0), s);
     cudaError_t e = mttkrp2_launch(p, std::max(1, std::min(items, core_sm_count())), s);

@@ -85,14 +85,8 @@ __global__ void __launch_bounds__(Mttkrp2Cfg::kThreads, 1) umma_mttkrp2_kernel(c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cconv_bar + 1);
     uint32_t* abort_slot = tmem_slot + 1;
 
-    int warp = threadIdx.x >> 5;
+    const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-#ifdef T2SP_DEBUG_KNOBS
-    const int knobs = p.knobs;
-    if ((knobs & 2) && warp < 2) warp ^= 1;  // variant: producer and MMA issuer trade warps (and scheduler partitions)
-#else
-    constexpr int knobs = 0;
-#endif
     const AbortCtx ab{abort_slot, p.status, p.wait_cycles > 0 ? p.wait_cycles : kWaitTimeoutCycles};
     const int slabs = p.mt_lranges * p.mt_kranges;
     const int num_items = p.tiles_m * slabs;

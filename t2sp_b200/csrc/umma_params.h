@@ -95,7 +95,6 @@ struct CoreParams {
     unsigned* status;
 #ifdef T2SP_DEBUG_KNOBS
     long long* trace;  // per-role cycle stamps of CTAs 0 and 1 (timing experiments), or null
-    int knobs;         // variants under test (instrumented builds only)
 #endif
 };
 
