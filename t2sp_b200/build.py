@@ -14,7 +14,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libt2sp_b200.so")
 
 EXTRA_LINK = ["-ldl"]
-SOURCES = ["launch_core.cu", "launch_core_x3.cu", "launch_pair.cu", "launch_x3pair.cu", "launch_mttkrp.cu", "umma_launch.cu", "host_rt.cpp", "errors.cpp", "halide_rt.cpp", "ops.cpp", "multigpu.cpp", "noalloc.cu"]
+SOURCES = ["launch_core.cu", "launch_core_x3.cu", "launch_pair.cu", "launch_x3pair.cu", "launch_x3tm.cu", "launch_mttkrp.cu", "umma_launch.cu", "host_rt.cpp", "errors.cpp", "halide_rt.cpp", "ops.cpp", "multigpu.cpp", "noalloc.cu"]
 
 
 def _nvcc():

@@ -67,6 +67,7 @@ const Env* read_env() {
     e->no_pipeline = getenv("T2SP_B200_NO_PIPELINE") != nullptr;
     e->log = getenv("T2SP_B200_LOG") != nullptr;
     e->mttkrp_v1 = getenv("T2SP_B200_MTTKRP_V1") != nullptr;
+    e->no_x3tm = getenv("T2SP_B200_NO_X3TM") != nullptr;
     if (const char* f = getenv("T2SP_B200_SPLITK")) e->splitk = std::max(1, atoi(f));
     e->precision = T2SP_PRECISION_TF32X3;
     if (const char* p = getenv("T2SP_B200_PRECISION")) {

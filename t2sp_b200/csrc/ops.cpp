@@ -301,7 +301,7 @@ int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool syn
     if (pair) grid = 2 * std::max(1, std::min(items, core_sm_count() / 2));  // one cluster of 2 CTAs per work item slot
     if (sync_after) cudaEventRecord(rt_event(0), s);
     cudaError_t e = !pair ? core_launch(arith, op, bn, p, grid, s)
-                          : (arith == AR_TF32X3 ? x3pair_launch(op, bn, p, grid, s)
+                          : (arith == AR_TF32X3 ? ((bn == 256 && !rt_env().no_x3tm) ? x3tm_launch(op, p, grid, s) : x3pair_launch(op, bn, p, grid, s))
                                                 : (pair2 ? pair2_launch(arith, op, p, grid, s) : pair_launch(arith, op, p, grid, s)));
     if (e == cudaSuccess && partials) {
         e = splitk_finalize_launch(partials, ld_part, slab_rows, p.splits, final_p, s);

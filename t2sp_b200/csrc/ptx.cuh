@@ -239,15 +239,22 @@ __device__ __forceinline__ void umma_f16_a_tmem_warp(uint32_t d_tmem, uint32_t a
         "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// Single-thread forms of the two above.
-template <int KIND>
+// Single-thread forms of the two above; CTA_GROUP 2: a CTA pair's MMA, each CTA holding its 128 rows of A at the same
+// address of its own tensor memory.
+template <int KIND, int CTA_GROUP = 1>
 __device__ __forceinline__ void umma_a_tmem(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    if constexpr (KIND == KIND_TF32)
-        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
-                     "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-    else
-        asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem),
-                     "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+#define T2SP_UMMA_TS(GRP, KND)                                                                                      \
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::" GRP ".kind::" KND          \
+                 " [%0], [%1], %2, %3, p;\n}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) \
+                 : "memory")
+    if constexpr (CTA_GROUP == 1) {
+        if constexpr (KIND == KIND_TF32) T2SP_UMMA_TS("1", "tf32");
+        else T2SP_UMMA_TS("1", "f16");
+    } else {
+        if constexpr (KIND == KIND_TF32) T2SP_UMMA_TS("2", "tf32");
+        else T2SP_UMMA_TS("2", "f16");
+    }
+#undef T2SP_UMMA_TS
 }
 __device__ __forceinline__ void umma_commit_warp(uint64_t* bar) {
     asm volatile(

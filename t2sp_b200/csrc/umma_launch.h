@@ -27,6 +27,8 @@ cudaError_t pair2_launch(int arith, int op, const CoreParams& p, int grid, cudaS
 // OP_GEMM / OP_TTM / OP_CONV / OP_CAPSULE; `grid` must be even, tiles count 256 x un tiles and
 // p.idesc describes a 256 x un TF32 MMA.
 cudaError_t x3pair_launch(int op, int un, const CoreParams& p, int grid, cudaStream_t stream);
+// The 256-column pair tile with the A operand in tensor memory and the cross terms as bf16 MMAs (umma_x3tm.cuh).
+cudaError_t x3tm_launch(int op, const CoreParams& p, int grid, cudaStream_t stream);
 
 // Launches the accumulate-then-scale MTTKRP kernel (umma_mttkrp.cuh; R <= 64) with `grid` persistent CTAs over the
 // work items that p.tiles_m, p.mt_lranges and p.mt_kranges describe; partial slabs go to p.out.
