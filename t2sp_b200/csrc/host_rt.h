@@ -48,6 +48,7 @@ ThreadState& tls();
 // Environment knobs, read once when the library is first used and again on t2sp_b200_reload_env().
 struct Env {
     bool no_tma_store = false, no_pair = false, pair128 = false, no_splitk = false, no_pipeline = false, log = false;
+    bool no_presplit = false;  // fp32 pair kernel: B's bf16 tiles always from the split warps, never from a pre-pass
     bool no_x3tm = false;      // fp32 pair tiles through the all-shared-memory 3xTF32 kernel instead of the tensor-memory one
     bool mttkrp_v1 = false;    // MTTKRP through the Khatri-Rao-tile kernel even where the accumulate-then-scale kernel applies
     int splitk = 0;            // forced number of split-K ranges of the fp32 pair kernel, 0 = choose

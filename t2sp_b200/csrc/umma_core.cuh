@@ -160,6 +160,20 @@ __device__ __forceinline__ void store_chunk_tma(const CoreParams& p, uint8_t* bu
                                                 const uint32_t (&r)[32], int lane) {
     if (lane == 0) ptx::bulk_wait_read_all();  // the previous store has finished reading the tile
     __syncwarp();
+    if (p.tma_t) {
+        // column-major output (m contiguous): the tile is staged as [column][row], 128 bytes per column, and one
+        // store writes 32 pieces of 128 contiguous bytes (plain stores of the same pieces, one instruction per
+        // column with a column pitch between them, held the epilogue warps up for longer than the whole k-loop)
+#pragma unroll
+        for (int j = 0; j < 32; ++j) *reinterpret_cast<uint32_t*>(buf + j * 128 + lane * 4) = r[j];
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0 && m_warp0 < p.M && nc < p.N) {
+            ptx::tma_store_2d(&p.mapC, buf, m_warp0, nc);
+            ptx::bulk_commit_group();
+        }
+        return;
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j)
         *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) =

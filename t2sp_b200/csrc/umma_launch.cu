@@ -2,6 +2,8 @@
 // their launchers; the contraction kernels themselves are instantiated in launch_*.cu.
 #include "launch_util.cuh"
 #include "umma_core.cuh"
+#include <cuda_bf16.h>
+
 #include "umma_launch.h"
 
 namespace t2sp {
@@ -25,6 +27,41 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partials, float
     const float pair = (part & 1) ? other + acc : acc + other;   // (s0 + s1) resp. (s2 + s3), same operand order in both lanes
     const float far = __shfl_xor_sync(0xffffffffu, pair, 2);
     if (idx < elems && part == 0) out[(idx / rows) * ld_out + idx % rows] = pair + far;
+}
+
+// Pre-pass of the fp32 pair kernel with its A operand in tensor memory: the bf16 operands of the cross-term MMAs,
+// bf16(x) and bf16(x - trunc_tf32(x)), of an operand that many row tiles re-read.
+__device__ __forceinline__ float presplit_lo(float v) { return v - __uint_as_float(__float_as_uint(v) & 0xFFFFE000u); }
+__device__ __forceinline__ uint32_t presplit_pack(float a, float b) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+// K-major operand (rows of `cols` contraction values): row n of the result holds, per block of 32 contraction
+// values, 32 bf16(x) (64 bytes) followed by 32 bf16(lo) (64 bytes); values beyond `cols` are zero. One thread per
+// group of four values.
+__global__ void presplit_kmajor_kernel(const float* __restrict__ src, long long ld_src, int rows, int cols, int num_kb,
+                                       uint8_t* __restrict__ dst) {
+    const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+    const int groups = num_kb * 8;
+    if (idx >= static_cast<long long>(rows) * groups) return;
+    const int n = static_cast<int>(idx / groups), g = static_cast<int>(idx % groups), k0 = g * 4;
+    const float* s = src + n * ld_src + k0;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = k0 + j < cols ? s[j] : 0.f;
+    uint8_t* d = dst + (static_cast<long long>(n) * num_kb + (g >> 3)) * 128 + (g & 7) * 8;
+    *reinterpret_cast<uint2*>(d) = make_uint2(presplit_pack(v[0], v[1]), presplit_pack(v[2], v[3]));
+    *reinterpret_cast<uint2*>(d + 64) = make_uint2(presplit_pack(presplit_lo(v[0]), presplit_lo(v[1])),
+                                                   presplit_pack(presplit_lo(v[2]), presplit_lo(v[3])));
+}
+// Any layout, element by element: hb[i] = bf16(src[i]), lb[i] = bf16(lo(src[i])) for i < count. Two values per thread.
+__global__ void presplit_elem_kernel(const float* __restrict__ src, long long count, uint32_t* __restrict__ hb,
+                                     uint32_t* __restrict__ lb) {
+    const long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 2;
+    if (i >= count) return;
+    const float a = src[i], b = i + 1 < count ? src[i + 1] : 0.f;
+    hb[i >> 1] = presplit_pack(a, b);
+    lb[i >> 1] = presplit_pack(presplit_lo(a), presplit_lo(b));
 }
 
 // One thread per row and four consecutive columns; the sum over the slabs runs in slab order.
@@ -240,6 +277,23 @@ cudaError_t transpose32_launch(const void* src, long long ld_src, void* dst, lon
     dim3 grid((cols + 31) / 32, (rows + 31) / 32, batch), block(32, 8);
     transpose32_kernel<<<grid, block, 0, stream>>>(static_cast<const uint32_t*>(src), ld_src, bs_src,
                                                    static_cast<uint32_t*>(dst), ld_dst, bs_dst, rows, cols);
+    return cudaGetLastError();
+}
+
+cudaError_t presplit_kmajor_launch(const void* src, long long ld_src, int rows, int cols, void* dst, cudaStream_t stream) {
+    const int num_kb = (cols + 31) / 32;
+    const long long work = static_cast<long long>(rows) * num_kb * 8;
+    if (work <= 0) return cudaSuccess;
+    presplit_kmajor_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
+        static_cast<const float*>(src), ld_src, rows, cols, num_kb, static_cast<uint8_t*>(dst));
+    return cudaGetLastError();
+}
+
+cudaError_t presplit_elem_launch(const void* src, long long count, void* hb, void* lb, cudaStream_t stream) {
+    const long long work = (count + 1) / 2;
+    if (work <= 0) return cudaSuccess;
+    presplit_elem_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
+        static_cast<const float*>(src), count, static_cast<uint32_t*>(hb), static_cast<uint32_t*>(lb));
     return cudaGetLastError();
 }
 

@@ -39,6 +39,12 @@ cudaError_t mttkrp2_launch(const CoreParams& p, int grid, cudaStream_t stream);
 cudaError_t transpose32_launch(const void* src, long long ld_src, void* dst, long long ld_dst, int rows, int cols,
                                cudaStream_t stream, int batch = 1, long long bs_src = 0, long long bs_dst = 0);
 
+// Pre-pass for the fp32 pair kernel's pre-split B. K-major operand [rows][cols] (row pitch ld_src elements) ->
+// [rows][ceil(cols / 32)][32 bf16(x) | 32 bf16(lo)] (128 bytes per row and k-block, zero beyond cols).
+cudaError_t presplit_kmajor_launch(const void* src, long long ld_src, int rows, int cols, void* dst, cudaStream_t stream);
+// Element by element over `count` fp32 values: hb[i] = bf16(src[i]), lb[i] = bf16(src[i] - trunc_tf32(src[i])).
+cudaError_t presplit_elem_launch(const void* src, long long count, void* hb, void* lb, cudaStream_t stream);
+
 // Number of SMs of the current device (cached).
 int core_sm_count();
 

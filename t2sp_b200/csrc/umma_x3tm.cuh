@@ -20,11 +20,15 @@
 //               by quarters: warps 12 and 13 take the rows of quarters 0 and 1, warps 2 / 14 and 3 / 15 share
 //               quarters 2 and 3 by halves of the k-block; the B tile's 1024 16-byte pieces are dealt out so that
 //               all six warps carry about the same number of pieces.
+//               With BPRE the bf16 tiles of B come from a pre-pass over the whole operand (worth it when many row tiles
+//               re-read a small B: weights, the factor of a TTM) and the split warps convert A only.
 //   warps 4-11  epilogue as in umma_x3pair.cuh: every 8 k-blocks the accumulator is added into fp32 registers
 //               (round to nearest) and handed back
 // TMEM per CTA (512 columns): [accumulator 256 | 4 A slots of 64: hi 32, bf16(a) 16, bf16(lo) 16].
 #pragma once
 #include <cuda_bf16.h>
+
+#include <type_traits>
 
 #include "umma_core.cuh"
 #include "umma_x3pair.cuh"
@@ -58,12 +62,17 @@ struct X3TmCfg {
 };
 
 __device__ __forceinline__ uint32_t x3_pack_bf16(float lo_elem, float hi_elem) {
+#ifdef T2SP_X3_INT_PACK
+    // round to nearest (ties up) with integer adds and one byte permute: full-rate instructions instead of a conversion
+    return __byte_perm(__float_as_uint(lo_elem) + 0x8000u, __float_as_uint(hi_elem) + 0x8000u, 0x7632);
+#else
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo_elem, hi_elem);  // .x (low half) = first argument
     return *reinterpret_cast<const uint32_t*>(&v);
+#endif
 }
 __device__ __forceinline__ float x3_tf32_lo(float x) { return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
 
-template <int OP, int STAGES>
+template <int OP, int STAGES, bool BPRE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(X3TmCfg<OP, STAGES>::kThreads, 1)
 umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
     using Cfg = X3TmCfg<OP, STAGES>;
@@ -121,8 +130,9 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
     if (threadIdx.x == 0) T2SP_TRACE(p, 10, 0);
 
     // Split role. `q`: TMEM lane quarter of the warp; `a_half0`, `a_halves`: which halves of the k-block's 32 columns
-    // of the quarter's A rows this warp converts; `b0`, `nb`: its B pieces are b0 + lane + 32 i, i < nb.
-    auto split_role = [&](const int q, const int a_half0, const int a_halves, const int b0, const int nb) {
+    // of the quarter's A rows this warp converts; `b0`, NB: its B pieces are b0 + lane + 32 i, i < NB.
+    auto split_role = [&](const int q, const int a_half0, const int a_halves, const int b0, auto nb_const) {
+        constexpr int NB = decltype(nb_const)::value;
         int it = 0;
         bool ok = true;
         const int row = q * 32 + lane;
@@ -135,8 +145,14 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
                 uint8_t* b16 = b16_ring + ls * Cfg::kB16Bytes;
                 if (!bounded_wait_warp(&free_bar[ls], ((it / Cfg::kSlots) & 1) ^ 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
                 ptx::tc_fence_after_sync();
+#ifdef T2SP_TRACE_HEAVY
+                if (warp == 12 && lane == 0) T2SP_TRACE(p, 8, it);
+#endif
                 if (!bounded_wait_warp(&full_bar[s], (it / STAGES) & 1, ab, ST_TIMEOUT_SPLITTER, lane)) { ok = false; break; }
                 if (warp == 12 && lane == 0) T2SP_TRACE(p, 1, it);
+#ifdef T2SP_TRACE_HEAVY
+                if (warp == 2 && lane == 0) T2SP_TRACE(p, 11, it);
+#endif
                 // A: this thread's tile row (16-byte chunk c sits at c ^ (row & 7)), half a k-block at a time:
                 // raw words for the TF32 pass, bf16(a) and bf16(lo_a) (two k values per 32-bit column) for the others
                 const uint8_t* rp = raw + row * 128;
@@ -160,16 +176,30 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
                         ptx::tmem_st_32x8(taddr + 48 + 8 * h, vl);
                     }
                 }
+#ifdef T2SP_TRACE_HEAVY
+                if (warp == 12 && lane == 0) T2SP_TRACE(p, 7, it);
+#endif
+#ifdef T2SP_TRACE_HEAVY
+                if (warp == 2 && lane == 0) T2SP_TRACE(p, 12, it);
+#endif
                 // B: 16-byte pieces of the raw tile (four consecutive K or N values) become two 8-byte pieces
-                if (!p.single_pass) {
+                if (!BPRE && !p.single_pass) {
                     const uint8_t* braw = raw + Cfg::kABytes;
-#pragma unroll 1
-                    for (int i = 0; i < nb; ++i) {
-                        const int ci = b0 + lane + 32 * i;
-                        const float4 v = *reinterpret_cast<const float4*>(braw + (ci << 4));
-                        const uint2 hb = make_uint2(x3_pack_bf16(v.x, v.y), x3_pack_bf16(v.z, v.w));
-                        const uint2 lb = make_uint2(x3_pack_bf16(x3_tf32_lo(v.x), x3_tf32_lo(v.y)),
-                                                    x3_pack_bf16(x3_tf32_lo(v.z), x3_tf32_lo(v.w)));
+                    // in batches of up to four pieces: loads first, then conversions and stores, so that a batch's loads overlap
+                    // (all of a warp's pieces at once spilled registers in the warps with the small budget)
+#pragma unroll
+                    for (int i0 = 0; i0 < NB; i0 += 4) {
+                    float4 v[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (i0 + i < NB) v[i] = *reinterpret_cast<const float4*>(braw + ((b0 + lane + 32 * (i0 + i)) << 4));
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        if (i0 + i >= NB) break;
+                        const int ci = b0 + lane + 32 * (i0 + i);
+                        const uint2 hb = make_uint2(x3_pack_bf16(v[i].x, v[i].y), x3_pack_bf16(v[i].z, v[i].w));
+                        const uint2 lb = make_uint2(x3_pack_bf16(x3_tf32_lo(v[i].x), x3_tf32_lo(v[i].y)),
+                                                    x3_pack_bf16(x3_tf32_lo(v[i].z), x3_tf32_lo(v[i].w)));
                         if constexpr (!Cfg::kBMnMajor) {
                             // K-major tile: row r (an n) holds 32 K values in 128 bytes, chunk c stored at c ^ (r & 7). The
                             // bf16 tile keeps the row pitch: bf16(b) of the row in its first 64 bytes, bf16(lo_b) in its
@@ -190,8 +220,16 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
                             *reinterpret_cast<uint2*>(d + Cfg::kB16Bytes / 2) = lb;
                         }
                     }
+                    asm volatile("" ::: "memory");
+                    }
+#ifdef T2SP_TRACE_HEAVY
+                    if (warp == 2 && lane == 0) T2SP_TRACE(p, 15, it);
+#endif
                     ptx::fence_proxy_async_smem();
                 }
+#ifdef T2SP_TRACE_HEAVY
+                if (warp == 2 && lane == 0) T2SP_TRACE(p, 14, it);
+#endif
                 ptx::tmem_st_wait();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
@@ -200,6 +238,12 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
                     else ptx::mbar_arrive_peer(&ready_bar[ls], 0);
                 }
                 if (warp == 12 && lane == 0) T2SP_TRACE(p, 2, it);
+#ifdef T2SP_TRACE_HEAVY
+                if (warp == 2 && lane == 0) T2SP_TRACE(p, 13, it);
+#endif
+#ifdef T2SP_TRACE_HEAVY
+                if (lane == 0) T2SP_TRACE(p, 16 + (warp < 4 ? warp - 2 : warp - 10), it);
+#endif
             }
         }
     };
@@ -214,6 +258,10 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
                 ptx::prefetch_tensormap(&p.mapA[0]);
             }
             ptx::prefetch_tensormap(&p.mapB);
+            if (BPRE) {
+                ptx::prefetch_tensormap(&p.mapB2);
+                if (Cfg::kBMnMajor) ptx::prefetch_tensormap(&p.mapB3);
+            }
             int it = 0;
             bool ok = true;
             for (int t = pair; t < num_tiles && ok; t += num_pairs) {
@@ -231,8 +279,34 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
                     if (!bounded_wait(&empty_bar[s], ((it / STAGES) & 1) ^ 1, ab, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
                     uint8_t* sa = smem + s * Cfg::kStageBytes;
                     uint8_t* sb = sa + Cfg::kABytes;
+                    const int ls = it % Cfg::kSlots;
+                    uint8_t* b16 = b16_ring + ls * Cfg::kB16Bytes;
+                    // BPRE: bf16(b) and bf16(lo_b) were computed once per call by a pre-pass and come by TMA, straight
+                    // into the slot the MMAs read them from (free once the MMAs of k-block it - kSlots retired)
+                    if (BPRE && !p.single_pass &&
+                        !bounded_wait(&free_bar[ls], ((it / Cfg::kSlots) & 1) ^ 1, ab, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
                     T2SP_TRACE(p, 0, it);
-                    ptx::mbar_expect_tx(&full_bar[s], Cfg::kStageBytes);
+                    ptx::mbar_expect_tx(&full_bar[s], Cfg::kStageBytes + ((BPRE && !p.single_pass) ? Cfg::kB16Bytes : 0));
+                    if (BPRE && !p.single_pass) {
+                        if constexpr (OP == OP_TTM) {
+                            // rows of [bf16(b) 32 k | bf16(lo_b) 32 k] per k-block
+                            ptx::tma_load_2d(b16, &p.mapB2, &full_bar[s], kb * 64, n0);
+                        } else if constexpr (OP == OP_GEMM) {
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                ptx::tma_load_2d(b16 + j * 4096, &p.mapB2, &full_bar[s], n0 + j * 64, kb * 32);
+                                ptx::tma_load_2d(b16 + Cfg::kB16Bytes / 2 + j * 4096, &p.mapB3, &full_bar[s], n0 + j * 64, kb * 32);
+                            }
+                        } else if constexpr (OP == OP_CONV) {
+                            const int tap = kb / p.cblks, cb = kb % p.cblks;
+                            const int ky = tap % p.KY, kx = tap / p.KY;
+#pragma unroll
+                            for (int j = 0; j < 2; ++j) {
+                                ptx::tma_load_4d(b16 + j * 4096, &p.mapB2, &full_bar[s], n0 + j * 64, kx, cb * 32, ky);
+                                ptx::tma_load_4d(b16 + Cfg::kB16Bytes / 2 + j * 4096, &p.mapB3, &full_bar[s], n0 + j * 64, kx, cb * 32, ky);
+                            }
+                        }
+                    }
                     if constexpr (OP == OP_GEMM || OP == OP_TTM) {
                         ptx::tma_load_2d(sa, &p.mapA[0], &full_bar[s], kb * 32, m0);
                         if constexpr (OP == OP_TTM) {
@@ -275,11 +349,13 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
                                                  tap, ci0 / p.CII, mk0);
                         }
                     }
+                    T2SP_TRACE(p, 22, it);
                 }
             }
         } else if (warp >= 2) {
-            // quarters 2 and 3, first half of the k-block; B pieces 128 + 224 w ...
-            split_role(warp, 0, 1, 128 + (warp - 2) * 224, 7);
+            // quarters 2 and 3, first half of the k-block. B pieces: 8 per thread in warps 12 and 13, 4 per thread in the
+            // other four, so that each of the SM's four schedulers (warp % 4) carries the same number of conversions
+            split_role(warp, 0, 1, 512 + (warp - 2) * 128, std::integral_constant<int, 4>{});
         } else if (warp == 1 && lane == 0 && rank == 0) {
             // ------------------------------------------------------------ MMA issuer (leader CTA)
             int it = 0, gch = 0;
@@ -400,8 +476,8 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
     } else {
         // ------------------------------------------------------------ split warps (both CTAs)
         set_max_regs_dec<88>();
-        if (warp < 14) split_role(warp & 3, 0, 2, (warp - 12) * 64, 2);                  // quarters 0 and 1, whole rows
-        else split_role(warp & 3, 1, 1, 128 + (warp - 12) * 224, 7);                     // quarters 2 and 3, second half
+        if (warp < 14) split_role(warp & 3, 0, 2, (warp - 12) * 256, std::integral_constant<int, 8>{});                // quarters 0 and 1, whole rows
+        else split_role(warp & 3, 1, 1, 512 + (warp - 12) * 128, std::integral_constant<int, 4>{});                    // quarters 2 and 3, second half
     }
 
     // ---------------------------------------------------------------- teardown

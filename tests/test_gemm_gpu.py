@@ -220,6 +220,30 @@ def test_fp32_split_k(lib, M, N, K, trans_b, force):
     assert componentwise(split, truth, O.gemm_f32(np.abs(A), np.abs(B), acc64=True)) <= TOL_FP32
 
 
+@pytest.mark.parametrize("M,N,K,trans_b", [(9728, 256, 96, 0), (9728, 264, 200, 0), (9728, 256, 100, 1), (5120, 500, 640, 1)])
+def test_fp32_pair_presplit_b_is_bit_identical(lib, M, N, K, trans_b):
+    """fp32 pair kernel with A in tensor memory: with many row tiles over one B, the bf16 operands of the cross-term
+    MMAs (bf16(b), bf16(b - tf32(b))) come from a pre-pass over B instead of from the split warps, tile by tile.
+    Same values either way, so the same bits out; one launch more. K = 100 / 200 end inside a k-block."""
+    import t2sp_b200
+    from t2sp_b200 import Buffer, GemmDesc
+    A, B = O.uniform(21, 1, (M, K)), O.uniform(21, 2, (K, N))
+    d = GemmDesc()
+    d.trans_b = trans_b
+    Bin = np.ascontiguousarray(B.T) if trans_b else B
+    outs = []
+    for env in ({"T2SP_B200_NO_SPLITK": "1"}, {"T2SP_B200_NO_SPLITK": "1", "T2SP_B200_NO_PRESPLIT": "1"}):
+        with library_env(**env):
+            cb = Buffer.from_numpy(np.full((M, N), np.nan, np.float32))
+            before = lib.t2sp_b200_kernel_launches()
+            assert t2sp_b200.gemm(Buffer.from_numpy(A), Buffer.from_numpy(Bin), cb, d) == 0
+            outs.append((cb.keepalive.copy(), lib.t2sp_b200_kernel_launches() - before))
+    (pre, n_pre), (plain, n_plain) = outs
+    assert n_pre == n_plain + 1, "the pre-pass is a launch of its own"
+    assert np.array_equal(pre, plain)
+    assert normwise(pre, O.gemm_f32(A, B, acc64=True)) <= TOL_FP32
+
+
 def test_fp32_split_k_tiled_layout_and_blas_epilogue(lib):
     """The summing kernel applies the call's own epilogue: the 6-D tiled layout and alpha/beta.
     (Split-K is forced: by itself the library avoids it for tiled layouts, whose summing pass is dear.)"""
