@@ -7,10 +7,10 @@
 namespace t2sp {
 
 namespace {
-template <int OP, int STAGES, bool BPRE>
+template <int OP>
 cudaError_t launch_x3tm(const CoreParams& p, int grid, cudaStream_t stream) {
-    using Cfg = X3TmCfg<OP, STAGES>;
-    auto kern = umma_x3tm_kernel<OP, STAGES, BPRE>;
+    using Cfg = X3TmCfg<OP>;
+    auto kern = umma_x3tm_kernel<OP>;
     static std::atomic<bool> configured[kMaxDev];
     if (cudaError_t e = allow_smem(kern, Cfg::kSmemBytes, configured)) return e;
     kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
@@ -19,11 +19,11 @@ cudaError_t launch_x3tm(const CoreParams& p, int grid, cudaStream_t stream) {
 }  // namespace
 
 cudaError_t x3tm_launch(int op, const CoreParams& p, int grid, cudaStream_t stream) {
+    if (!p.b_pre || !p.b_images) return cudaErrorInvalidValue;
     switch (op) {
-        case OP_GEMM: return p.b_pre ? launch_x3tm<OP_GEMM, 4, true>(p, grid, stream) : launch_x3tm<OP_GEMM, 4, false>(p, grid, stream);
-        case OP_TTM: return p.b_pre ? launch_x3tm<OP_TTM, 4, true>(p, grid, stream) : launch_x3tm<OP_TTM, 4, false>(p, grid, stream);
-        case OP_CONV: return p.b_pre ? launch_x3tm<OP_CONV, 4, true>(p, grid, stream) : launch_x3tm<OP_CONV, 4, false>(p, grid, stream);
-        case OP_CAPSULE: return p.b_pre ? cudaErrorInvalidValue : launch_x3tm<OP_CAPSULE, 4, false>(p, grid, stream);
+        case OP_GEMM: return launch_x3tm<OP_GEMM>(p, grid, stream);
+        case OP_TTM: return launch_x3tm<OP_TTM>(p, grid, stream);
+        case OP_CONV: return launch_x3tm<OP_CONV>(p, grid, stream);
     }
     return cudaErrorInvalidValue;
 }

@@ -319,7 +319,7 @@ int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool syn
     if (pair) grid = 2 * std::max(1, std::min(items, core_sm_count() / 2));  // one cluster of 2 CTAs per work item slot
     if (sync_after) cudaEventRecord(rt_event(0), s);
     cudaError_t e = !pair ? core_launch(arith, op, bn, p, grid, s)
-                          : (arith == AR_TF32X3 ? ((bn == 256 && !rt_env().no_x3tm) ? x3tm_launch(op, p, grid, s) : x3pair_launch(op, bn, p, grid, s))
+                          : (arith == AR_TF32X3 ? (p.b_pre ? x3tm_launch(op, p, grid, s) : x3pair_launch(op, bn, p, grid, s))
                                                 : (pair2 ? pair2_launch(arith, op, p, grid, s) : pair_launch(arith, op, p, grid, s)));
     if (e == cudaSuccess && partials) {
         e = splitk_finalize_launch(partials, ld_part, slab_rows, p.splits, final_p, s);
@@ -401,44 +401,20 @@ bool presplit_worthwhile(int un, int prec, long long M, long long b_bytes) {
     return un == 256 && prec != T2SP_PRECISION_TF32 && !rt_env().no_x3tm && !rt_env().no_presplit && (M + 255) / 256 >= 16 &&
            b_bytes > 0 && b_bytes <= (64ll << 20);
 }
-// K-major B [rows][cols] (TTM's factor, B of a GEMM with trans_b): pre-pass into scratch and the map the kernel loads
-// one [128 rows][32 bf16(b) | 32 bf16(lo_b)] tile per k-block with. Leaves p.b_pre = 0 when anything is in the way.
-void presplit_b_kmajor(Views& vw, CoreParams& p, const char* pb, int64_t ldb_bytes, int rows, int cols) {
-    const int num_kb = (cols + 31) / 32;
-    const size_t pitch = size_t(num_kb) * 128;
-    if (vw.n >= 8) return;
-    void* scratch = rt_alloc(pitch * rows);
+// Runs the pre-pass that writes B's slot images into scratch and points the kernel at them. Leaves p.b_pre = 0 (the
+// kernel then loads B through mapB and splits it itself) when anything is in the way.
+void prepack_b(Views& vw, CoreParams& p, BImageParams q, int n_tiles256) {
+    q.halves = 2 * n_tiles256;
+    const size_t bytes = size_t(q.num_kb) * q.halves * 32768;
+    if (vw.n >= 8 || bytes == 0 || bytes > (size_t(256) << 20)) return;
+    void* scratch = rt_alloc(bytes);
     if (!scratch) return;
     vw.v[vw.n].ptr = scratch; vw.v[vw.n].borrowed = false; vw.n++;
-    if (presplit_kmajor_launch(pb, ldb_bytes / 4, rows, cols, scratch, rt_stream()) != cudaSuccess) { cudaGetLastError(); return; }
+    if (b_images_launch(q, scratch, rt_stream()) != cudaSuccess) { cudaGetLastError(); return; }
     rt_count_launch(1);
-    uint64_t dims[2] = {uint64_t(num_kb) * 64, uint64_t(rows)}, str[2] = {2, uint64_t(pitch)};
-    uint32_t box[2] = {64, 128};
-    if (rt_encode_tmap(&p.mapB2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, scratch, dims, str, box)) p.b_pre = 1;
-}
-// MN-major B of any rank (B of a plain GEMM, conv weights): element-by-element pre-pass over B's span into two bf16
-// arrays with B's own index structure; `dims` / `str_bytes` are those of the fp32 map, the box is 64 columns x 32
-// contraction values. Needs every outer fp32 stride to be a multiple of 32 bytes (16 after halving).
-void presplit_b_mnmajor(Views& vw, CoreParams& p, const char* pb, long long span_elems, int rank, const uint64_t* dims,
-                        const uint64_t* str_bytes, const uint32_t* box) {
-    if (vw.n + 2 > 8 || span_elems <= 0) return;
-    uint64_t str2[5] = {2, 0, 0, 0, 0};
-    for (int d = 1; d < rank; ++d) {
-        if (str_bytes[d] % 32) return;
-        str2[d] = str_bytes[d] / 2;
-    }
-    const size_t bytes = (size_t(span_elems) * 2 + 255) / 256 * 256;
-    void* hb = rt_alloc(bytes);
-    if (!hb) return;
-    vw.v[vw.n].ptr = hb; vw.v[vw.n].borrowed = false; vw.n++;
-    void* lb = rt_alloc(bytes);
-    if (!lb) return;
-    vw.v[vw.n].ptr = lb; vw.v[vw.n].borrowed = false; vw.n++;
-    if (presplit_elem_launch(pb, span_elems, hb, lb, rt_stream()) != cudaSuccess) { cudaGetLastError(); return; }
-    rt_count_launch(1);
-    if (rt_encode_tmap(&p.mapB2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, hb, dims, str2, box) &&
-        rt_encode_tmap(&p.mapB3, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, lb, dims, str2, box))
-        p.b_pre = 1;
+    p.b_images = scratch;
+    p.b_halves = q.halves;
+    p.b_pre = 1;
 }
 
 uint32_t idesc_for(int arith, uint32_t in_type, bool b_mn_major, int bn) {
@@ -744,14 +720,17 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
             uint64_t dims[2] = {uint64_t(K), uint64_t(N)}, str[2] = {uint64_t(es), uint64_t(ldb2)};
             uint32_t box[2] = {uint32_t(bk), uint32_t(pair ? bn / 2 : bn)};
             if (!rt_encode_tmap(&p.mapB, tmap_type(in_t), 2, pb, dims, str, box)) return tma_unsupported("B");
-            if (presplit_worthwhile(x3un, prec, M, int64_t(N) * ldb2)) presplit_b_kmajor(vw, p, pb, ldb2, N, K);
+            if (presplit_worthwhile(x3un, prec, M, int64_t(N) * ldb2)) {
+                BImageParams q{reinterpret_cast<const float*>(pb), 1, ldb2 / 4, K, N, (K + 31) / 32, 0, 0, 0};
+                prepack_b(vw, p, q, (N + 255) / 256);
+            }
         } else {
             uint64_t dims[2] = {uint64_t(N), uint64_t(K)}, str[2] = {uint64_t(es), uint64_t(ldb2)};
             uint32_t box[2] = {uint32_t(128 / es), uint32_t(bk)};
             if (!rt_encode_tmap(&p.mapB, tmap_type(in_t), 2, pb, dims, str, box, arith == AR_TF32X3)) return tma_unsupported("B");
             if (presplit_worthwhile(x3un, prec, M, int64_t(K) * ldb2)) {
-                uint32_t box16[2] = {64, 32};
-                presplit_b_mnmajor(vw, p, pb, (ldb2 / 4) * (int64_t(K) - 1) + N, 2, dims, str, box16);
+                BImageParams q{reinterpret_cast<const float*>(pb), 0, ldb2 / 4, K, N, (K + 31) / 32, 0, 0, 0};
+                prepack_b(vw, p, q, (N + 255) / 256);
             }
         }
         p.M = M; p.N = N; p.tile_rows = kBlockM; p.a_tx_bytes = kBlockM * 128;
@@ -908,7 +887,10 @@ extern "C" int t2sp_b200_ttm(halide_buffer_t* a, halide_buffer_t* b, halide_buff
             uint64_t dims[2] = {uint64_t(L), uint64_t(N)}, str[2] = {4, uint64_t(ldb)};
             uint32_t box[2] = {32, uint32_t(x3un ? bn / 2 : bn)};
             if (!rt_encode_tmap(&p.mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, pb, dims, str, box)) return tma_unsupported("b");
-            if (presplit_worthwhile(x3un, prec, M, int64_t(N) * ldb)) presplit_b_kmajor(vw, p, pb, ldb, N, L);
+            if (presplit_worthwhile(x3un, prec, M, int64_t(N) * ldb)) {
+                BImageParams q{reinterpret_cast<const float*>(pb), 1, ldb / 4, L, N, (L + 31) / 32, 0, 0, 0};
+                prepack_b(vw, p, q, (N + 255) / 256);
+            }
         }
         p.M = M; p.N = N; p.tile_rows = kBlockM; p.a_tx_bytes = kBlockM * 128;
         p.single_pass = prec == T2SP_PRECISION_TF32;
@@ -1059,10 +1041,8 @@ extern "C" int t2sp_b200_conv(halide_buffer_t* I, halide_buffer_t* K, halide_buf
     const int x3un = x3_pair_width(p.M, CO, p.tile_rows, p.num_kb);
     if (x3un) bn = x3un;
     if (presplit_worthwhile(x3un, prec, p.M, int64_t(CI) * KY * t1)) {
-        uint64_t dims[4] = {uint64_t(CO), uint64_t(KX), uint64_t(CI), uint64_t(KY)};
-        uint64_t str[4] = {4, uint64_t(CO) * 4, uint64_t(t1), uint64_t(CI) * uint64_t(t1)};
-        uint32_t box16[4] = {64, 1, 32, 1};
-        presplit_b_mnmajor(vw, p, pk, (t1 / 4) * (int64_t(CI) * KY - 1) + int64_t(CO) * KX, 4, dims, str, box16);
+        BImageParams q{reinterpret_cast<const float*>(pk), 2, t1 / 4, CI, CO, p.num_kb, 0, p.cblks, KY};
+        prepack_b(vw, p, q, (CO + 255) / 256);
     }
     p.tiles_m = x3un ? (p.M + 255) / 256 : (p.M + p.tile_rows - 1) / p.tile_rows; p.tiles_n = (CO + bn - 1) / bn;
     p.idesc = x3un ? make_instr_desc(1, 2, false, true, 256, bn) : idesc_for(AR_TF32X3, kF32, true, bn);

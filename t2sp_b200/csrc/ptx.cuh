@@ -151,6 +151,12 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const void* map, uin
 // ---------------------------------------------------------------- TMA stores (shared -> global, tiled mode)
 // The box is clipped to the tensor's extents, so ragged edges need no masking. The issuing
 // thread tracks completion through its bulk async-groups.
+// Plain (untiled) bulk copy global -> shared: both addresses 16-byte aligned, size a multiple of 16 bytes.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
 __device__ __forceinline__ void tma_store_2d(const void* map, const void* src, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
                      reinterpret_cast<uint64_t>(map)),

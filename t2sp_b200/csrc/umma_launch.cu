@@ -36,32 +36,59 @@ __device__ __forceinline__ uint32_t presplit_pack(float a, float b) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<const uint32_t*>(&v);
 }
-// K-major operand (rows of `cols` contraction values): row n of the result holds, per block of 32 contraction
-// values, 32 bf16(x) (64 bytes) followed by 32 bf16(lo) (64 bytes); values beyond `cols` are zero. One thread per
-// group of four values.
-__global__ void presplit_kmajor_kernel(const float* __restrict__ src, long long ld_src, int rows, int cols, int num_kb,
-                                       uint8_t* __restrict__ dst) {
+// Writes, for every k-block and every 128-column half tile of B, the 32 KB image of the kernel's B slot: the raw
+// fp32 tile as TMA would have laid it out (16 KB) followed by the bf16 tile [bf16(b) | bf16(lo_b)] (16 KB). One
+// thread per 16-byte piece of the raw tile (four consecutive N values of an MN-major B, four consecutive K values of
+// a K-major one); elements outside B are zero.
+__global__ void b_images_kernel(const BImageParams q, uint8_t* __restrict__ dst) {
     const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
-    const int groups = num_kb * 8;
-    if (idx >= static_cast<long long>(rows) * groups) return;
-    const int n = static_cast<int>(idx / groups), g = static_cast<int>(idx % groups), k0 = g * 4;
-    const float* s = src + n * ld_src + k0;
-    float v[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = k0 + j < cols ? s[j] : 0.f;
-    uint8_t* d = dst + (static_cast<long long>(n) * num_kb + (g >> 3)) * 128 + (g & 7) * 8;
-    *reinterpret_cast<uint2*>(d) = make_uint2(presplit_pack(v[0], v[1]), presplit_pack(v[2], v[3]));
-    *reinterpret_cast<uint2*>(d + 64) = make_uint2(presplit_pack(presplit_lo(v[0]), presplit_lo(v[1])),
-                                                   presplit_pack(presplit_lo(v[2]), presplit_lo(v[3])));
-}
-// Any layout, element by element: hb[i] = bf16(src[i]), lb[i] = bf16(lo(src[i])) for i < count. Two values per thread.
-__global__ void presplit_elem_kernel(const float* __restrict__ src, long long count, uint32_t* __restrict__ hb,
-                                     uint32_t* __restrict__ lb) {
-    const long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * 2;
-    if (i >= count) return;
-    const float a = src[i], b = i + 1 < count ? src[i + 1] : 0.f;
-    hb[i >> 1] = presplit_pack(a, b);
-    lb[i >> 1] = presplit_pack(presplit_lo(a), presplit_lo(b));
+    const long long blobs = static_cast<long long>(q.num_kb) * q.halves;
+    if (idx >= blobs * 1024) return;
+    const int pi = static_cast<int>(idx & 1023);
+    const long long blob = idx >> 10;
+    const int kb = static_cast<int>(blob / q.halves), half = static_cast<int>(blob % q.halves);
+    uint8_t* img = dst + blob * 32768;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    int off_raw, off_hb, off_lb;
+    if (q.mode == 1) {
+        // K-major: row r (an n) holds 32 K values in 128 bytes, 16-byte chunk c stored at c ^ (r & 7); the bf16 tile
+        // keeps the row pitch, bf16(b) in the first 64 bytes of the row, bf16(lo_b) in the second, same swizzle
+        const int r = pi >> 3, c = pi & 7, x = r & 7;
+        const long long n = static_cast<long long>(half) * 128 + r;
+        const int k0 = kb * 32 + 4 * c;
+        if (n < q.N)
+            for (int j = 0; j < 4; ++j)
+                if (k0 + j < q.K) v[j] = q.src[n * q.ld + k0 + j];
+        off_raw = r * 128 + ((c ^ x) << 4);
+        off_hb = 16384 + r * 128 + (((c >> 1) ^ x) << 4) + (c & 1) * 8;
+        off_lb = 16384 + r * 128 + (((4 + (c >> 1)) ^ x) << 4) + (c & 1) * 8;
+    } else {
+        // MN-major: boxes of 32 K rows x 32 N values (128-byte rows) with 32-byte atoms swizzled (atom a of row k
+        // stored at a ^ (k & 3)); the bf16 tiles are boxes of 32 K rows x 64 N values, 16-byte chunk c stored at
+        // c ^ (k & 7), the boxes of bf16(b) first, then those of bf16(lo_b)
+        const int k = pi >> 5, g = pi & 31;
+        const int n = half * 128 + 4 * g;
+        const float* s = nullptr;
+        if (q.mode == 0) {
+            const int kg = kb * 32 + k;
+            if (kg < q.K) s = q.src + static_cast<long long>(kg) * q.ld;
+        } else {
+            const int tap = kb / q.cblks, cb = kb % q.cblks, ky = tap % q.KY, kx = tap / q.KY, ci = cb * 32 + k;
+            if (ci < q.K) s = q.src + static_cast<long long>(q.N) * kx + (static_cast<long long>(ci) + static_cast<long long>(ky) * q.K) * q.ld;
+        }
+        if (s)
+            for (int j = 0; j < 4; ++j)
+                if (n + j < q.N) v[j] = s[n + j];
+        const int jb = g >> 3, a = (g & 7) >> 1, sub = g & 1;
+        off_raw = jb * 4096 + k * 128 + ((((a ^ (k & 3)) << 1) | sub) << 4);
+        const int c8 = (jb & 1) * 4 + a;
+        off_hb = 16384 + (jb >> 1) * 4096 + k * 128 + ((c8 ^ (k & 7)) << 4) + sub * 8;
+        off_lb = off_hb + 8192;
+    }
+    *reinterpret_cast<float4*>(img + off_raw) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<uint2*>(img + off_hb) = make_uint2(presplit_pack(v[0], v[1]), presplit_pack(v[2], v[3]));
+    *reinterpret_cast<uint2*>(img + off_lb) = make_uint2(presplit_pack(presplit_lo(v[0]), presplit_lo(v[1])),
+                                                         presplit_pack(presplit_lo(v[2]), presplit_lo(v[3])));
 }
 
 // One thread per row and four consecutive columns; the sum over the slabs runs in slab order.
@@ -280,20 +307,10 @@ cudaError_t transpose32_launch(const void* src, long long ld_src, void* dst, lon
     return cudaGetLastError();
 }
 
-cudaError_t presplit_kmajor_launch(const void* src, long long ld_src, int rows, int cols, void* dst, cudaStream_t stream) {
-    const int num_kb = (cols + 31) / 32;
-    const long long work = static_cast<long long>(rows) * num_kb * 8;
+cudaError_t b_images_launch(const BImageParams& q, void* dst, cudaStream_t stream) {
+    const long long work = static_cast<long long>(q.num_kb) * q.halves * 1024;
     if (work <= 0) return cudaSuccess;
-    presplit_kmajor_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
-        static_cast<const float*>(src), ld_src, rows, cols, num_kb, static_cast<uint8_t*>(dst));
-    return cudaGetLastError();
-}
-
-cudaError_t presplit_elem_launch(const void* src, long long count, void* hb, void* lb, cudaStream_t stream) {
-    const long long work = (count + 1) / 2;
-    if (work <= 0) return cudaSuccess;
-    presplit_elem_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(
-        static_cast<const float*>(src), count, static_cast<uint32_t*>(hb), static_cast<uint32_t*>(lb));
+    b_images_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(q, static_cast<uint8_t*>(dst));
     return cudaGetLastError();
 }
 

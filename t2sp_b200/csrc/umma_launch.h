@@ -27,7 +27,8 @@ cudaError_t pair2_launch(int arith, int op, const CoreParams& p, int grid, cudaS
 // OP_GEMM / OP_TTM / OP_CONV / OP_CAPSULE; `grid` must be even, tiles count 256 x un tiles and
 // p.idesc describes a 256 x un TF32 MMA.
 cudaError_t x3pair_launch(int op, int un, const CoreParams& p, int grid, cudaStream_t stream);
-// The 256-column pair tile with the A operand in tensor memory and the cross terms as bf16 MMAs (umma_x3tm.cuh).
+// The 256-column pair tile with the A operand in tensor memory, B pre-packed by b_images_launch (p.b_pre) and the
+// cross terms as bf16 MMAs (umma_x3tm.cuh); GEMM, TTM and conv.
 cudaError_t x3tm_launch(int op, const CoreParams& p, int grid, cudaStream_t stream);
 
 // Launches the accumulate-then-scale MTTKRP kernel (umma_mttkrp.cuh; R <= 64) with `grid` persistent CTAs over the
@@ -39,11 +40,17 @@ cudaError_t mttkrp2_launch(const CoreParams& p, int grid, cudaStream_t stream);
 cudaError_t transpose32_launch(const void* src, long long ld_src, void* dst, long long ld_dst, int rows, int cols,
                                cudaStream_t stream, int batch = 1, long long bs_src = 0, long long bs_dst = 0);
 
-// Pre-pass for the fp32 pair kernel's pre-split B. K-major operand [rows][cols] (row pitch ld_src elements) ->
-// [rows][ceil(cols / 32)][32 bf16(x) | 32 bf16(lo)] (128 bytes per row and k-block, zero beyond cols).
-cudaError_t presplit_kmajor_launch(const void* src, long long ld_src, int rows, int cols, void* dst, cudaStream_t stream);
-// Element by element over `count` fp32 values: hb[i] = bf16(src[i]), lb[i] = bf16(src[i] - trunc_tf32(src[i])).
-cudaError_t presplit_elem_launch(const void* src, long long count, void* hb, void* lb, cudaStream_t stream);
+// Pre-pass of the fp32 pair kernel with its A operand in tensor memory (umma_x3tm.cuh): the 32 KB slot images of B,
+// [k-block][128-column half tile][raw fp32 tile | bf16(b), bf16(lo_b) tile], for an operand many row tiles re-read.
+struct BImageParams {
+    const float* src;
+    int mode;        // 0: MN-major B[k][n]; 1: K-major B[n][k]; 2: conv weights (co, kx, ci, ky)
+    long long ld;    // elements between rows (mode 0: k rows, mode 1: n rows, mode 2: between channels ci)
+    int K, N;        // contraction extent (mode 2: CI, per tap) and columns (mode 2: CO)
+    int num_kb, halves;
+    int cblks, KY;   // mode 2: k-block = (tap = ky + KY * kx) * cblks + channel block
+};
+cudaError_t b_images_launch(const BImageParams& q, void* dst, cudaStream_t stream);
 
 // Number of SMs of the current device (cached).
 int core_sm_count();

@@ -56,7 +56,6 @@ struct RowSpace {
 struct CoreParams {
     CUtensorMap mapA[4];
     CUtensorMap mapB;
-    CUtensorMap mapB2, mapB3;  // fp32 pair kernel with a pre-split B: bf16(b) [| bf16(lo_b)] and (MN-major B) bf16(lo_b)
     CUtensorMap mapC;  // EPI_TMA: row-major output as (N, M), box 32 columns x 32 rows, 128-byte swizzle; with tma_t (M, N), 32 rows x 32 columns, no swizzle
     int M, N;         // GEMM-view extents of the output
     int tile_rows;    // output rows per tile (128 unless the row boxes cannot fill a tile)
@@ -67,7 +66,9 @@ struct CoreParams {
     int group_m;      // row-blocks per rasterisation group (tile order, L2 reuse)
     uint32_t idesc;   // tcgen05 instruction descriptor
     int epi;          // EPI_*
-    int b_pre;        // fp32 pair kernel: B's bf16 tiles come from a pre-pass (mapB2, mapB3)
+    int b_pre;        // fp32 pair kernel: B comes as the 32 KB slot images a pre-pass wrote (b_images), not through mapB
+    int b_halves;     // 128-column half tiles per k-block in b_images (2 x tiles_n)
+    const void* b_images;  // [k-block][half tile][raw fp32 tile 16 KB | bf16(b), bf16(lo_b) tile 16 KB]
     int tma_t;        // EPI_TMA on a column-major output: mapC is (M, N) with m innermost, the staged tile is transposed
     void* out;        // fp32 or int32 elements
     long long ldo;    // EPI_ROWMAJOR: row pitch; EPI_COLMAJOR: column pitch (elements)

@@ -221,10 +221,12 @@ def test_fp32_split_k(lib, M, N, K, trans_b, force):
 
 
 @pytest.mark.parametrize("M,N,K,trans_b", [(9728, 256, 96, 0), (9728, 264, 200, 0), (9728, 256, 100, 1), (5120, 500, 640, 1)])
-def test_fp32_pair_presplit_b_is_bit_identical(lib, M, N, K, trans_b):
-    """fp32 pair kernel with A in tensor memory: with many row tiles over one B, the bf16 operands of the cross-term
-    MMAs (bf16(b), bf16(b - tf32(b))) come from a pre-pass over B instead of from the split warps, tile by tile.
-    Same values either way, so the same bits out; one launch more. K = 100 / 200 end inside a k-block."""
+def test_fp32_pair_prepacked_b(lib, M, N, K, trans_b):
+    """With many 256-row tiles over one B, the fp32 pair kernel with its A operand in tensor memory runs: a pre-pass
+    writes B's shared-memory tile images (raw fp32 and the bf16 operands of the cross-term MMAs) once, the kernel
+    fetches them with one bulk copy per k-block and carries the cross terms at bf16 rate. Same tolerance as the
+    all-TF32 kernel, which the same call uses when the pre-pass is switched off; one launch more.
+    K = 100 / 200 end inside a k-block, N = 264 / 500 inside a tile."""
     import t2sp_b200
     from t2sp_b200 import Buffer, GemmDesc
     A, B = O.uniform(21, 1, (M, K)), O.uniform(21, 2, (K, N))
@@ -240,8 +242,14 @@ def test_fp32_pair_presplit_b_is_bit_identical(lib, M, N, K, trans_b):
             outs.append((cb.keepalive.copy(), lib.t2sp_b200_kernel_launches() - before))
     (pre, n_pre), (plain, n_plain) = outs
     assert n_pre == n_plain + 1, "the pre-pass is a launch of its own"
-    assert np.array_equal(pre, plain)
-    assert normwise(pre, O.gemm_f32(A, B, acc64=True)) <= TOL_FP32
+    truth = O.gemm_f32(A, B, acc64=True)
+    absprod = O.gemm_f32(np.abs(A), np.abs(B), acc64=True)
+    assert not np.isnan(pre).any()
+    for got in (pre, plain):
+        assert normwise(got, truth) <= TOL_FP32
+        assert componentwise(got, truth, absprod) <= TOL_FP32
+    print(f"fp32 pair, pre-packed B {M}x{N}x{K}: componentwise {componentwise(pre, truth, absprod):.3e} "
+          f"(all-TF32 kernel {componentwise(plain, truth, absprod):.3e})")
 
 
 def test_fp32_split_k_tiled_layout_and_blas_epilogue(lib):
