@@ -24,7 +24,7 @@
 //   A slots    4 x 64 columns of tensor memory [hi 32 | bf16(a) 16 | bf16(lo_a) 16], handed back by the MMAs' commit
 //
 // Per CTA: 16 warps as in umma_x3pair.cuh.
-//   warp 0      producer (own 128 A rows, own 128 of the 256 B columns); A is issued kALead k-blocks ahead of B
+//   warp 0      producer (own 128 A rows, own 128 of the 256 B columns); serves the A and the B queue as they open
 //   warp 1      MMA issuer (leader CTA only), TMEM owner
 //   warps 2-3, 12-15  split warps. A warp may touch only the TMEM lanes of its quarter (warp % 4), so the A tile goes
 //               by quarters: warps 12 and 13 take the rows of quarters 0 and 1, warps 2 / 14 and 3 / 15 share
@@ -52,7 +52,6 @@ struct X3TmCfg {
     static constexpr int kBSlotBytes = 2 * kBBytes;
     static constexpr int kAStages = 4;
     static constexpr int kBSlots = 4;
-    static constexpr int kALead = 2;                   // how many k-blocks A's copies are issued ahead of B's
     static constexpr int kTSlots = 4;                  // A slots in tensor memory
     static constexpr int kBoxBytesMn = 32 * 128;       // MN-major fp32 box: 32 k-rows x 32 columns
     static constexpr int kBoxesMn = kBBytes / kBoxBytesMn;
@@ -266,12 +265,16 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
             wa.t = wb.t = pair;
             tile_setup(wa, true);
             tile_setup(wb, false);
+            // The two queues are served as they open, neither waits for the other: a copy of A needs a stage the
+            // split warps have read, a copy of B a slot whose MMAs have retired, and which of the two comes first
+            // changes with how far the split warps are ahead of the MMAs.
             int ia = 0, ib = 0;
             bool ok = true;
-            while (wb.t < num_tiles && ok) {
-                while (wa.t < num_tiles && ia <= ib + Cfg::kALead) {
+            long long idle_since = -1;
+            while ((wa.t < num_tiles || wb.t < num_tiles) && ok) {
+                bool progressed = false;
+                if (wa.t < num_tiles && ptx::mbar_test_wait(&aempty_bar[ia % NA], ((ia / NA) & 1) ^ 1)) {
                     const int s = ia % NA;
-                    if (!bounded_wait(&aempty_bar[s], ((ia / NA) & 1) ^ 1, ab, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
                     uint8_t* sa = smem + s * Cfg::kABytes;
                     T2SP_TRACE(p, 0, ia);
                     ptx::mbar_expect_tx(&afull_bar[s], Cfg::kABytes);
@@ -305,19 +308,36 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
                     }
                     ++ia;
                     advance(wa, true);
+                    progressed = true;
                 }
-                if (!ok) break;
-                const int sl = ib % NB;
-                if (!bounded_wait(&bfree_bar[sl], ((ib / NB) & 1) ^ 1, ab, ST_TIMEOUT_PRODUCER)) { ok = false; break; }
-                T2SP_TRACE(p, 22, ib);
-                // the pre-pass wrote, per k-block and half tile, the 32 KB image of the slot
-                ptx::mbar_expect_tx(&bfull_bar[sl], Cfg::kBSlotBytes);
-                ptx::bulk_load(b_ring + sl * Cfg::kBSlotBytes,
-                               static_cast<const uint8_t*>(p.b_images) +
-                                   (static_cast<size_t>(wb.kb) * p.b_halves + wb.half) * Cfg::kBSlotBytes,
-                               Cfg::kBSlotBytes, &bfull_bar[sl]);
-                ++ib;
-                advance(wb, false);
+                if (wb.t < num_tiles && ptx::mbar_test_wait(&bfree_bar[ib % NB], ((ib / NB) & 1) ^ 1)) {
+                    const int sl = ib % NB;
+                    T2SP_TRACE(p, 22, ib);
+                    // the pre-pass wrote, per k-block and half tile, the 32 KB image of the slot
+                    ptx::mbar_expect_tx(&bfull_bar[sl], Cfg::kBSlotBytes);
+                    ptx::bulk_load(b_ring + sl * Cfg::kBSlotBytes,
+                                   static_cast<const uint8_t*>(p.b_images) +
+                                       (static_cast<size_t>(wb.kb) * p.b_halves + wb.half) * Cfg::kBSlotBytes,
+                                   Cfg::kBSlotBytes, &bfull_bar[sl]);
+                    ++ib;
+                    advance(wb, false);
+                    progressed = true;
+                }
+                if (progressed) {
+                    idle_since = -1;
+                } else {
+                    // bounded like every other wait: give up when neither queue has opened for the limit
+                    const long long now = clock64();
+                    if (idle_since < 0) idle_since = now;
+                    if (*ab.flag) { ok = false; break; }
+                    if (now - idle_since > ab.limit) {
+                        *ab.flag = 1u;
+                        atomicOr(ab.status, ST_TIMEOUT_PRODUCER);
+                        ok = false;
+                        break;
+                    }
+                    __nanosleep(64);
+                }
             }
         } else if (warp >= 2) {
             split_role(warp, 0, std::integral_constant<int, 1>{});  // quarters 2 and 3, first half of the k-block

@@ -252,6 +252,38 @@ def test_fp32_pair_prepacked_b(lib, M, N, K, trans_b):
           f"(all-TF32 kernel {componentwise(plain, truth, absprod):.3e})")
 
 
+@pytest.mark.parametrize("dist", ["uniform", "positive"])
+def test_fp32_bf16_cross_terms_bound_k8192(lib, dist):
+    """Known-answer check of the error bound of the bf16 cross terms (a = hi + lo: hi_a hi_b in TF32, bf16(lo_a) bf16(b)
+    and bf16(a) bf16(lo_b) in bf16; each product off by at most about 2^-18 |a||b|): a long contraction, K = 8192,
+    against the fp64-accumulated oracle, elementwise relative to sum_k |a||b|, on inputs of mixed sign and on the
+    positive distribution of the reference's own drivers (where every rounding error has the same sign and nothing
+    cancels in the result either). The all-TF32 kernel on the same inputs is printed beside it."""
+    import t2sp_b200
+    from t2sp_b200 import Buffer
+    M, N, K = 4864, 256, 8192
+    A, B = O.uniform(31, 1, (M, K)), O.uniform(31, 2, (K, N))
+    if dist == "positive":
+        A, B = np.abs(A), np.abs(B)
+    truth = O.gemm_f32(A, B, acc64=True)
+    absprod = O.gemm_f32(np.abs(A), np.abs(B), acc64=True)
+    errs = []
+    for env in ({}, {"T2SP_B200_NO_PRESPLIT": "1"}):
+        with library_env(**env):
+            cb = Buffer.from_numpy(np.full((M, N), np.nan, np.float32))
+            before = lib.t2sp_b200_kernel_launches()
+            assert t2sp_b200.gemm(Buffer.from_numpy(A), Buffer.from_numpy(B), cb) == 0
+            launches = lib.t2sp_b200_kernel_launches() - before
+            got = cb.keepalive
+            assert not np.isnan(got).any()
+            errs.append((componentwise(got, truth, absprod), normwise(got, truth), launches))
+    (cw, nw, n_pre), (cw_tf32, nw_tf32, n_plain) = errs
+    print(f"K=8192 {dist}: bf16 cross terms componentwise {cw:.3e} normwise {nw:.3e}; all TF32 {cw_tf32:.3e} / {nw_tf32:.3e}")
+    assert n_pre == n_plain + 1, "the first call ran the pre-pass and the tensor-memory kernel"
+    assert cw <= TOL_FP32 and nw <= TOL_FP32
+    assert cw_tf32 <= TOL_FP32 and nw_tf32 <= TOL_FP32
+
+
 def test_fp32_split_k_tiled_layout_and_blas_epilogue(lib):
     """The summing kernel applies the call's own epilogue: the 6-D tiled layout and alpha/beta.
     (Split-K is forced: by itself the library avoids it for tiled layouts, whose summing pass is dear.)"""
