@@ -13,8 +13,24 @@ cudaError_t launch_x3tm(const CoreParams& p, int grid, cudaStream_t stream) {
     auto kern = umma_x3tm_kernel<OP>;
     static std::atomic<bool> configured[kMaxDev];
     if (cudaError_t e = allow_smem(kern, Cfg::kSmemBytes, configured)) return e;
+#ifdef T2SP_X3TM_NO_PDL
     kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
     return cudaGetLastError();
+#else
+    // programmatic stream serialization: the grid is set up while the pre-pass that writes B's images still runs; the
+    // kernel's producer waits for that grid before its first copy of B, everything before that overlaps
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(Cfg::kThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, p);
+#endif
 }
 }  // namespace
 

@@ -41,6 +41,7 @@ __device__ __forceinline__ uint32_t presplit_pack(float a, float b) {
 // thread per 16-byte piece of the raw tile (four consecutive N values of an MN-major B, four consecutive K values of
 // a K-major one); elements outside B are zero.
 __global__ void b_images_kernel(const BImageParams q, uint8_t* __restrict__ dst) {
+    ptx::grid_dep_launch();  // the contraction kernel may set itself up meanwhile; it waits for this grid before it reads an image
     const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
     const long long blobs = static_cast<long long>(q.num_kb) * q.halves;
     if (idx >= blobs * 1024) return;

@@ -261,6 +261,7 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
                     }
                 }
             };
+            bool b_images_ready = false;  // the pre-pass that wrote them may still be running when this grid starts
             Walk wa, wb;
             wa.t = wb.t = pair;
             tile_setup(wa, true);
@@ -312,6 +313,7 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
                 }
                 if (wb.t < num_tiles && ptx::mbar_test_wait(&bfree_bar[ib % NB], ((ib / NB) & 1) ^ 1)) {
                     const int sl = ib % NB;
+                    if (!b_images_ready) { ptx::grid_dep_wait(); b_images_ready = true; }
                     T2SP_TRACE(p, 22, ib);
                     // the pre-pass wrote, per k-block and half tile, the 32 KB image of the slot
                     ptx::mbar_expect_tx(&bfull_bar[sl], Cfg::kBSlotBytes);
