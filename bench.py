@@ -286,6 +286,10 @@ def run_reference(args, kind, w, name):
 SIDE_WORKLOADS = ["sgemm_1024", "conv_cfg2", "ttm_cfg3", "mttkrp_cfg3", "capsule_cfg4", "gemm_bf16_4096",
                   "gemm_bf16_16384", "gemm_i8_8192"]
 RATE = {"bf16": 1.0, "f16": 1.0, "i8": 2.0, "f32": 1.0 / 6.0}  # tensor ceiling relative to the bf16 peak
+# fp32 workloads that run on the pair kernel with the A operand in tensor memory (many row tiles over one B): per 32
+# contraction values four TF32 MMAs (hi * hi) and four bf16 MMAs (the cross terms) where a bf16 GEMM issues two, so the
+# ceiling is a quarter of the bf16 peak instead of the sixth of three TF32 passes
+BF16_CROSS_TERMS = {"conv_cfg2", "ttm_cfg3"}
 
 
 class Resident:
@@ -362,7 +366,7 @@ def roofline_of(name, kernel_ms, long_run=False):
     kind, w = WORKLOADS[name]
     flops, abytes = flops_bytes(kind, w)
     pk = peaks()
-    scale = RATE[w.get("dtype", "f32")]
+    scale = 0.25 if name in BF16_CROSS_TERMS else RATE[w.get("dtype", "f32")]
     t_hbm = abytes / (pk["hbm"] * 1e9)
     t_tensor = flops / (pk["burst"] * scale * 1e12)
     if t_hbm > t_tensor:
@@ -372,7 +376,8 @@ def roofline_of(name, kernel_ms, long_run=False):
         bf16_peak = pk["sustained"] if long_run else pk["burst"]
         achieved, peak, unit, bound = flops / (kernel_ms * 1e-3) / 1e12, bf16_peak * scale, "TFLOP/s", "tensor"
         note = (f"{pk['src']} cuBLAS bf16 {'sustained' if long_run else 'burst'} {bf16_peak} TFLOP/s"
-                + {1.0: "", 2.0: " x2 (int8 rate)", 1.0 / 6.0: " /2 (tf32 rate) /3 (three MMAs per product)"}[scale])
+                + {1.0: "", 2.0: " x2 (int8 rate)", 1.0 / 6.0: " /2 (tf32 rate) /3 (three MMAs per product)",
+                   0.25: " /4 (one TF32 pass = two bf16 passes, plus two bf16 passes for the cross terms)"}[scale])
     return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak,
             "traffic": KNOWN_TRAFFIC.get(name), "peak_source": note, "kernel_ms": kernel_ms,
             "algorithmic_flops": flops, "algorithmic_bytes": abytes}
@@ -628,8 +633,9 @@ KNOWN_TRAFFIC = {
     # profiles/fp32_3xtf32_kernels_conv_ttm_mttkrp_capsule_sgemm_full.md
     "gemm_bf16_4096": 94957312 + 32456192,
     "gemm_i8_4096": 35462400 + 18725376,
-    "conv_cfg2": 19220480 + 142336,
-    "ttm_cfg3": 268876800 + 218153984,
+    # profiles/fp32_x3tm_kernel_ttm_conv_full.md
+    "conv_cfg2": 21600256 + 485888,
+    "ttm_cfg3": 269131520 + 217162752,
     # profiles/mttkrp_cfg3_mttkrp2_kernel_full.md
     "mttkrp_cfg3": 537191168 + 4868352,
     "capsule_cfg4": 21994496 + 7168,
