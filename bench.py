@@ -42,6 +42,7 @@ WORKLOADS = {
     "conv_cfg2": ("conv", dict(N=64, CI=256, CO=256, KY=3, KX=3, OY=14, OX=14)),
     "ttm_cfg3": ("ttm", dict(L=256, I=512, J=512, K=256)),
     "mttkrp_cfg3": ("mttkrp", dict(L=512, I=512, K=512, R=64)),
+    "sgemm_n128": ("gemm", dict(M=32768, N=128, K=1152, dtype="f32")),  # the GEMM shape of capsule_cfg4
     "capsule_cfg4": ("capsule", dict(N=1, NN=32, CI=32, CII=32, CO=32, KY=3, KX=3, OY=16, OX=16, s=1)),
     # the GER design's A10 constants with its 32 x 32 outer loops: 10240 x 16384 elements
     "ger_a10": ("ger", dict(KKK=16, III=10, II=32, KK=32, K=32, I=32)),

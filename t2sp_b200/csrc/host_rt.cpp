@@ -68,6 +68,7 @@ const Env* read_env() {
     e->log = getenv("T2SP_B200_LOG") != nullptr;
     e->mttkrp_v1 = getenv("T2SP_B200_MTTKRP_V1") != nullptr;
     e->no_x3tm = getenv("T2SP_B200_NO_X3TM") != nullptr;
+    e->no_tm128 = getenv("T2SP_B200_NO_TM128") != nullptr;
     e->no_presplit = getenv("T2SP_B200_NO_PRESPLIT") != nullptr;
     if (const char* f = getenv("T2SP_B200_SPLITK")) e->splitk = std::max(1, atoi(f));
     e->precision = T2SP_PRECISION_TF32X3;

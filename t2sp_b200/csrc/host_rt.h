@@ -49,6 +49,7 @@ ThreadState& tls();
 struct Env {
     bool no_tma_store = false, no_pair = false, pair128 = false, no_splitk = false, no_pipeline = false, log = false;
     bool no_presplit = false;  // fp32 pair kernel: B's bf16 tiles always from the split warps, never from a pre-pass
+    bool no_tm128 = false;     // fp32 outputs of exactly 128 columns never on the 256 x 128 form of the tensor-memory pair kernel
     bool no_x3tm = false;      // fp32 pair tiles through the all-shared-memory 3xTF32 kernel instead of the tensor-memory one
     bool mttkrp_v1 = false;    // MTTKRP through the Khatri-Rao-tile kernel even where the accumulate-then-scale kernel applies
     int splitk = 0;            // forced number of split-K ranges of the fp32 pair kernel, 0 = choose

@@ -7,10 +7,10 @@
 namespace t2sp {
 
 namespace {
-template <int OP>
+template <int OP, int UN>
 cudaError_t launch_x3tm(const CoreParams& p, int grid, cudaStream_t stream) {
-    using Cfg = X3TmCfg<OP>;
-    auto kern = umma_x3tm_kernel<OP>;
+    using Cfg = X3TmCfg<OP, UN>;
+    auto kern = umma_x3tm_kernel<OP, UN>;
     static std::atomic<bool> configured[kMaxDev];
     if (cudaError_t e = allow_smem(kern, Cfg::kSmemBytes, configured)) return e;
 #ifdef T2SP_X3TM_NO_PDL
@@ -34,13 +34,19 @@ cudaError_t launch_x3tm(const CoreParams& p, int grid, cudaStream_t stream) {
 }
 }  // namespace
 
-cudaError_t x3tm_launch(int op, const CoreParams& p, int grid, cudaStream_t stream) {
+cudaError_t x3tm_launch(int op, int un, const CoreParams& p, int grid, cudaStream_t stream) {
     if (!p.b_pre || !p.b_images) return cudaErrorInvalidValue;
-    switch (op) {
-        case OP_GEMM: return launch_x3tm<OP_GEMM>(p, grid, stream);
-        case OP_TTM: return launch_x3tm<OP_TTM>(p, grid, stream);
-        case OP_CONV: return launch_x3tm<OP_CONV>(p, grid, stream);
-    }
+#define T2SP_X3TM(OPC, UNV) \
+    if (op == OPC && un == UNV) return launch_x3tm<OPC, UNV>(p, grid, stream)
+    T2SP_X3TM(OP_GEMM, 256);
+    T2SP_X3TM(OP_GEMM, 128);
+    T2SP_X3TM(OP_TTM, 256);
+    T2SP_X3TM(OP_TTM, 128);
+    T2SP_X3TM(OP_CONV, 256);
+    T2SP_X3TM(OP_CONV, 128);
+    T2SP_X3TM(OP_CAPSULE, 256);
+    T2SP_X3TM(OP_CAPSULE, 128);
+#undef T2SP_X3TM
     return cudaErrorInvalidValue;
 }
 

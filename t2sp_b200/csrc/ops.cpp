@@ -193,11 +193,12 @@ void add_digit(Digits& d, int div, int mod, long long stride) { add_digit2(d, di
 // fp32 contractions move to CTA pairs (256 x 256 or 256 x 128 tiles) when such tiles, cut along the
 // contraction where that pays (x3_pick_splits), occupy most SM pairs; returns the pair tile width or 0.
 int x3_pick_splits(int tiles, int total_kb, bool scatter = false);
-int x3_pair_width(long long M, int N, int tile_rows, int num_kb) {
+int x3_pair_width(long long M, int N, int tile_rows, int num_kb, bool tm128 = false) {
     // 256 x 128 pair tiles did not beat the single-CTA kernel (capsule, N = 128: 133 us vs 108 us), so
     // pairs are used for wide outputs only unless $T2SP_B200_PAIR128 asks otherwise.
     if (rt_env().no_pair || tile_rows != kBlockM || N < 128) return 0;
-    if (N <= 128 && !rt_env().pair128) return 0;
+    // (tm128: the caller would run the 128-column form of the tensor-memory kernel, which is another matter)
+    if (N <= 128 && !rt_env().pair128 && !tm128) return 0;
     const int un = N > 128 ? 256 : 128;
     const long long tiles = ((M + 255) / 256) * ((N + un - 1) / un);
     if (tiles > (1 << 20)) return un;
@@ -319,7 +320,7 @@ int run_core(const char* who, int arith, int op, int bn, CoreParams& p, bool syn
     if (pair) grid = 2 * std::max(1, std::min(items, core_sm_count() / 2));  // one cluster of 2 CTAs per work item slot
     if (sync_after) cudaEventRecord(rt_event(0), s);
     cudaError_t e = !pair ? core_launch(arith, op, bn, p, grid, s)
-                          : (arith == AR_TF32X3 ? (p.b_pre ? x3tm_launch(op, p, grid, s) : x3pair_launch(op, bn, p, grid, s))
+                          : (arith == AR_TF32X3 ? (p.b_pre ? x3tm_launch(op, bn, p, grid, s) : x3pair_launch(op, bn, p, grid, s))
                                                 : (pair2 ? pair2_launch(arith, op, p, grid, s) : pair_launch(arith, op, p, grid, s)));
     if (e == cudaSuccess && partials) {
         e = splitk_finalize_launch(partials, ld_part, slab_rows, p.splits, final_p, s);
@@ -398,14 +399,15 @@ int repack_if_unaligned(Views& vw, char*& ptr, int64_t& ld_bytes, int64_t row_by
 // fp32 pair kernel with 256-column tiles (umma_x3tm.cuh): is B worth a pre-pass? Only when many row tiles re-read it
 // (the pre-pass costs a launch and a read and write of B) and full precision is asked for.
 bool presplit_worthwhile(int un, int prec, long long M, long long b_bytes) {
-    return un == 256 && prec != T2SP_PRECISION_TF32 && !rt_env().no_x3tm && !rt_env().no_presplit && (M + 255) / 256 >= 16 &&
+    return (un == 256 || un == 128) && prec != T2SP_PRECISION_TF32 && !rt_env().no_x3tm && !rt_env().no_presplit && (M + 255) / 256 >= 16 &&
            b_bytes > 0 && b_bytes <= (64ll << 20);
 }
 // Runs the pre-pass that writes B's slot images into scratch and points the kernel at them. Leaves p.b_pre = 0 (the
 // kernel then loads B through mapB and splits it itself) when anything is in the way.
-void prepack_b(Views& vw, CoreParams& p, BImageParams q, int n_tiles256) {
-    q.halves = 2 * n_tiles256;
-    const size_t bytes = size_t(q.num_kb) * q.halves * 32768;
+void prepack_b(Views& vw, CoreParams& p, BImageParams q, int un, int n_extent) {
+    q.halves = 2 * ((n_extent + un - 1) / un);
+    q.half_cols = un / 2;
+    const size_t bytes = size_t(q.num_kb) * q.halves * q.half_cols * 256;
     if (vw.n >= 8 || bytes == 0 || bytes > (size_t(256) << 20)) return;
     void* scratch = rt_alloc(bytes);
     if (!scratch) return;
@@ -685,7 +687,11 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
         const int bk = block_k_for(arith);
         const int op = trans_b ? OP_TTM : OP_GEMM;  // OP_TTM is the "both operands K-major" loader
         // Large 16-bit / 8-bit problems run on CTA pairs with 256 x 256 tiles.
-        const int x3un = arith == AR_TF32X3 ? x3_pair_width(M, N, kBlockM, (K + bk - 1) / bk) : 0;
+        // exactly 128 columns and many row tiles: the 256 x 128 form of the tensor-memory pair kernel (capsule cfg4,
+        // which is such a shape: 100 -> 71 us against the single-CTA kernel)
+        const bool tm128 = arith == AR_TF32X3 && !rt_env().no_tm128 && N == 128 &&
+                           presplit_worthwhile(128, prec, M, int64_t(K) * N * 4);
+        const int x3un = arith == AR_TF32X3 ? x3_pair_width(M, N, kBlockM, (K + bk - 1) / bk, tm128) : 0;
         const bool pair = x3un || (arith != AR_TF32X3 && M >= 512 && N >= 512 && !rt_env().no_pair);
         const int bn = x3un ? x3un : (pair ? 256 : core_pick_bn(arith, op, N, M));
         int64_t lda = int64_t(A->dim[1].stride) * es;
@@ -721,16 +727,16 @@ extern "C" int t2sp_b200_gemm(halide_buffer_t* A, halide_buffer_t* B, halide_buf
             uint32_t box[2] = {uint32_t(bk), uint32_t(pair ? bn / 2 : bn)};
             if (!rt_encode_tmap(&p.mapB, tmap_type(in_t), 2, pb, dims, str, box)) return tma_unsupported("B");
             if (presplit_worthwhile(x3un, prec, M, int64_t(N) * ldb2)) {
-                BImageParams q{reinterpret_cast<const float*>(pb), 1, ldb2 / 4, K, N, (K + 31) / 32, 0, 0, 0};
-                prepack_b(vw, p, q, (N + 255) / 256);
+                BImageParams q{reinterpret_cast<const float*>(pb), 1, ldb2 / 4, K, N, (K + 31) / 32};
+                prepack_b(vw, p, q, x3un, N);
             }
         } else {
             uint64_t dims[2] = {uint64_t(N), uint64_t(K)}, str[2] = {uint64_t(es), uint64_t(ldb2)};
             uint32_t box[2] = {uint32_t(128 / es), uint32_t(bk)};
             if (!rt_encode_tmap(&p.mapB, tmap_type(in_t), 2, pb, dims, str, box, arith == AR_TF32X3)) return tma_unsupported("B");
             if (presplit_worthwhile(x3un, prec, M, int64_t(K) * ldb2)) {
-                BImageParams q{reinterpret_cast<const float*>(pb), 0, ldb2 / 4, K, N, (K + 31) / 32, 0, 0, 0};
-                prepack_b(vw, p, q, (N + 255) / 256);
+                BImageParams q{reinterpret_cast<const float*>(pb), 0, ldb2 / 4, K, N, (K + 31) / 32};
+                prepack_b(vw, p, q, x3un, N);
             }
         }
         p.M = M; p.N = N; p.tile_rows = kBlockM; p.a_tx_bytes = kBlockM * 128;
@@ -869,7 +875,8 @@ extern "C" int t2sp_b200_ttm(halide_buffer_t* a, halide_buffer_t* b, halide_buff
     } else {
         const int prec = resolve_precision(desc ? desc->precision : 0);
         const int M = static_cast<int>(Mrows), N = Kn;
-        const int x3un = x3_pair_width(M, N, kBlockM, (L + 31) / 32);
+        const bool tm128 = !rt_env().no_tm128 && N == 128 && presplit_worthwhile(128, prec, M, int64_t(L) * N * 4);
+        const int x3un = x3_pair_width(M, N, kBlockM, (L + 31) / 32, tm128);
         const int bn = x3un ? x3un : core_pick_bn(AR_TF32X3, OP_TTM, N, M);
         int64_t lda = int64_t(a->dim[1].stride) * 4, ldb = int64_t(b->dim[1].stride) * 4;
         if (int e = repack_if_unaligned(vw, pa, lda, int64_t(L) * 4, M)) return e;
@@ -888,8 +895,8 @@ extern "C" int t2sp_b200_ttm(halide_buffer_t* a, halide_buffer_t* b, halide_buff
             uint32_t box[2] = {32, uint32_t(x3un ? bn / 2 : bn)};
             if (!rt_encode_tmap(&p.mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, pb, dims, str, box)) return tma_unsupported("b");
             if (presplit_worthwhile(x3un, prec, M, int64_t(N) * ldb)) {
-                BImageParams q{reinterpret_cast<const float*>(pb), 1, ldb / 4, L, N, (L + 31) / 32, 0, 0, 0};
-                prepack_b(vw, p, q, (N + 255) / 256);
+                BImageParams q{reinterpret_cast<const float*>(pb), 1, ldb / 4, L, N, (L + 31) / 32};
+                prepack_b(vw, p, q, x3un, N);
             }
         }
         p.M = M; p.N = N; p.tile_rows = kBlockM; p.a_tx_bytes = kBlockM * 128;
@@ -1038,11 +1045,12 @@ extern "C" int t2sp_b200_conv(halide_buffer_t* I, halide_buffer_t* K, halide_buf
     p.single_pass = prec == T2SP_PRECISION_TF32;
     p.cblks = (CI + 31) / 32; p.KY = KY; p.KX = KX; p.stride = 1;
     p.num_kb = KY * KX * p.cblks; p.total_kb = p.num_kb;
-    const int x3un = x3_pair_width(p.M, CO, p.tile_rows, p.num_kb);
+    const bool tm128c = !rt_env().no_tm128 && CO == 128 && presplit_worthwhile(128, prec, p.M, int64_t(CI) * KY * t1);
+    const int x3un = x3_pair_width(p.M, CO, p.tile_rows, p.num_kb, tm128c);
     if (x3un) bn = x3un;
     if (presplit_worthwhile(x3un, prec, p.M, int64_t(CI) * KY * t1)) {
         BImageParams q{reinterpret_cast<const float*>(pk), 2, t1 / 4, CI, CO, p.num_kb, 0, p.cblks, KY};
-        prepack_b(vw, p, q, (CO + 255) / 256);
+        prepack_b(vw, p, q, x3un, CO);
     }
     p.tiles_m = x3un ? (p.M + 255) / 256 : (p.M + p.tile_rows - 1) / p.tile_rows; p.tiles_n = (CO + bn - 1) / bn;
     p.idesc = x3un ? make_instr_desc(1, 2, false, true, 256, bn) : idesc_for(AR_TF32X3, kF32, true, bn);
@@ -1205,8 +1213,13 @@ extern "C" int t2sp_b200_capsule(halide_buffer_t* P, halide_buffer_t* W, halide_
     p.single_pass = prec == T2SP_PRECISION_TF32;
     p.cblks = (CP + 31) / 32; p.KY = KY; p.KX = KX; p.stride = s; p.CI = CI; p.CII = CII;
     p.num_kb = KY * KX * p.cblks; p.total_kb = p.num_kb;
-    const int x3un = x3_pair_width(p.M, NW, p.tile_rows, p.num_kb);
+    const bool tm128 = !rt_env().no_tm128 && NW == 128 && presplit_worthwhile(128, prec, p.M, int64_t(CI) * KY * KX * MK * t1);
+    const int x3un = x3_pair_width(p.M, NW, p.tile_rows, p.num_kb, tm128);
     if (x3un) bn = x3un;
+    if (presplit_worthwhile(x3un, prec, p.M, int64_t(CI) * KY * KX * MK * t1) && (x3un == 256 || tm128)) {
+        BImageParams q{reinterpret_cast<const float*>(pw), 3, t1 / 4, CP, NW, p.num_kb, 0, p.cblks, KY, 0, CI, CII, KY * KX};
+        prepack_b(vw, p, q, x3un, NW);
+    }
     p.tiles_m = x3un ? (p.M + 255) / 256 : (p.M + p.tile_rows - 1) / p.tile_rows; p.tiles_n = (NW + bn - 1) / bn;
     p.idesc = x3un ? make_instr_desc(1, 2, false, true, 256, bn) : idesc_for(AR_TF32X3, kF32, true, bn);
     p.out = pv;

@@ -36,46 +36,55 @@ __device__ __forceinline__ uint32_t presplit_pack(float a, float b) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
     return *reinterpret_cast<const uint32_t*>(&v);
 }
-// Writes, for every k-block and every 128-column half tile of B, the 32 KB image of the kernel's B slot: the raw
-// fp32 tile as TMA would have laid it out (16 KB) followed by the bf16 tile [bf16(b) | bf16(lo_b)] (16 KB). One
+// Writes, for every k-block and every half tile of B (128 or 64 columns), the image of the kernel's B slot: the raw
+// fp32 tile as TMA would have laid it out followed by the bf16 tile [bf16(b) | bf16(lo_b)] of the same size. One
 // thread per 16-byte piece of the raw tile (four consecutive N values of an MN-major B, four consecutive K values of
 // a K-major one); elements outside B are zero.
 __global__ void b_images_kernel(const BImageParams q, uint8_t* __restrict__ dst) {
     ptx::grid_dep_launch();  // the contraction kernel may set itself up meanwhile; it waits for this grid before it reads an image
+    const int H = q.half_cols, raw_bytes = H * 128, pieces = H * 8;
     const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
     const long long blobs = static_cast<long long>(q.num_kb) * q.halves;
-    if (idx >= blobs * 1024) return;
-    const int pi = static_cast<int>(idx & 1023);
-    const long long blob = idx >> 10;
+    if (idx >= blobs * pieces) return;
+    const int pi = static_cast<int>(idx % pieces);
+    const long long blob = idx / pieces;
     const int kb = static_cast<int>(blob / q.halves), half = static_cast<int>(blob % q.halves);
-    uint8_t* img = dst + blob * 32768;
+    uint8_t* img = dst + blob * (2 * raw_bytes);
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     int off_raw, off_hb, off_lb;
     if (q.mode == 1) {
         // K-major: row r (an n) holds 32 K values in 128 bytes, 16-byte chunk c stored at c ^ (r & 7); the bf16 tile
         // keeps the row pitch, bf16(b) in the first 64 bytes of the row, bf16(lo_b) in the second, same swizzle
         const int r = pi >> 3, c = pi & 7, x = r & 7;
-        const long long n = static_cast<long long>(half) * 128 + r;
+        const long long n = static_cast<long long>(half) * H + r;
         const int k0 = kb * 32 + 4 * c;
         if (n < q.N)
             for (int j = 0; j < 4; ++j)
                 if (k0 + j < q.K) v[j] = q.src[n * q.ld + k0 + j];
         off_raw = r * 128 + ((c ^ x) << 4);
-        off_hb = 16384 + r * 128 + (((c >> 1) ^ x) << 4) + (c & 1) * 8;
-        off_lb = 16384 + r * 128 + (((4 + (c >> 1)) ^ x) << 4) + (c & 1) * 8;
+        off_hb = raw_bytes + r * 128 + (((c >> 1) ^ x) << 4) + (c & 1) * 8;
+        off_lb = raw_bytes + r * 128 + (((4 + (c >> 1)) ^ x) << 4) + (c & 1) * 8;
     } else {
         // MN-major: boxes of 32 K rows x 32 N values (128-byte rows) with 32-byte atoms swizzled (atom a of row k
         // stored at a ^ (k & 3)); the bf16 tiles are boxes of 32 K rows x 64 N values, 16-byte chunk c stored at
         // c ^ (k & 7), the boxes of bf16(b) first, then those of bf16(lo_b)
-        const int k = pi >> 5, g = pi & 31;
-        const int n = half * 128 + 4 * g;
+        const int groups = H / 4;
+        const int k = pi / groups, g = pi % groups;
+        const int n = half * H + 4 * g;
         const float* s = nullptr;
         if (q.mode == 0) {
             const int kg = kb * 32 + k;
             if (kg < q.K) s = q.src + static_cast<long long>(kg) * q.ld;
-        } else {
+        } else if (q.mode == 2) {
             const int tap = kb / q.cblks, cb = kb % q.cblks, ky = tap % q.KY, kx = tap / q.KY, ci = cb * 32 + k;
             if (ci < q.K) s = q.src + static_cast<long long>(q.N) * kx + (static_cast<long long>(ci) + static_cast<long long>(ky) * q.K) * q.ld;
+        } else {
+            const int tap = kb / q.cblks, c = (kb % q.cblks) * 32 + k;
+            if (c < q.K) {
+                const int mk = c / q.CI, ci = c % q.CI, cii = ci % q.CII, cio = ci / q.CII;
+                s = q.src + (static_cast<long long>(cii) + static_cast<long long>(tap) * q.CII +
+                             static_cast<long long>(cio) * q.CII * q.taps + static_cast<long long>(mk) * q.CI * q.taps) * q.ld;
+            }
         }
         if (s)
             for (int j = 0; j < 4; ++j)
@@ -83,8 +92,8 @@ __global__ void b_images_kernel(const BImageParams q, uint8_t* __restrict__ dst)
         const int jb = g >> 3, a = (g & 7) >> 1, sub = g & 1;
         off_raw = jb * 4096 + k * 128 + ((((a ^ (k & 3)) << 1) | sub) << 4);
         const int c8 = (jb & 1) * 4 + a;
-        off_hb = 16384 + (jb >> 1) * 4096 + k * 128 + ((c8 ^ (k & 7)) << 4) + sub * 8;
-        off_lb = off_hb + 8192;
+        off_hb = raw_bytes + (jb >> 1) * 4096 + k * 128 + ((c8 ^ (k & 7)) << 4) + sub * 8;
+        off_lb = off_hb + raw_bytes / 2;
     }
     *reinterpret_cast<float4*>(img + off_raw) = make_float4(v[0], v[1], v[2], v[3]);
     *reinterpret_cast<uint2*>(img + off_hb) = make_uint2(presplit_pack(v[0], v[1]), presplit_pack(v[2], v[3]));
@@ -309,7 +318,7 @@ cudaError_t transpose32_launch(const void* src, long long ld_src, void* dst, lon
 }
 
 cudaError_t b_images_launch(const BImageParams& q, void* dst, cudaStream_t stream) {
-    const long long work = static_cast<long long>(q.num_kb) * q.halves * 1024;
+    const long long work = static_cast<long long>(q.num_kb) * q.halves * q.half_cols * 8;
     if (work <= 0) return cudaSuccess;
     b_images_kernel<<<static_cast<unsigned>((work + 255) / 256), 256, 0, stream>>>(q, static_cast<uint8_t*>(dst));
     return cudaGetLastError();

@@ -28,8 +28,8 @@ cudaError_t pair2_launch(int arith, int op, const CoreParams& p, int grid, cudaS
 // p.idesc describes a 256 x un TF32 MMA.
 cudaError_t x3pair_launch(int op, int un, const CoreParams& p, int grid, cudaStream_t stream);
 // The 256-column pair tile with the A operand in tensor memory, B pre-packed by b_images_launch (p.b_pre) and the
-// cross terms as bf16 MMAs (umma_x3tm.cuh); GEMM, TTM and conv.
-cudaError_t x3tm_launch(int op, const CoreParams& p, int grid, cudaStream_t stream);
+// cross terms as bf16 MMAs (umma_x3tm.cuh); pair tiles of 256 x un, un = 256 or 128.
+cudaError_t x3tm_launch(int op, int un, const CoreParams& p, int grid, cudaStream_t stream);
 
 // Launches the accumulate-then-scale MTTKRP kernel (umma_mttkrp.cuh; R <= 64) with `grid` persistent CTAs over the
 // work items that p.tiles_m, p.mt_lranges and p.mt_kranges describe; partial slabs go to p.out.
@@ -40,15 +40,18 @@ cudaError_t mttkrp2_launch(const CoreParams& p, int grid, cudaStream_t stream);
 cudaError_t transpose32_launch(const void* src, long long ld_src, void* dst, long long ld_dst, int rows, int cols,
                                cudaStream_t stream, int batch = 1, long long bs_src = 0, long long bs_dst = 0);
 
-// Pre-pass of the fp32 pair kernel with its A operand in tensor memory (umma_x3tm.cuh): the 32 KB slot images of B,
-// [k-block][128-column half tile][raw fp32 tile | bf16(b), bf16(lo_b) tile], for an operand many row tiles re-read.
+// Pre-pass of the fp32 pair kernel with its A operand in tensor memory (umma_x3tm.cuh): the slot images of B,
+// [k-block][half tile of 128 or 64 columns][raw fp32 tile | bf16(b), bf16(lo_b) tile], for an operand many row tiles re-read.
 struct BImageParams {
     const float* src;
-    int mode;        // 0: MN-major B[k][n]; 1: K-major B[n][k]; 2: conv weights (co, kx, ci, ky)
-    long long ld;    // elements between rows (mode 0: k rows, mode 1: n rows, mode 2: between channels ci)
-    int K, N;        // contraction extent (mode 2: CI, per tap) and columns (mode 2: CO)
+    int mode;        // 0: MN-major B[k][n]; 1: K-major B[n][k]; 2: conv weights (co, kx, ci, ky); 3: capsule weights
+                     //    (n = co + CO * my, cii, tap = ky + KY * kx, ci / CII, mk)
+    long long ld;    // elements between rows (mode 0: k rows, mode 1: n rows, modes 2 and 3: between channels)
+    int K, N;        // contraction extent (mode 2: CI per tap, mode 3: CI * MK per tap) and columns
     int num_kb, halves;
-    int cblks, KY;   // mode 2: k-block = (tap = ky + KY * kx) * cblks + channel block
+    int cblks, KY;   // modes 2 and 3: k-block = tap * cblks + channel block; mode 2: tap = ky + KY * kx
+    int half_cols;   // columns of a half tile: 128 (256-column pair tiles) or 64
+    int CI, CII, taps;  // mode 3: capsule channels, inner channel extent, KY * KX
 };
 cudaError_t b_images_launch(const BImageParams& q, void* dst, cudaStream_t stream);
 

@@ -31,7 +31,8 @@
 //               quarters 2 and 3 by halves of the k-block.
 //   warps 4-11  epilogue as in umma_x3pair.cuh: every 8 k-blocks the accumulator is added into fp32 registers
 //               (round to nearest) and handed back
-// TMEM per CTA (512 columns): [accumulator 256 | 4 A slots of 64].
+// TMEM per CTA (512 columns): [accumulator 256 | 4 A slots of 64]; with 128-column tiles [2 accumulators of 128 | 4 A
+// slots of 64], so that a chunk accumulates while the one before it is drained, and six A stages and B slots.
 #pragma once
 #include <cuda_bf16.h>
 
@@ -42,28 +43,30 @@
 
 namespace t2sp {
 
-template <int OP>
+template <int OP, int UN_>
 struct X3TmCfg {
+    static_assert(UN_ == 256 || UN_ == 128, "tile width");
     static constexpr bool kBMnMajor = (OP == OP_GEMM || OP == OP_CONV || OP == OP_CAPSULE);
-    static constexpr int UN = 256;
+    static constexpr int UN = UN_;
     static constexpr int kHalfN = UN / 2;
     static constexpr int kABytes = kBlockM * 128;
     static constexpr int kBBytes = kHalfN * 128;  // raw fp32 B tile; the bf16 tile [bf16(b) | bf16(lo_b)] is as large
     static constexpr int kBSlotBytes = 2 * kBBytes;
-    static constexpr int kAStages = 4;
-    static constexpr int kBSlots = 4;
+    static constexpr int kAStages = UN == 256 ? 4 : 6;
+    static constexpr int kBSlots = UN == 256 ? 4 : 6;
     static constexpr int kTSlots = 4;                  // A slots in tensor memory
+    static constexpr int kAccBufs = UN == 256 ? 1 : 2; // 128-column tiles: a chunk accumulates while the one before drains
     static constexpr int kBoxBytesMn = 32 * 128;       // MN-major fp32 box: 32 k-rows x 32 columns
     static constexpr int kBoxesMn = kBBytes / kBoxBytesMn;
     static constexpr uint32_t kBSwizzle = kBMnMajor ? 1u : 2u;
     static constexpr uint32_t kBSbo = kBMnMajor ? 512u : 1024u;
     static constexpr int kThreads = 16 * 32;
     static constexpr int kTmemCols = 512;
-    static constexpr int kASlotCol0 = UN;
+    static constexpr int kASlotCol0 = kAccBufs * UN;
     static constexpr int kChunkKb = 8;
     static constexpr int kColsPerWarp = UN / 2;
     static constexpr int kCStage = 8 * 4096;
-    static constexpr int kNumBars = 2 * kAStages + 2 * kBSlots + 2 * kTSlots + 2;
+    static constexpr int kNumBars = 2 * kAStages + 2 * kBSlots + 2 * kTSlots + 2 * kAccBufs;
     static constexpr int kMaxBoxTab = 16;  // conv / capsule: boxes of an A tile whose row coordinates are kept per tile
     static constexpr int kTailBytes = kNumBars * 8 + 16 + kMaxBoxTab * 16;
     static constexpr int kSmemBytes = kAStages * kABytes + kBSlots * kBSlotBytes + kCStage + kTailBytes + 1024;
@@ -76,10 +79,11 @@ __device__ __forceinline__ uint32_t x3_pack_bf16(float lo_elem, float hi_elem) {
 }
 __device__ __forceinline__ float x3_tf32_lo(float x) { return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
 
-template <int OP>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(X3TmCfg<OP>::kThreads, 1)
+template <int OP, int UN_>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(X3TmCfg<OP, UN_>::kThreads, 1)
 umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
-    using Cfg = X3TmCfg<OP>;
+    using Cfg = X3TmCfg<OP, UN_>;
+    constexpr int AB = Cfg::kAccBufs;
     constexpr int UN = Cfg::UN, NA = Cfg::kAStages, NB = Cfg::kBSlots, TS = Cfg::kTSlots;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -92,9 +96,9 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
     uint64_t* bfree_bar = bfull_bar + NB;                     // own: MMAs that read the B slot retired
     uint64_t* ready_bar = bfree_bar + NB;                     // leader's: both CTAs' A slot written and B slot complete (12)
     uint64_t* tfree_bar = ready_bar + TS;                     // own: MMAs that read the A slot retired
-    uint64_t* cfull_bar = tfree_bar + TS;                     // own: a chunk of the accumulator is complete
-    uint64_t* cempty_bar = cfull_bar + 1;                     // leader's: the chunk was drained by both CTAs
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cempty_bar + 1);
+    uint64_t* cfull_bar = tfree_bar + TS;                     // own: a chunk of an accumulator is complete
+    uint64_t* cempty_bar = cfull_bar + AB;                    // leader's: the chunk was drained by both CTAs
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cempty_bar + AB);
     uint32_t* abort_slot = tmem_slot + 1;
     int* box_tab = reinterpret_cast<int*>(tmem_slot + 4);  // the producer's own
     long long* ntable = reinterpret_cast<long long*>(cstage);
@@ -123,8 +127,10 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
             ptx::mbar_init(&ready_bar[a], 12);  // 6 split warps in each CTA
             ptx::mbar_init(&tfree_bar[a], 1);
         }
-        ptx::mbar_init(cfull_bar, 1);
-        ptx::mbar_init(cempty_bar, 16);         // 8 epilogue warps in each CTA
+        for (int a = 0; a < AB; ++a) {
+            ptx::mbar_init(&cfull_bar[a], 1);
+            ptx::mbar_init(&cempty_bar[a], 16);  // 8 epilogue warps in each CTA
+        }
         *abort_slot = 0u;
         ptx::fence_mbar_init();
     }
@@ -352,17 +358,18 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
             constexpr uint32_t kStepB16 = Cfg::kBMnMajor ? ((16 * 128) >> 4) : 2u;   // 16 K values of a bf16 tile
             // the same tile shape and operand majors as p.idesc, with bf16 operands
             const uint32_t idesc16 = (p.idesc & ~((7u << 7) | (7u << 10))) | (1u << 7) | (1u << 10);
-            const uint32_t d_acc = tmem_base;
             for (int t = pair; t < num_tiles && ok; t += num_pairs) {
                 const int nkb = item_kb_count(t);
                 for (int kb0 = 0; kb0 < nkb && ok; kb0 += Cfg::kChunkKb, ++gch) {
                     const int kend = min(kb0 + Cfg::kChunkKb, nkb);
+                    const int acc = gch % AB;
+                    const uint32_t d_acc = tmem_base + acc * UN;
                     for (int kb = kb0; kb < kend; ++kb, ++it) {
                         const int sl = it % NB, ts = it % TS;
                         if (!bounded_wait(&ready_bar[ts], (it / TS) & 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
                         if (kb == kb0) {
-                            // the accumulator is free once the epilogue warps of both CTAs drained the previous chunk
-                            if (!bounded_wait(cempty_bar, (gch & 1) ^ 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
+                            // the accumulator is free once the epilogue warps of both CTAs drained the chunk that used it last
+                            if (!bounded_wait(&cempty_bar[acc], ((gch / AB) & 1) ^ 1, ab, ST_TIMEOUT_MMA)) { ok = false; break; }
                         }
                         ptx::tc_fence_after_sync();
                         T2SP_TRACE(p, 3, it);
@@ -388,8 +395,8 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
                         T2SP_TRACE(p, 4, it);
                     }
                     if (ok) {
-                        ptx::umma_commit_pair(ptx::map_to_cta(cfull_bar, 0));
-                        ptx::umma_commit_pair(ptx::map_to_cta(cfull_bar, 1));
+                        ptx::umma_commit_pair(ptx::map_to_cta(&cfull_bar[acc], 0));
+                        ptx::umma_commit_pair(ptx::map_to_cta(&cfull_bar[acc], 1));
                     }
                 }
             }
@@ -426,13 +433,14 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
 #pragma unroll
             for (int j = 0; j < CW; ++j) sum[j] = 0u;
             for (int kb0 = 0; kb0 < nkb && ok; kb0 += Cfg::kChunkKb, ++gch) {
-                if (!bounded_wait_warp(cfull_bar, gch & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
+                const int acc = gch % AB;
+                if (!bounded_wait_warp(&cfull_bar[acc], (gch / AB) & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
                 ptx::tc_fence_after_sync();
                 if (threadIdx.x == 128) T2SP_TRACE(p, 5, gch);
 #pragma unroll
                 for (int c = 0; c < CW / 32; ++c) {
                     uint32_t r[32];
-                    ptx::tmem_ld_32x32(lane_base + c * 32, r);
+                    ptx::tmem_ld_32x32(lane_base + acc * UN + c * 32, r);
                     ptx::tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
@@ -440,7 +448,7 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
                 }
                 ptx::tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive_peer(cempty_bar, 0);
+                if (lane == 0) ptx::mbar_arrive_peer(&cempty_bar[acc], 0);
                 if (threadIdx.x == 128) T2SP_TRACE(p, 6, gch);
             }
             if (!ok) break;

@@ -220,7 +220,8 @@ def test_fp32_split_k(lib, M, N, K, trans_b, force):
     assert componentwise(split, truth, O.gemm_f32(np.abs(A), np.abs(B), acc64=True)) <= TOL_FP32
 
 
-@pytest.mark.parametrize("M,N,K,trans_b", [(9728, 256, 96, 0), (9728, 264, 200, 0), (9728, 256, 100, 1), (5120, 500, 640, 1)])
+@pytest.mark.parametrize("M,N,K,trans_b", [(9728, 256, 96, 0), (9728, 264, 200, 0), (9728, 256, 100, 1), (5120, 500, 640, 1),
+                                           (9728, 128, 200, 0), (9600, 128, 96, 1)])  # the last two: 256 x 128 tiles
 def test_fp32_pair_prepacked_b(lib, M, N, K, trans_b):
     """With many 256-row tiles over one B, the fp32 pair kernel with its A operand in tensor memory runs: a pre-pass
     writes B's shared-memory tile images (raw fp32 and the bf16 operands of the cross-term MMAs) once, the kernel
