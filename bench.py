@@ -290,7 +290,7 @@ RATE = {"bf16": 1.0, "f16": 1.0, "i8": 2.0, "f32": 1.0 / 6.0}  # tensor ceiling 
 # fp32 workloads that run on the pair kernel with the A operand in tensor memory (many row tiles over one B): per 32
 # contraction values four TF32 MMAs (hi * hi) and four bf16 MMAs (the cross terms) where a bf16 GEMM issues two, so the
 # ceiling is a quarter of the bf16 peak instead of the sixth of three TF32 passes
-BF16_CROSS_TERMS = {"conv_cfg2", "ttm_cfg3"}
+BF16_CROSS_TERMS = {"conv_cfg2", "ttm_cfg3", "capsule_cfg4", "sgemm_n128"}
 
 
 class Resident:
@@ -639,7 +639,7 @@ KNOWN_TRAFFIC = {
     "ttm_cfg3": 269131520 + 217162752,
     # profiles/mttkrp_cfg3_mttkrp2_kernel_full.md
     "mttkrp_cfg3": 537191168 + 4868352,
-    "capsule_cfg4": 21994496 + 7168,
+    "capsule_cfg4": 22507008 + 11008,
     "sgemm_1024": 8471808,
     # profiles/ger_a10_rows_kernel_full.md
     "ger_a10": 671217664 + 620295680,

@@ -307,9 +307,11 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
                             if constexpr (OP == OP_CONV) {
                                 ptx::tma_load_4d(dst, &p.mapA[0], &afull_bar[s], c0, c[0], c[1] + wa.ky, c[2] + wa.kx);
                             } else {
-                                const int sy = wa.ky % p.stride, sx = wa.kx % p.stride;
-                                ptx::tma_load_5d(dst, &p.mapA[sy + 2 * sx], &afull_bar[s], c0, c[0], c[1] + wa.ky / p.stride,
-                                                 c[2] + wa.kx / p.stride, c[3]);
+                                // (stride 1 spelled out: this thread issues every copy of the CTA and has no time for divisions)
+                                const bool unit = p.stride == 1;
+                                const int sy = unit ? 0 : wa.ky % p.stride, sx = unit ? 0 : wa.kx % p.stride;
+                                const int dy = unit ? wa.ky : wa.ky / p.stride, dx = unit ? wa.kx : wa.kx / p.stride;
+                                ptx::tma_load_5d(dst, &p.mapA[sy + 2 * sx], &afull_bar[s], c0, c[0], c[1] + dy, c[2] + dx, c[3]);
                             }
                         }
                     }
