@@ -13,10 +13,6 @@ cudaError_t launch_x3tm(const CoreParams& p, int grid, cudaStream_t stream) {
     auto kern = umma_x3tm_kernel<OP, UN>;
     static std::atomic<bool> configured[kMaxDev];
     if (cudaError_t e = allow_smem(kern, Cfg::kSmemBytes, configured)) return e;
-#ifdef T2SP_X3TM_NO_PDL
-    kern<<<grid, Cfg::kThreads, Cfg::kSmemBytes, stream>>>(p);
-    return cudaGetLastError();
-#else
     // programmatic stream serialization: the grid is set up while the pre-pass that writes B's images still runs; the
     // kernel's producer waits for that grid before its first copy of B, everything before that overlaps
     cudaLaunchConfig_t cfg = {};
@@ -30,7 +26,6 @@ cudaError_t launch_x3tm(const CoreParams& p, int grid, cudaStream_t stream) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, p);
-#endif
 }
 }  // namespace
 
