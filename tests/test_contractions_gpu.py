@@ -55,6 +55,20 @@ def test_ttm_random(lib, L, I, J, K):
     assert normwise(c, O.ttm_f32(a, b)) <= TOL_FP32
 
 
+def test_ttm_tiled_output_many_row_tiles(lib):
+    """The 9-D tiled output through the scatter epilogue of the tensor-memory pair kernel (12288 rows i + I*j over a
+    256-column factor: 48 row tiles)."""
+    L, I, J, K = 96, 128, 96, 256
+    tiles = (2, 4, 2, 8, 2, 4)  # JJ, KK, II, KKK, JJJ, III
+    a = O.uniform(5, 1, (J, I, L))
+    b = O.uniform(5, 2, (K, L))
+    rc, c9 = run_ttm(a, b, tiled=tiles)
+    assert rc == 0
+    assert not np.isnan(c9).any()
+    ref9 = O.ttm_tile_layout(O.ttm_f32(a, b, acc64=True).astype(np.float32), *tiles)
+    assert normwise(c9, ref9) <= TOL_FP32
+
+
 def run_mttkrp(a, b, c, splits=0):
     K, I, L = a.shape
     R = b.shape[0]

@@ -306,7 +306,9 @@ def test_fp32_split_k_tiled_layout_and_blas_epilogue(lib):
 
 
 @pytest.mark.parametrize("ta,tb,m,n,k", [("N", "N", 256, 192, 128), ("T", "N", 300, 200, 100), ("N", "T", 128, 260, 64),
-                                         ("T", "T", 520, 516, 90), ("N", "N", 2048, 1024, 256)])
+                                         ("T", "T", 520, 516, 90), ("N", "N", 2048, 1024, 256),
+                                         # many row tiles over one B: the tensor-memory pair kernel, 256- and 128-column tiles
+                                         ("N", "N", 9728, 300, 96), ("T", "T", 9728, 128, 70)])
 def test_blas_sgemm(lib, ta, tb, m, n, k):
     """BLAS-style entry (reference: t2s/peppers/blas/level3/gemm/release/a10/blas-gemm.cpp): row-major arrays,
     transposes, alpha/beta. transa = 'T' exercises the on-device transpose, including K not a multiple of 4."""
