@@ -41,7 +41,8 @@ def test_ttm_known_answer(lib):
 
 
 @pytest.mark.parametrize("L,I,J,K", [(256, 64, 48, 256), (100, 24, 10, 72), (64, 128, 128, 64),
-                                     (96, 128, 100, 256), (64, 256, 64, 128)])  # the last two run on CTA pairs
+                                     (96, 128, 100, 256), (64, 256, 64, 128),  # these two run on CTA pairs
+                                     (100, 128, 96, 256), (72, 100, 99, 250)])  # pairs; L, rows and K ending inside blocks / tiles
 def test_ttm_random(lib, L, I, J, K):
     a = O.uniform(0, 1, (J, I, L))
     b = O.uniform(0, 2, (K, L))

@@ -43,6 +43,8 @@ CONV_CASES = [
     (2, 32, 32, 1, 1, 8, 8),      # 1x1 filter
     (64, 32, 256, 3, 3, 14, 14),  # BASELINE config 2 with fewer input channels: CTA-pair kernel, 256-wide tiles
     (64, 64, 128, 3, 3, 14, 12),  # CTA-pair kernel, 128-wide tiles
+    (64, 40, 256, 3, 2, 14, 14),  # tensor-memory pair kernel with a channel count that ends inside a 32-channel block
+    (64, 72, 200, 2, 3, 14, 14),  # ... and an output channel count that ends inside a tile
 ]
 
 
