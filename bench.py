@@ -39,6 +39,8 @@ WORKLOADS = {
     "gemm_i8_4096": ("gemm", dict(M=4096, N=4096, K=4096, dtype="i8")),
     "gemm_i8_16384": ("gemm", dict(M=16384, N=16384, K=16384, dtype="i8")),
     "sgemm_1024": ("gemm", dict(M=1024, N=1024, K=1024, dtype="f32")),
+    "sgemm_4096": ("gemm", dict(M=4096, N=4096, K=4096, dtype="f32")),
+    "sgemm_8192": ("gemm", dict(M=8192, N=8192, K=8192, dtype="f32")),
     "conv_cfg2": ("conv", dict(N=64, CI=256, CO=256, KY=3, KX=3, OY=14, OX=14)),
     "ttm_cfg3": ("ttm", dict(L=256, I=512, J=512, K=256)),
     "mttkrp_cfg3": ("mttkrp", dict(L=512, I=512, K=512, R=64)),
@@ -290,7 +292,7 @@ RATE = {"bf16": 1.0, "f16": 1.0, "i8": 2.0, "f32": 1.0 / 6.0}  # tensor ceiling 
 # fp32 workloads that run on the pair kernel with the A operand in tensor memory (many row tiles over one B): per 32
 # contraction values four TF32 MMAs (hi * hi) and four bf16 MMAs (the cross terms) where a bf16 GEMM issues two, so the
 # ceiling is a quarter of the bf16 peak instead of the sixth of three TF32 passes
-BF16_CROSS_TERMS = {"conv_cfg2", "ttm_cfg3", "capsule_cfg4", "sgemm_n128"}
+BF16_CROSS_TERMS = {"conv_cfg2", "ttm_cfg3", "capsule_cfg4", "sgemm_n128", "sgemm_4096", "sgemm_8192"}
 
 
 class Resident:

@@ -400,7 +400,7 @@ int repack_if_unaligned(Views& vw, char*& ptr, int64_t& ld_bytes, int64_t row_by
 // (the pre-pass costs a launch and a read and write of B) and full precision is asked for.
 bool presplit_worthwhile(int un, int prec, long long M, long long b_bytes) {
     return (un == 256 || un == 128) && prec != T2SP_PRECISION_TF32 && !rt_env().no_x3tm && !rt_env().no_presplit && (M + 255) / 256 >= 16 &&
-           b_bytes > 0 && b_bytes <= (64ll << 20);
+           b_bytes > 0 && b_bytes <= (256ll << 20);
 }
 // Runs the pre-pass that writes B's slot images into scratch and points the kernel at them. Leaves p.b_pre = 0 (the
 // kernel then loads B through mapB and splits it itself) when anything is in the way.
@@ -408,7 +408,7 @@ void prepack_b(Views& vw, CoreParams& p, BImageParams q, int un, int n_extent) {
     q.halves = 2 * ((n_extent + un - 1) / un);
     q.half_cols = un / 2;
     const size_t bytes = size_t(q.num_kb) * q.halves * q.half_cols * 256;
-    if (vw.n >= 8 || bytes == 0 || bytes > (size_t(256) << 20)) return;
+    if (vw.n >= 8 || bytes == 0 || bytes > (size_t(512) << 20)) return;
     void* scratch = rt_alloc(bytes);
     if (!scratch) return;
     vw.v[vw.n].ptr = scratch; vw.v[vw.n].borrowed = false; vw.n++;
