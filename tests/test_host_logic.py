@@ -185,3 +185,38 @@ def test_nd_fronts_and_syrk_validation(lib):
     assert t2sp_b200.ger(A, X, Y, z(2, 2, 2, 2, 3, 4)) == -8     # III*II*I = 12, A has 8 rows
     assert t2sp_b200.ger(A, z(4), Y, z(2, 2, 2, 2, 2, 4)) == -4  # X shorter than A's row count
     assert t2sp_b200.ger(A, X, z(2, 8), z(2, 2, 2, 2, 2, 4)) == -43  # Y must be 1-D
+
+
+def test_bf16_cross_term_formulation_bound():
+    """The arithmetic of the fp32 pair kernel with bf16 cross terms, restated in numpy (no GPU): a = hi + lo with
+    hi = a truncated to TF32 (what the tensor core reads from a raw fp32 word) and lo = a - hi (exact in fp32);
+    a b ~ hi_a hi_b + bf16(lo_a) bf16(b) + bf16(a) bf16(lo_b), products and sums exact here (fp64), so that only the
+    formulation's own error shows: the dropped lo_a lo_b (2^-22) and the four bf16 roundings of terms that are
+    2^-11 of the product. Bound per product: 2 x 2^-9 x 2^-11 x (1 + 2^-9) + 2^-22 < 2^-18.
+    K = 8192 on mixed-sign and on positive inputs, elementwise relative to sum_k |a||b|."""
+    import numpy as np
+    from tests import oracle_lib as O
+
+    def tf32_trunc(x):
+        return (x.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+
+    def bf16(x):
+        return O.bf16_to_f32(O.to_bf16(x))
+
+    M, N, K = 48, 40, 8192
+    for positive in (False, True):
+        A, B = O.uniform(41, 1, (M, K)), O.uniform(41, 2, (K, N))
+        if positive:
+            A, B = np.abs(A), np.abs(B)
+        hi_a, hi_b = tf32_trunc(A), tf32_trunc(B)
+        lo_a, lo_b = A - hi_a, B - hi_b
+        assert np.array_equal(hi_a.astype(np.float64) + lo_a.astype(np.float64), A.astype(np.float64)), "the split is exact"
+        f = np.float64
+        got = hi_a.astype(f) @ hi_b.astype(f) + bf16(lo_a).astype(f) @ bf16(B).astype(f) + bf16(A).astype(f) @ bf16(lo_b).astype(f)
+        truth = A.astype(f) @ B.astype(f)
+        absprod = np.abs(A).astype(f) @ np.abs(B).astype(f)
+        err = float(np.max(np.abs(got - truth) / absprod))
+        assert err < 2.0 ** -18, err
+        # on positive inputs nothing cancels: the typical error is far below the bound
+        if positive:
+            assert err < 2.0 ** -20, err
