@@ -22,6 +22,7 @@
 //              images the pre-pass wrote). That pays when many row tiles re-read a small B (weights, the factor of
 //              a TTM), which is when the host side picks this kernel; otherwise umma_x3pair.cuh runs.
 //   A slots    4 x 64 columns of tensor memory [hi 32 | bf16(a) 16 | bf16(lo_a) 16], handed back by the MMAs' commit
+//              (the same commit that hands back B slot i: k-block it uses slot it % 4 of both)
 //
 // Per CTA: 16 warps as in umma_x3pair.cuh.
 //   warp 0      producer (own 128 A rows, own 128 of the 256 B columns); serves the A and the B queue as they open
@@ -32,7 +33,7 @@
 //   warps 4-11  epilogue as in umma_x3pair.cuh: every 8 k-blocks the accumulator is added into fp32 registers
 //               (round to nearest) and handed back
 // TMEM per CTA (512 columns): [accumulator 256 | 4 A slots of 64]; with 128-column tiles [2 accumulators of 128 | 4 A
-// slots of 64], so that a chunk accumulates while the one before it is drained, and six A stages and B slots.
+// slots of 64], so that a chunk accumulates while the one before it is drained, and six A stages.
 #pragma once
 #include <cuda_bf16.h>
 
@@ -53,7 +54,7 @@ struct X3TmCfg {
     static constexpr int kBBytes = kHalfN * 128;  // raw fp32 B tile; the bf16 tile [bf16(b) | bf16(lo_b)] is as large
     static constexpr int kBSlotBytes = 2 * kBBytes;
     static constexpr int kAStages = UN == 256 ? 4 : 6;
-    static constexpr int kBSlots = UN == 256 ? 4 : 6;
+    static constexpr int kBSlots = 4;                  // as many as A slots: slot i of both is handed back by one commit
     static constexpr int kTSlots = 4;                  // A slots in tensor memory
     static constexpr int kAccBufs = UN == 256 ? 1 : 2; // 128-column tiles: a chunk accumulates while the one before drains
     static constexpr int kBoxBytesMn = 32 * 128;       // MN-major fp32 box: 32 k-rows x 32 columns
@@ -93,9 +94,10 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
     uint64_t* afull_bar = reinterpret_cast<uint64_t*>(tail);  // own: this CTA's A rows landed
     uint64_t* aempty_bar = afull_bar + NA;                    // own: all six split warps hold their part in registers
     uint64_t* bfull_bar = aempty_bar + NA;                    // own: this CTA's B columns landed
-    uint64_t* bfree_bar = bfull_bar + NB;                     // own: MMAs that read the B slot retired
-    uint64_t* ready_bar = bfree_bar + NB;                     // leader's: both CTAs' A slot written and B slot complete (12)
-    uint64_t* tfree_bar = ready_bar + TS;                     // own: MMAs that read the A slot retired
+    uint64_t* ready_bar = bfull_bar + 2 * NB;                 // leader's: both CTAs' A slot written and B slot complete (12)
+    uint64_t* tfree_bar = ready_bar + TS;                     // own: MMAs that read the A slot and the B slot retired
+    uint64_t* bfree_bar = tfree_bar;                          // (k-block it uses A slot it % 4 and B slot it % 4: one commit)
+    static_assert(NB == TS, "the A slots in tensor memory and the B slots share their hand-back barriers");
     uint64_t* cfull_bar = tfree_bar + TS;                     // own: a chunk of an accumulator is complete
     uint64_t* cempty_bar = cfull_bar + AB;                    // leader's: the chunk was drained by both CTAs
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(cempty_bar + AB);
@@ -121,7 +123,6 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
         }
         for (int s = 0; s < NB; ++s) {
             ptx::mbar_init(&bfull_bar[s], 1);
-            ptx::mbar_init(&bfree_bar[s], 1);
         }
         for (int a = 0; a < TS; ++a) {
             ptx::mbar_init(&ready_bar[a], 12);  // 6 split warps in each CTA
@@ -390,8 +391,6 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
                             ptx::umma_a_tmem<ptx::KIND_F16, 2>(d_acc, a_lb + 8 * j, db_hb + j * kStepB16, idesc16, 1u);
                             ptx::umma_a_tmem<ptx::KIND_F16, 2>(d_acc, a_hb + 8 * j, db_lb + j * kStepB16, idesc16, 1u);
                         }
-                        ptx::umma_commit_pair(ptx::map_to_cta(&bfree_bar[sl], 0));
-                        ptx::umma_commit_pair(ptx::map_to_cta(&bfree_bar[sl], 1));
                         ptx::umma_commit_pair(ptx::map_to_cta(&tfree_bar[ts], 0));
                         ptx::umma_commit_pair(ptx::map_to_cta(&tfree_bar[ts], 1));
                         T2SP_TRACE(p, 4, it);
