@@ -7,10 +7,10 @@
 namespace t2sp {
 
 namespace {
-template <int OP, int UN>
+template <int OP, int UN, bool ONE_CHUNK = false>
 cudaError_t launch_x3tm(const CoreParams& p, int grid, cudaStream_t stream) {
     using Cfg = X3TmCfg<OP, UN>;
-    auto kern = umma_x3tm_kernel<OP, UN>;
+    auto kern = umma_x3tm_kernel<OP, UN, ONE_CHUNK>;
     static std::atomic<bool> configured[kMaxDev];
     if (cudaError_t e = allow_smem(kern, Cfg::kSmemBytes, configured)) return e;
     // programmatic stream serialization: the grid is set up while the pre-pass that writes B's images still runs; the
@@ -31,6 +31,11 @@ cudaError_t launch_x3tm(const CoreParams& p, int grid, cudaStream_t stream) {
 
 cudaError_t x3tm_launch(int op, int un, const CoreParams& p, int grid, cudaStream_t stream) {
     if (!p.b_pre || !p.b_images) return cudaErrorInvalidValue;
+    // short contractions on the 256-column form: every tile is a single chunk of the accumulator
+    if (un == 256 && p.num_kb <= X3TmCfg<OP_GEMM, 256>::kChunkKb) {
+        if (op == OP_GEMM) return launch_x3tm<OP_GEMM, 256, true>(p, grid, stream);
+        if (op == OP_TTM) return launch_x3tm<OP_TTM, 256, true>(p, grid, stream);
+    }
 #define T2SP_X3TM(OPC, UNV) \
     if (op == OPC && un == UNV) return launch_x3tm<OPC, UNV>(p, grid, stream)
     T2SP_X3TM(OP_GEMM, 256);

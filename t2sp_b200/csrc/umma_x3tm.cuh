@@ -80,7 +80,10 @@ __device__ __forceinline__ uint32_t x3_pack_bf16(float lo_elem, float hi_elem) {
 }
 __device__ __forceinline__ float x3_tf32_lo(float x) { return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); }
 
-template <int OP, int UN_>
+// ONE_CHUNK: every work item has at most kChunkKb k-blocks, so a tile is one chunk and the epilogue loads it straight
+// into its registers, all loads in flight at once, instead of adding chunk after chunk: the single accumulator of the
+// 256-column form is handed back after a third of the time (a TTM with a contraction of 256, 8 k-blocks per tile).
+template <int OP, int UN_, bool ONE_CHUNK = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(X3TmCfg<OP, UN_>::kThreads, 1)
 umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
     using Cfg = X3TmCfg<OP, UN_>;
@@ -429,28 +432,45 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
                 offm = digits_offset(p.dm, m);
                 __syncwarp();
             }
-            // (one uniform add-from-zero loop: with the first chunk loaded straight into `sum` the compiler spilled)
             uint32_t sum[CW];
-#pragma unroll
-            for (int j = 0; j < CW; ++j) sum[j] = 0u;
-            for (int kb0 = 0; kb0 < nkb && ok; kb0 += Cfg::kChunkKb, ++gch) {
+            if constexpr (ONE_CHUNK) {
                 const int acc = gch % AB;
                 if (!bounded_wait_warp(&cfull_bar[acc], (gch / AB) & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
                 ptx::tc_fence_after_sync();
                 if (threadIdx.x == 128) T2SP_TRACE(p, 5, gch);
 #pragma unroll
-                for (int c = 0; c < CW / 32; ++c) {
-                    uint32_t r[32];
-                    ptx::tmem_ld_32x32(lane_base + acc * UN + c * 32, r);
-                    ptx::tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        sum[c * 32 + j] = __float_as_uint(__uint_as_float(sum[c * 32 + j]) + __uint_as_float(r[j]));
-                }
+                for (int c = 0; c < CW / 32; ++c)
+                    ptx::tmem_ld_32x32(lane_base + acc * UN + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sum[c * 32]));
+                ptx::tmem_ld_wait();
                 ptx::tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive_peer(&cempty_bar[acc], 0);
                 if (threadIdx.x == 128) T2SP_TRACE(p, 6, gch);
+                ++gch;
+            } else {
+                // (one uniform add-from-zero loop: with the first chunk loaded straight into `sum` and the later ones
+                // added the compiler spilled)
+#pragma unroll
+                for (int j = 0; j < CW; ++j) sum[j] = 0u;
+                for (int kb0 = 0; kb0 < nkb && ok; kb0 += Cfg::kChunkKb, ++gch) {
+                    const int acc = gch % AB;
+                    if (!bounded_wait_warp(&cfull_bar[acc], (gch / AB) & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
+                    ptx::tc_fence_after_sync();
+                    if (threadIdx.x == 128) T2SP_TRACE(p, 5, gch);
+#pragma unroll
+                    for (int c = 0; c < CW / 32; ++c) {
+                        uint32_t r[32];
+                        ptx::tmem_ld_32x32(lane_base + acc * UN + c * 32, r);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            sum[c * 32 + j] = __float_as_uint(__uint_as_float(sum[c * 32 + j]) + __uint_as_float(r[j]));
+                    }
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive_peer(&cempty_bar[acc], 0);
+                    if (threadIdx.x == 128) T2SP_TRACE(p, 6, gch);
+                }
             }
             if (!ok) break;
             uint32_t* out32 = reinterpret_cast<uint32_t*>(p.out);
