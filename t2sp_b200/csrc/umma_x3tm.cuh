@@ -450,9 +450,27 @@ umma_x3tm_kernel(const __grid_constant__ CoreParams p) {
             } else {
                 // (one uniform add-from-zero loop: with the first chunk loaded straight into `sum` and the later ones
                 // added the compiler spilled)
+                // 256-column form (one accumulator, the MMAs wait for every drain): the first chunk goes straight into
+                // the sums, all loads in flight at once (conv cfg2, three chunks per item: 68.2 -> 66.5 us). The
+                // 128-column form drains behind the MMAs of the next chunk and was slower with it (capsule 65 -> 70 us).
+                constexpr bool kPeel = UN == 256;
+                if constexpr (!kPeel) {
 #pragma unroll
-                for (int j = 0; j < CW; ++j) sum[j] = 0u;
-                for (int kb0 = 0; kb0 < nkb && ok; kb0 += Cfg::kChunkKb, ++gch) {
+                    for (int j = 0; j < CW; ++j) sum[j] = 0u;
+                } else {
+                    const int acc = gch % AB;
+                    if (!bounded_wait_warp(&cfull_bar[acc], (gch / AB) & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
+                    ptx::tc_fence_after_sync();
+#pragma unroll
+                    for (int c = 0; c < CW / 32; ++c)
+                        ptx::tmem_ld_32x32(lane_base + acc * UN + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sum[c * 32]));
+                    ptx::tmem_ld_wait();
+                    ptx::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive_peer(&cempty_bar[acc], 0);
+                    ++gch;
+                }
+                for (int kb0 = kPeel ? Cfg::kChunkKb : 0; kb0 < nkb && ok; kb0 += Cfg::kChunkKb, ++gch) {
                     const int acc = gch % AB;
                     if (!bounded_wait_warp(&cfull_bar[acc], (gch / AB) & 1, ab, ST_TIMEOUT_EPILOGUE, lane)) { ok = false; break; }
                     ptx::tc_fence_after_sync();
